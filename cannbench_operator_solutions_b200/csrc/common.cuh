@@ -1,0 +1,220 @@
+// Shared device helpers for the W8A8 quantised-FFN kernels (sm_100a).
+//
+// The whole library is compiled with -fmad=false: the operators' results
+// depend on which multiplies and adds are rounded separately, so every fused
+// multiply-add in these sources is an explicit fmaf().
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/w8a8ffn.h"
+
+namespace w8a8 {
+
+constexpr unsigned FULL_MASK = 0xffffffffu;
+constexpr float INV127 = 1.0f / 127.0f;
+
+// ---------------------------------------------------------------------------
+// 16-bit float <-> fp32
+// ---------------------------------------------------------------------------
+template <int DT>
+__device__ __forceinline__ void unpack2(uint32_t p, float& lo, float& hi)
+{
+    if constexpr (DT == W8A8_DT_BF16) {
+        lo = __uint_as_float(p << 16);
+        hi = __uint_as_float(p & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p));
+        lo = f.x;
+        hi = f.y;
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi)
+{
+    if constexpr (DT == W8A8_DT_BF16) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&b);
+    } else {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ float bits16_to_float(uint32_t b)
+{
+    if constexpr (DT == W8A8_DT_BF16) {
+        return __uint_as_float(b << 16);
+    } else {
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ uint16_t float_to_bits16(float v)
+{
+    if constexpr (DT == W8A8_DT_BF16) {
+        return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    } else {
+        return __half_as_ushort(__float2half_rn(v));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// fp32 -> int8 narrowing.
+//
+// "As written" (the reference's two casts): fp32 -> fp16 RNE, then fp16 ->
+// int8 RNE.  For |v| <= 128 the second step is done without a conversion
+// instruction: adding 1536 (= 1.5 * 2^10, where fp16 has unit spacing)
+// rounds to the nearest integer, ties to even, and leaves the two's
+// complement byte in the low 8 bits of the sum's bit pattern.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t narrow4_fp16_fast(float a, float b, float c, float d)
+{
+    const __half2 magic = __floats2half2_rn(1536.0f, 1536.0f);
+    __half2 h01 = __hadd2(__floats2half2_rn(a, b), magic);
+    __half2 h23 = __hadd2(__floats2half2_rn(c, d), magic);
+    return __byte_perm(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23), 0x6420);
+}
+
+// Direct fp32 -> int8 RNE for |v| <= 128: 1.5 * 2^23 trick.
+__device__ __forceinline__ uint32_t narrow4_direct_fast(float a, float b, float c, float d)
+{
+    const float magic = 12582912.0f;
+    const uint32_t ua = __float_as_uint(__fadd_rn(a, magic));
+    const uint32_t ub = __float_as_uint(__fadd_rn(b, magic));
+    const uint32_t uc = __float_as_uint(__fadd_rn(c, magic));
+    const uint32_t ud = __float_as_uint(__fadd_rn(d, magic));
+    const uint32_t ab = __byte_perm(ua, ub, 0x0040);
+    const uint32_t cd = __byte_perm(uc, ud, 0x0040);
+    return __byte_perm(ab, cd, 0x5410);
+}
+
+// Fully general narrowing: any fp32 including NaN (-> 0), inf and values
+// outside the int8 range (saturate).
+template <bool DIRECT>
+__device__ __forceinline__ int narrow1_general(float v)
+{
+    int r;
+    if constexpr (DIRECT) {
+        r = (v != v) ? 0 : __float2int_rn(fminf(fmaxf(v, -128.0f), 127.0f));
+    } else {
+        const __half h = __float2half_rn(v);
+        const float hv = __half2float(h);
+        r = (hv != hv) ? 0 : __float2int_rn(fminf(fmaxf(hv, -128.0f), 127.0f));
+    }
+    return r;
+}
+
+template <bool DIRECT>
+__device__ __forceinline__ uint32_t narrow4_general(float a, float b, float c, float d)
+{
+    const uint32_t ua = static_cast<uint32_t>(narrow1_general<DIRECT>(a)) & 0xffu;
+    const uint32_t ub = static_cast<uint32_t>(narrow1_general<DIRECT>(b)) & 0xffu;
+    const uint32_t uc = static_cast<uint32_t>(narrow1_general<DIRECT>(c)) & 0xffu;
+    const uint32_t ud = static_cast<uint32_t>(narrow1_general<DIRECT>(d)) & 0xffu;
+    return ua | (ub << 8) | (uc << 16) | (ud << 24);
+}
+
+template <bool DIRECT>
+__device__ __forceinline__ uint32_t narrow4_fast(float a, float b, float c, float d)
+{
+    if constexpr (DIRECT) {
+        return narrow4_direct_fast(a, b, c, d);
+    } else {
+        return narrow4_fp16_fast(a, b, c, d);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// One 8-element chunk of a 16-bit row: 128-bit streaming load when the row
+// is 16-byte aligned and a multiple of 8 long, element-wise otherwise
+// (missing elements read as +0, the identity of both row reductions).
+// ---------------------------------------------------------------------------
+template <bool VEC>
+__device__ __forceinline__ uint4 load_chunk16(const uint16_t* row, int c, int64_t N)
+{
+    if constexpr (VEC) {
+        return __ldcs(reinterpret_cast<const uint4*>(row) + c);
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t e = static_cast<int64_t>(c) * 8 + 2 * i;
+            const uint32_t lo = (e < N) ? row[e] : 0u;
+            const uint32_t hi = (e + 1 < N) ? row[e + 1] : 0u;
+            w[i] = lo | (hi << 16);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// gamma-like vectors are re-read by every row: keep them cacheable
+template <bool VEC>
+__device__ __forceinline__ uint4 load_chunk16_cached(const uint16_t* row, int c, int64_t N)
+{
+    if constexpr (VEC) {
+        return __ldg(reinterpret_cast<const uint4*>(row) + c);
+    } else {
+        return load_chunk16<false>(row, c, N);
+    }
+}
+
+template <bool VEC>
+__device__ __forceinline__ void store_chunk16(uint16_t* row, int c, int64_t N, uint4 v)
+{
+    if constexpr (VEC) {
+        __stcs(reinterpret_cast<uint4*>(row) + c, v);
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t e = static_cast<int64_t>(c) * 8 + 2 * i;
+            if (e < N) {
+                row[e] = static_cast<uint16_t>(w[i] & 0xffffu);
+            }
+            if (e + 1 < N) {
+                row[e + 1] = static_cast<uint16_t>(w[i] >> 16);
+            }
+        }
+    }
+}
+
+template <bool VEC>
+__device__ __forceinline__ void store_chunk8(int8_t* row, int c, int64_t N, uint32_t lo, uint32_t hi)
+{
+    if constexpr (VEC) {
+        __stcs(reinterpret_cast<uint2*>(row) + c, make_uint2(lo, hi));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t e = static_cast<int64_t>(c) * 8 + i;
+            if (e < N) {
+                const uint32_t w = (i < 4) ? lo : hi;
+                row[e] = static_cast<int8_t>((w >> (8 * (i & 3))) & 0xffu);
+            }
+        }
+    }
+}
+
+// Largest |.| bit pattern of the eight 16-bit values in a chunk, compared as
+// unsigned integers: orders finite magnitudes, inf above them, NaN above inf.
+__device__ __forceinline__ uint32_t chunk_absmax16(uint4 v, uint32_t m2)
+{
+    m2 = __vmaxu2(m2, v.x & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.y & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.z & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.w & 0x7fff7fffu);
+    return m2;
+}
+
+inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int sm_count();  // cached multiprocessor count of the current device
+
+}  // namespace w8a8

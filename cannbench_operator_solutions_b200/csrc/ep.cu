@@ -1,0 +1,289 @@
+// Expert-parallel bookkeeping kernels for sm_100a: routing plan (stable
+// counting sort by expert), row scatter into expert-major order, and the
+// weighted combine.
+//
+// Layout contract: rows of one expert are contiguous and keep (token, k)
+// order, which is what a rank-major all-to-all followed by the reference's
+// MoeReRouting permutation yields (operators/moererouting/csrc/ops/
+// moe_re_routing/op_kernel/moe_re_routing_launch.h:15-21).  Combine
+// arithmetic: fp32, term = prob * row rounded, then added, ascending k,
+// round-to-nearest-even store (operators/moefinalizerouting/csrc/ops/
+// moe_finalize_routing/op_kernel/moe_finalize_routing_kernel.cpp:15-25,165-170).
+//
+// All three are HBM-bound byte movers: 128-bit accesses, a row read once and
+// written topk times (scatter) or topk rows read and one written (combine).
+#include "common.cuh"
+
+namespace w8a8 {
+
+constexpr int RP_BLOCK = 256;  // pairs per counting block
+
+// workspace layout: int32 block_count[B][E] (becomes the exclusive prefix over
+// blocks), then int64 base[E]
+__global__ void __launch_bounds__(RP_BLOCK) rp_count_kernel(const int32_t* __restrict__ expert_idx, int64_t P,
+                                                            int64_t E, int32_t* __restrict__ block_count,
+                                                            int32_t* __restrict__ bad)
+{
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * RP_BLOCK + threadIdx.x;
+    if (p < P) {
+        const int32_t e = expert_idx[p];
+        if (e < 0 || e >= E) {
+            atomicExch(bad, 1);
+        } else {
+            atomicAdd(&block_count[static_cast<int64_t>(blockIdx.x) * E + e], 1);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024) rp_scan_kernel(int32_t* __restrict__ block_count, int64_t B, int64_t E,
+                                                       int64_t* __restrict__ base, int64_t* __restrict__ count,
+                                                       int64_t* __restrict__ cumsum)
+{
+    for (int64_t e = threadIdx.x; e < E; e += blockDim.x) {
+        int64_t run = 0;
+        for (int64_t b = 0; b < B; ++b) {
+            const int32_t c = block_count[b * E + e];
+            block_count[b * E + e] = static_cast<int32_t>(run);
+            run += c;
+        }
+        count[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int64_t run = 0;
+        for (int64_t e = 0; e < E; ++e) {
+            base[e] = run;
+            run += count[e];
+            cumsum[e] = run;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(RP_BLOCK) rp_place_kernel(const int32_t* __restrict__ expert_idx, int64_t P,
+                                                            int64_t E, const int32_t* __restrict__ block_prefix,
+                                                            const int64_t* __restrict__ base,
+                                                            int64_t* __restrict__ expanded_pos)
+{
+    __shared__ int32_t s_e[RP_BLOCK];
+    const int64_t p = static_cast<int64_t>(blockIdx.x) * RP_BLOCK + threadIdx.x;
+    int32_t e = -1;
+    if (p < P) {
+        e = expert_idx[p];
+    }
+    s_e[threadIdx.x] = e;
+    __syncthreads();
+    if (p < P) {
+        if (e < 0 || e >= E) {
+            expanded_pos[p] = -1;
+            return;
+        }
+        int rank = 0;
+        for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) {
+            rank += (s_e[j] == e) ? 1 : 0;
+        }
+        expanded_pos[p] = base[e] + block_prefix[static_cast<int64_t>(blockIdx.x) * E + e] + rank;
+    }
+}
+
+// One CTA per token: the row is read once and written to its topk slots.
+template <bool VEC>
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __restrict__ src,
+                                                           const float* __restrict__ src_scale,
+                                                           uint8_t* __restrict__ dst, float* __restrict__ dst_scale,
+                                                           const int64_t* __restrict__ pos, int64_t T, int topk,
+                                                           int64_t row_bytes)
+{
+    for (int64_t i = blockIdx.x; i < T; i += gridDim.x) {
+        const uint8_t* s = src + i * row_bytes;
+        if constexpr (VEC) {
+            const int64_t n16 = row_bytes / 16;
+            for (int64_t c = threadIdx.x; c < n16; c += blockDim.x) {
+                const uint4 v = __ldcs(reinterpret_cast<const uint4*>(s) + c);
+                for (int k = 0; k < topk; ++k) {
+                    const int64_t p = pos[i * topk + k];
+                    if (p >= 0) {
+                        __stcs(reinterpret_cast<uint4*>(dst + p * row_bytes) + c, v);
+                    }
+                }
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < row_bytes; c += blockDim.x) {
+                const uint8_t v = s[c];
+                for (int k = 0; k < topk; ++k) {
+                    const int64_t p = pos[i * topk + k];
+                    if (p >= 0) {
+                        dst[p * row_bytes + c] = v;
+                    }
+                }
+            }
+        }
+        if (src_scale != nullptr && dst_scale != nullptr && static_cast<int>(threadIdx.x) < topk) {
+            const int64_t p = pos[i * topk + threadIdx.x];
+            if (p >= 0) {
+                dst_scale[p] = src_scale[i];
+            }
+        }
+    }
+}
+
+// One CTA per token; each thread owns 8-element chunks of the hidden row.
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(256) combine_kernel(const uint16_t* __restrict__ rows,
+                                                      const float* __restrict__ probs,
+                                                      const int64_t* __restrict__ pos, uint16_t* __restrict__ out,
+                                                      int64_t T, int topk, int64_t H)
+{
+    const int nchunks = static_cast<int>((H + 7) / 8);
+    for (int64_t i = blockIdx.x; i < T; i += gridDim.x) {
+        for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[j] = 0.0f;
+            }
+            for (int k = 0; k < topk; ++k) {
+                const int64_t p = pos[i * topk + k];
+                if (p < 0) {
+                    continue;
+                }
+                const float w = probs[i * topk + k];
+                const uint4 v = load_chunk16<VEC>(rows + p * H, c, H);
+                float f[8];
+                unpack2<DT>(v.x, f[0], f[1]);
+                unpack2<DT>(v.y, f[2], f[3]);
+                unpack2<DT>(v.z, f[4], f[5]);
+                unpack2<DT>(v.w, f[6], f[7]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[j] = __fadd_rn(acc[j], __fmul_rn(w, f[j]));
+                }
+            }
+            const uint4 o = make_uint4(pack2<DT>(acc[0], acc[1]), pack2<DT>(acc[2], acc[3]),
+                                       pack2<DT>(acc[4], acc[5]), pack2<DT>(acc[6], acc[7]));
+            store_chunk16<VEC>(out + i * H, c, H, o);
+        }
+    }
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace w8a8
+
+extern "C" size_t w8a8_route_plan_workspace_size(int64_t T, int64_t topk, int64_t E)
+{
+    if (T < 0 || topk <= 0 || E <= 0) {
+        return 0;
+    }
+    const int64_t P = T * topk;
+    const int64_t B = (P + w8a8::RP_BLOCK - 1) / w8a8::RP_BLOCK;
+    size_t bytes = 256;  // error word
+    bytes += w8a8::align_up(static_cast<size_t>(B > 0 ? B : 1) * static_cast<size_t>(E) * sizeof(int32_t), 256);
+    bytes += w8a8::align_up(static_cast<size_t>(E) * sizeof(int64_t), 256);
+    return bytes;
+}
+
+extern "C" int w8a8_route_plan(const int32_t* expert_idx, int64_t T, int64_t topk, int64_t E, int64_t* count,
+                               int64_t* cumsum, int64_t* expanded_pos, void* workspace, size_t workspace_bytes,
+                               void* stream)
+{
+    if (T < 0 || topk <= 0 || E <= 0 || count == nullptr || cumsum == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    if (T > 0 && (expert_idx == nullptr || expanded_pos == nullptr)) {
+        return W8A8_ERR_INVALID;
+    }
+    const size_t need = w8a8_route_plan_workspace_size(T, topk, E);
+    if (workspace == nullptr || workspace_bytes < need) {
+        return W8A8_ERR_WORKSPACE;
+    }
+    if (!w8a8::is_aligned(workspace, 256)) {
+        return W8A8_ERR_ALIGN;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t P = T * topk;
+    const int64_t B = (P + w8a8::RP_BLOCK - 1) / w8a8::RP_BLOCK;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int32_t* bad = reinterpret_cast<int32_t*>(ws);
+    int32_t* block_count = reinterpret_cast<int32_t*>(ws + 256);
+    const size_t bc_bytes = w8a8::align_up(static_cast<size_t>(B > 0 ? B : 1) * E * sizeof(int32_t), 256);
+    int64_t* base = reinterpret_cast<int64_t*>(ws + 256 + bc_bytes);
+    if (cudaMemsetAsync(ws, 0, 256 + bc_bytes, st) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    if (B > 0) {
+        w8a8::rp_count_kernel<<<static_cast<unsigned>(B), w8a8::RP_BLOCK, 0, st>>>(expert_idx, P, E, block_count, bad);
+    }
+    w8a8::rp_scan_kernel<<<1, 1024, 0, st>>>(block_count, B, E, base, count, cumsum);
+    if (B > 0) {
+        w8a8::rp_place_kernel<<<static_cast<unsigned>(B), w8a8::RP_BLOCK, 0, st>>>(expert_idx, P, E, block_count, base,
+                                                                                  expanded_pos);
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_scatter_rows(const void* src, const float* src_scale, void* dst, float* dst_scale,
+                                 const int64_t* expanded_pos, int64_t T, int64_t topk, int64_t row_bytes,
+                                 void* stream)
+{
+    if (T < 0 || topk <= 0 || topk > 256 || row_bytes <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (T == 0) {
+        return W8A8_OK;
+    }
+    if (src == nullptr || dst == nullptr || expanded_pos == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = (row_bytes % 16 == 0) && w8a8::is_aligned(src, 16) && w8a8::is_aligned(dst, 16);
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(T < cap ? T : cap);
+    if (vec) {
+        w8a8::scatter_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
+                                                             static_cast<uint8_t*>(dst), dst_scale, expanded_pos, T,
+                                                             static_cast<int>(topk), row_bytes);
+    } else {
+        w8a8::scatter_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
+                                                              static_cast<uint8_t*>(dst), dst_scale, expanded_pos, T,
+                                                              static_cast<int>(topk), row_bytes);
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out, int64_t T,
+                            int64_t topk, int64_t H, int dtype, void* stream)
+{
+    if (dtype != W8A8_DT_F16 && dtype != W8A8_DT_BF16) {
+        return W8A8_ERR_INVALID;
+    }
+    if (T < 0 || topk <= 0 || H <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (T == 0) {
+        return W8A8_OK;
+    }
+    if (rows == nullptr || probs == nullptr || expanded_pos == nullptr || out == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = (H % 8 == 0) && w8a8::is_aligned(rows, 16) && w8a8::is_aligned(out, 16);
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(T < cap ? T : cap);
+    const uint16_t* r = static_cast<const uint16_t*>(rows);
+    uint16_t* o = static_cast<uint16_t*>(out);
+    const int tk = static_cast<int>(topk);
+    if (dtype == W8A8_DT_BF16) {
+        if (vec) {
+            w8a8::combine_kernel<W8A8_DT_BF16, true><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
+        } else {
+            w8a8::combine_kernel<W8A8_DT_BF16, false><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
+        }
+    } else {
+        if (vec) {
+            w8a8::combine_kernel<W8A8_DT_F16, true><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
+        } else {
+            w8a8::combine_kernel<W8A8_DT_F16, false><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
+        }
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}

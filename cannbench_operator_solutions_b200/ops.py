@@ -1,0 +1,313 @@
+"""The reference's operator interface, backed by libw8a8ffn.so on B200.
+
+Each function keeps the name, argument order, argument meaning and error
+behaviour of the corresponding ``torch.ops.cann_bench.*`` operator of
+ai-jiaqian/cannbench-operator-solutions (schemas cited per function; paths
+relative to that project).  Validation mirrors the reference plugins'
+``TORCH_CHECK``s and raises ``RuntimeError`` like they do.  The work itself is
+one call through the C-ABI on the current CUDA stream; PyTorch only provides
+device memory and the stream.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib as L
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _status(rc: int, op: str) -> None:
+    if rc != L.OK:
+        raise RuntimeError(f"{op}: {L.status_string(rc)} (status {rc})")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return L.DT_F16
+    if t.dtype == torch.bfloat16:
+        return L.DT_BF16
+    if t.dtype == torch.float32:
+        return L.DT_F32
+    if t.dtype == torch.int8:
+        return L.DT_I8
+    raise RuntimeError(f"unsupported dtype {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("w8a8ffn operators run on CUDA tensors only (there is no CPU path)")
+
+
+# ---------------------------------------------------------------------------
+def dynamic_quant(x: torch.Tensor, *, round_direct: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``dynamic_quant(Tensor x) -> (Tensor y, Tensor scale)``
+    (operators/dynamicquant/csrc/ops/dynamic_quant/op_plugin/dynamic_quant_plugin.cpp:30,33-87)."""
+    _check(x.dim() >= 2, "dynamic_quant requires a tensor with rank >= 2.")
+    _check(x.dtype in (torch.float16, torch.bfloat16), "dynamic_quant only supports float16 / bfloat16 inputs.")
+    _need_cuda(x)
+    xc = x.contiguous()
+    y = torch.empty_like(xc, dtype=torch.int8)
+    scale = torch.empty(xc.shape[:-1], dtype=torch.float32, device=xc.device)
+    n = xc.size(-1)
+    _check(n > 0, "dynamic_quant requires a non-zero last dimension.")
+    m = xc.numel() // n
+    if m <= 0:
+        return y, scale
+    with torch.cuda.device(xc.device):
+        rc = L.load().w8a8_dynamic_quant(xc.data_ptr(), y.data_ptr(), scale.data_ptr(), m, n, _dt(xc),
+                                         L.F_ROUND_DIRECT if round_direct else 0, _stream())
+    _status(rc, "dynamic_quant")
+    return y, scale
+
+
+def add_rms_norm_dynamic_quant(x1: torch.Tensor, x2: torch.Tensor, gamma: torch.Tensor, epsilon: float, *,
+                               round_direct: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``add_rms_norm_dynamic_quant(Tensor x1, Tensor x2, Tensor gamma, float epsilon) -> (y, xOut, scaleOut)``
+    (operators/addrmsnormdynamicquant/csrc/ops/add_rms_norm_dynamic_quant/op_plugin/add_rms_norm_dynamic_quant_plugin.cpp:32,36-112)."""
+    _check(x1.dim() >= 1, "add_rms_norm_dynamic_quant: x1 must have at least one dimension.")
+    _check(x1.shape == x2.shape, "add_rms_norm_dynamic_quant: x1 and x2 must have the same shape.")
+    _check(gamma.dim() == 1 and gamma.size(0) == x1.size(-1),
+           "add_rms_norm_dynamic_quant: gamma must be 1-D with the size of the last dimension.")
+    _check(x1.dtype == x2.dtype == gamma.dtype, "add_rms_norm_dynamic_quant: x1, x2 and gamma must share a dtype.")
+    _need_cuda(x1, x2, gamma)
+    x1c, x2c, gc = x1.contiguous(), x2.contiguous(), gamma.contiguous()
+    y = torch.empty_like(x1c, dtype=torch.int8)
+    x_out = torch.empty_like(x1c)
+    scale = torch.empty(x1c.shape[:-1], dtype=torch.float32, device=x1c.device)
+    n = x1c.size(-1)
+    if x1c.numel() == 0 or n <= 0:
+        return y, x_out, scale
+    _check(x1c.dtype in (torch.float16, torch.bfloat16),
+           "add_rms_norm_dynamic_quant: only float16/bfloat16 inputs are supported.")
+    _check(n <= 16384, "add_rms_norm_dynamic_quant: row length must not exceed 16384.")
+    rows = x1c.numel() // n
+    with torch.cuda.device(x1c.device):
+        rc = L.load().w8a8_add_rms_norm_dynamic_quant(x1c.data_ptr(), x2c.data_ptr(), gc.data_ptr(), y.data_ptr(),
+                                                      x_out.data_ptr(), scale.data_ptr(), rows, n, float(epsilon),
+                                                      _dt(x1c), L.F_ROUND_DIRECT if round_direct else 0, _stream())
+    _status(rc, "add_rms_norm_dynamic_quant")
+    return y, x_out, scale
+
+
+def quant_matmul(x1: torch.Tensor, x2: torch.Tensor, scale: torch.Tensor, *, offset: Optional[torch.Tensor] = None,
+                 pertoken_scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                 output_dtype: Optional[str] = None, transpose_x2: bool = False) -> torch.Tensor:
+    """``quant_matmul(Tensor x1, Tensor x2, Tensor scale, *, Tensor? offset, Tensor? pertoken_scale, Tensor? bias,
+    str? output_dtype) -> Tensor`` (operators/quantmatmul/csrc/ops/quant_matmul/op_plugin/quant_matmul_plugin.cpp:48-49,77-267).
+
+    ``transpose_x2=True`` (not in the reference) takes x2 as [..., N, K]."""
+    _check(x1.dtype == torch.int8 and x2.dtype == torch.int8, "quant_matmul requires int8 x1 and x2.")
+    _check(x1.is_contiguous() and x2.is_contiguous() and scale.is_contiguous(),
+           "quant_matmul requires contiguous x1/x2/scale.")
+    _check(scale.dtype in (torch.float32, torch.bfloat16), "quant_matmul requires float32 or bfloat16 scale.")
+    _check(x1.dim() >= 2 and x2.dim() >= 2 and x1.dim() == x2.dim(), "quant_matmul expects equal ranks >= 2.")
+    k = x1.size(-1)
+    m = x1.size(-2)
+    n = x2.size(-2) if transpose_x2 else x2.size(-1)
+    _check(k == (x2.size(-1) if transpose_x2 else x2.size(-2)), "quant_matmul requires x1.size(-1) == x2.size(-2).")
+    _check(k > 0 and m > 0 and n > 0, "quant_matmul requires non-empty shapes.")
+    _need_cuda(x1, x2, scale, offset, pertoken_scale, bias)
+    batch = 1
+    for d in range(x1.dim() - 2):
+        _check(x1.size(d) == x2.size(d), "quant_matmul expects matching leading batch dimensions.")
+        batch *= x1.size(d)
+    bf16out = output_dtype == "bfloat16"
+    out = torch.empty(tuple(x1.shape[:-1]) + (n,), dtype=torch.bfloat16 if bf16out else torch.float16,
+                      device=x1.device)
+    flags = 0
+    _check(scale.numel() in (1, n), "quant_matmul expects scale length 1 or n.")
+    if scale.numel() > 1:
+        flags |= L.QM_SCALE_PERCHAN
+    if scale.dtype == torch.bfloat16:
+        flags |= L.QM_SCALE_BF16
+    if offset is not None:
+        _check(offset.dtype == torch.float32 and offset.is_contiguous(),
+               "quant_matmul requires float32 contiguous offset.")
+        _check(offset.numel() in (1, n), "quant_matmul expects offset length 1 or n.")
+        flags |= L.QM_HAS_OFFSET
+        if offset.numel() > 1:
+            flags |= L.QM_OFFSET_PERCHAN
+    if pertoken_scale is not None:
+        _check(pertoken_scale.dtype == torch.float32 and pertoken_scale.is_contiguous(),
+               "quant_matmul requires float32 contiguous pertoken_scale.")
+        _check(pertoken_scale.numel() == m, "quant_matmul expects pertoken_scale length m.")
+        flags |= L.QM_HAS_PT
+    bias_batch_stride = 0
+    if bias is not None:
+        _check(bias.is_contiguous(), "quant_matmul requires contiguous bias.")
+        kind = {torch.int32: L.QM_BIAS_I32, torch.float16: L.QM_BIAS_F16, torch.bfloat16: L.QM_BIAS_BF16,
+                torch.float32: L.QM_BIAS_F32}.get(bias.dtype)
+        _check(kind is not None, f"quant_matmul unsupported bias dtype: {bias.dtype}")
+        if bias.dim() == 3 and bias.size(1) == 1 and bias.size(2) == n and batch > 1 and bias.size(0) == batch:
+            bias_batch_stride = n
+            perchan = n > 1
+        else:
+            _check(bias.numel() in (1, n), "quant_matmul expects bias length 1 or n.")
+            perchan = bias.numel() > 1
+        flags |= kind << L.QM_BIAS_SHIFT
+        if perchan:
+            flags |= L.QM_BIAS_PERCHAN
+    if batch > 1:
+        flags |= L.QM_PT_MOD_M
+    with torch.cuda.device(x1.device):
+        rc = L.load().w8a8_quant_matmul(x1.data_ptr(), x2.data_ptr(), scale.data_ptr(), _ptr(offset),
+                                        _ptr(pertoken_scale), _ptr(bias), out.data_ptr(), batch, m, n, k, flags,
+                                        L.DT_BF16 if bf16out else L.DT_F16, L.W_NK if transpose_x2 else L.W_KN,
+                                        bias_batch_stride, _stream())
+    _status(rc, "quant_matmul")
+    return out
+
+
+GroupList = Union[Sequence[int], torch.Tensor]
+
+
+def _group_list(group_list: GroupList, e: int, m: int, op: str):
+    """Returns (pointer, on_device, keepalive).  A Python sequence is the reference's host attribute and is
+    validated here exactly like the plugins do; a CUDA int64 tensor is passed through untouched."""
+    if isinstance(group_list, torch.Tensor) and group_list.is_cuda:
+        _check(group_list.dtype == torch.int64 and group_list.is_contiguous() and group_list.numel() == e,
+               f"{op}: a device group_list must be a contiguous int64 tensor of length E")
+        return group_list.data_ptr(), 1, group_list
+    vals = [int(v) for v in (group_list.tolist() if isinstance(group_list, torch.Tensor) else group_list)]
+    _check(len(vals) == e, f"{op}: group_list length must equal the expert count")
+    prev = 0
+    for v in vals:
+        _check(prev <= v <= m, f"{op}: group_list must be a cumsum <= M")
+        prev = v
+    _check(prev == m, f"{op}: group_list[-1] must equal M")
+    host = torch.tensor(vals, dtype=torch.int64)
+    return host.data_ptr(), 0, host
+
+
+def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor,
+                                x_scale: torch.Tensor, group_list: GroupList, *, transpose_weight: bool = False,
+                                round_direct: bool = False,
+                                workspace: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``grouped_matmul_swiglu_quant(Tensor x, Tensor weight, Tensor weight_scale, Tensor x_scale, int[] group_list)
+    -> (Tensor y, Tensor y_scale)`` (operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:40-41,67-145).
+
+    Beyond the reference: any expert count (the reference stops at 64), ``group_list`` may be a CUDA int64
+    tensor, ``transpose_weight=True`` takes weight as [E, N, K], and a caller-owned ``workspace`` avoids the
+    per-call allocation."""
+    _check(x.dim() == 2, "grouped_matmul_swiglu_quant: x must be 2D [M, K]")
+    _check(weight.dim() == 3, "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]")
+    _check(x.dtype == torch.int8, "grouped_matmul_swiglu_quant: x must be int8")
+    _check(weight.dtype == torch.int8, "grouped_matmul_swiglu_quant: weight must be int8")
+    _check(weight_scale.dtype == torch.float32, "grouped_matmul_swiglu_quant: weight_scale must be float32")
+    _check(x_scale.dtype == torch.float32, "grouped_matmul_swiglu_quant: x_scale must be float32")
+    _need_cuda(x, weight, weight_scale, x_scale)
+    xc, wc, wsc, xsc = x.contiguous(), weight.contiguous(), weight_scale.contiguous(), x_scale.contiguous()
+    m, k = xc.shape
+    e = wc.size(0)
+    n = wc.size(1) if transpose_weight else wc.size(2)
+    _check(n % 2 == 0, "grouped_matmul_swiglu_quant: N must be even")
+    y = torch.empty((m, n // 2), dtype=torch.int8, device=xc.device)
+    y_scale = torch.empty((m,), dtype=torch.float32, device=xc.device)
+    if m == 0 or n == 0 or e == 0:
+        return y, y_scale
+    _check((wc.size(2) if transpose_weight else wc.size(1)) == k,
+           "grouped_matmul_swiglu_quant: K mismatch between x and weight")
+    _check(xsc.numel() == m, "grouped_matmul_swiglu_quant: x_scale must have M elements")
+    _check(wsc.dim() == 2 and wsc.size(0) == e and wsc.size(1) == n,
+           "grouped_matmul_swiglu_quant: weight_scale must be [E, N]")
+    gl_ptr, on_dev, keep = _group_list(group_list, e, m, "grouped_matmul_swiglu_quant")
+    lib = L.load()
+    need = lib.w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e)
+    if workspace is None:
+        workspace = torch.empty((need,), dtype=torch.uint8, device=xc.device)
+    _check(workspace.is_cuda and workspace.numel() * workspace.element_size() >= need,
+           "grouped_matmul_swiglu_quant: workspace too small")
+    with torch.cuda.device(xc.device):
+        rc = lib.w8a8_grouped_matmul_swiglu_quant(xc.data_ptr(), wc.data_ptr(), wsc.data_ptr(), xsc.data_ptr(),
+                                                  y.data_ptr(), y_scale.data_ptr(), m, k, n, e, gl_ptr, on_dev,
+                                                  L.W_NK if transpose_weight else L.W_KN,
+                                                  L.F_ROUND_DIRECT if round_direct else 0, workspace.data_ptr(),
+                                                  workspace.numel() * workspace.element_size(), _stream())
+    del keep
+    _status(rc, "grouped_matmul_swiglu_quant")
+    return y, y_scale
+
+
+def grouped_matmul(x: torch.Tensor, weight: torch.Tensor, group_list: GroupList,
+                   bias: Optional[torch.Tensor] = None, split_item: int = 0, transpose_weight: bool = False, *,
+                   x_scale: Optional[torch.Tensor] = None, weight_scale: Optional[torch.Tensor] = None,
+                   output_dtype: Optional[torch.dtype] = None,
+                   workspace: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    """``grouped_matmul(Tensor x, Tensor weight, int[] group_list, Tensor? bias=None, int split_item=0,
+    bool transpose_weight=False) -> Tensor[]`` (operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:42-43,120-183).
+
+    ``split_item`` 0/1 returns one view per expert of the joined [M, N] result, 2/3 the joined tensor
+    (grouped_matmul_plugin.cpp:65-80).  Beyond the reference: int8 ``x``/``weight`` with ``x_scale`` [M] and
+    ``weight_scale`` [E, N] (the quantised down projection; output ``output_dtype``, default bfloat16), any
+    expert count, device group lists."""
+    _check(x.dim() == 2, "grouped_matmul: x must be 2D [M, K]")
+    _check(weight.dim() == 3, "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]")
+    _need_cuda(x, weight, bias, x_scale, weight_scale)
+    xc, wc = x.contiguous(), weight.contiguous()
+    m, k = xc.shape
+    e = wc.size(0)
+    _check(e >= 1, "grouped_matmul: weight must contain at least one expert")
+    n = wc.size(1) if transpose_weight else wc.size(2)
+    _check((wc.size(2) if transpose_weight else wc.size(1)) == k,
+           "grouped_matmul: K dimension mismatch between x and weight")
+    _check(xc.dtype == wc.dtype, "grouped_matmul: x and weight must share a dtype")
+    dt = _dt(xc)
+    quant = dt == L.DT_I8
+    if quant:
+        _check(x_scale is not None and weight_scale is not None,
+               "grouped_matmul: int8 inputs need x_scale and weight_scale")
+        _check(x_scale.dtype == torch.float32 and x_scale.numel() == m, "grouped_matmul: x_scale must be fp32 [M]")
+        _check(weight_scale.dtype == torch.float32 and weight_scale.numel() == e * n,
+               "grouped_matmul: weight_scale must be fp32 [E, N]")
+        out_dtype = output_dtype or torch.bfloat16
+        _check(out_dtype in (torch.bfloat16, torch.float16), "grouped_matmul: output_dtype must be fp16 or bf16")
+    else:
+        _check(dt in (L.DT_F16, L.DT_BF16, L.DT_F32), "grouped_matmul: unsupported dtype")
+        _check(x_scale is None and weight_scale is None, "grouped_matmul: scales are only valid with int8 inputs")
+        out_dtype = xc.dtype
+    bc = None
+    if bias is not None:
+        bc = bias.contiguous()
+        _check(bc.numel() == e * n, "grouped_matmul: bias must have shape [E, N]")
+    gl_ptr, on_dev, keep = _group_list(group_list, e, m, "grouped_matmul")
+    y = torch.empty((m, n), dtype=out_dtype, device=xc.device)
+    if m > 0:
+        lib = L.load()
+        need = lib.w8a8_grouped_matmul_workspace_size(m, n, k, e)
+        if workspace is None:
+            workspace = torch.empty((max(need, 1),), dtype=torch.uint8, device=xc.device)
+        _check(workspace.numel() * workspace.element_size() >= need, "grouped_matmul: workspace too small")
+        xs = x_scale.contiguous() if x_scale is not None else None
+        ws = weight_scale.contiguous() if weight_scale is not None else None
+        with torch.cuda.device(xc.device):
+            rc = lib.w8a8_grouped_matmul(xc.data_ptr(), wc.data_ptr(), _ptr(bc), y.data_ptr(), _ptr(xs), _ptr(ws), m,
+                                         n, k, e, gl_ptr, on_dev, dt, _dt(bc) if bc is not None else dt,
+                                         _dt(y), L.W_NK if transpose_weight else L.W_KN, workspace.data_ptr(),
+                                         workspace.numel() * workspace.element_size(), _stream())
+        _status(rc, "grouped_matmul")
+    del keep
+    if split_item in (0, 1):
+        _check(not (isinstance(group_list, torch.Tensor) and group_list.is_cuda),
+               "grouped_matmul: split_item 0/1 needs a host group_list to build the per-expert views")
+        ends = [int(v) for v in group_list]
+        outs, s = [], 0
+        for v in ends:
+            outs.append(y.narrow(0, s, v - s))
+            s = v
+        return outs
+    return [y]

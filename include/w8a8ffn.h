@@ -1,0 +1,193 @@
+/*
+ * libw8a8ffn -- C ABI of the B200 (sm_100a) W8A8 quantised-FFN operators.
+ *
+ * Every entry point is the CUDA counterpart of one launcher (or launcher
+ * pair) of the Ascend operator catalog ai-jiaqian/cannbench-operator-solutions;
+ * the comment on each declaration names the reference interface it replaces
+ * (paths relative to that project's root).  The Ascend tiling arguments
+ * (numBlocks, rowsPerCore, ...) have no meaning here and are dropped: tiling
+ * is internal.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless the parameter says "host".
+ *   - The caller owns every buffer, including workspaces, whose size comes
+ *     from the matching *_workspace_size() query.  The library allocates
+ *     nothing and keeps no mutable global state besides cached function
+ *     attributes.
+ *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is
+ *     the legacy default stream) and the call returns without synchronising.
+ *   - Return value: W8A8_OK or a negative W8A8_ERR_* code.  Nothing throws.
+ *     A call with zero rows is a successful no-op, as in the reference
+ *     plugins.
+ *   - dtype codes: W8A8_DT_F16 / W8A8_DT_BF16 / W8A8_DT_F32 / W8A8_DT_I8.
+ *   - Row-major, densely packed tensors.  Rows that are 16-byte aligned
+ *     take the vectorised kernels; anything else takes a slower generic path
+ *     with identical results.
+ */
+#ifndef W8A8FFN_H
+#define W8A8FFN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define W8A8_OK 0
+#define W8A8_ERR_INVALID (-1)     /* bad shape, dtype, flag or null pointer          */
+#define W8A8_ERR_ALIGN (-2)       /* a pointer or pitch misses a required alignment   */
+#define W8A8_ERR_GROUP_LIST (-3)  /* group list not a non-decreasing cumsum ending at M */
+#define W8A8_ERR_WORKSPACE (-4)   /* workspace missing or too small                   */
+#define W8A8_ERR_CUDA (-5)        /* a CUDA runtime / driver call failed              */
+#define W8A8_ERR_UNSUPPORTED (-6) /* valid in the reference, not implemented here     */
+
+#define W8A8_DT_F16 0
+#define W8A8_DT_BF16 1
+#define W8A8_DT_F32 2
+#define W8A8_DT_I8 3
+
+/* `flags` of the quantising operators */
+#define W8A8_F_ROUND_DIRECT 1 /* fp32 -> int8 in one rounding instead of the
+                                 reference's fp32 -> fp16 -> int8 */
+
+/* weight layout of the matmuls */
+#define W8A8_W_KN 0 /* [.., K, N], N contiguous: the reference's layout       */
+#define W8A8_W_NK 1 /* [.., N, K], K contiguous: transpose_weight=True layout */
+
+/* quant_matmul epilogue flag word; identical bit layout to the reference's
+ * QM_F_* (operators/quantmatmul/csrc/ops/quant_matmul/op_kernel/quant_matmul_launch.h:39-53) */
+#define W8A8_QM_SCALE_PERCHAN (1LL << 0)
+#define W8A8_QM_SCALE_BF16 (1LL << 1)
+#define W8A8_QM_HAS_OFFSET (1LL << 2)
+#define W8A8_QM_OFFSET_PERCHAN (1LL << 3)
+#define W8A8_QM_HAS_PT (1LL << 4)
+#define W8A8_QM_BIAS_SHIFT 5
+#define W8A8_QM_BIAS_MASK (7LL << W8A8_QM_BIAS_SHIFT)
+#define W8A8_QM_BIAS_PERCHAN (1LL << 8)
+#define W8A8_QM_PT_MOD_M (1LL << 9)
+#define W8A8_QM_BIAS_NONE 0
+#define W8A8_QM_BIAS_I32 1
+#define W8A8_QM_BIAS_F16 2
+#define W8A8_QM_BIAS_BF16 3
+#define W8A8_QM_BIAS_F32 4
+
+/* Library identification and error text. */
+int w8a8_version(void);
+const char* w8a8_status_string(int status);
+
+/*
+ * DynamicQuant: per-row absmax int8 quantisation of x[M, N] (fp16 / bf16).
+ *   scale[m] = max(amax_m, 1e-12) * (1/127);  y = narrow(x * ((1/amax_m) * 127))
+ * Replaces launch_dynamic_quant_half / launch_dynamic_quant_bfloat16
+ * (operators/dynamicquant/csrc/ops/dynamic_quant/op_kernel/dynamic_quant_launch.h:29-41).
+ */
+int w8a8_dynamic_quant(const void* x, int8_t* y, float* scale, int64_t M, int64_t N, int dtype,
+                       int flags, void* stream);
+
+/*
+ * AddRmsNormDynamicQuant: x_out = x1 + x2 (rounded to dtype on store),
+ * RMSNorm * gamma, per-row absmax int8 quantisation.  N <= 16384.
+ * Replaces launch_ardq_half / launch_ardq_bf16
+ * (operators/addrmsnormdynamicquant/csrc/ops/add_rms_norm_dynamic_quant/op_kernel/add_rms_norm_dynamic_quant_launch.h:32-41).
+ */
+int w8a8_add_rms_norm_dynamic_quant(const void* x1, const void* x2, const void* gamma, int8_t* y,
+                                    void* x_out, float* scale_out, int64_t rows, int64_t N,
+                                    float epsilon, int dtype, int flags, void* stream);
+
+/*
+ * QuantMatmul: out[b] = epilogue(x1[b] @ x2[b]), int8 x int8 -> int32 on the
+ * tensor cores with the dequant chain fused into the epilogue (no int32
+ * workspace):  ((float(acc) + i32bias) * scale + offset) * pertoken + fbias,
+ * rounded to out_dtype (F16 or BF16).
+ * Replaces the pair qm_launch_cube_i32 + qm_launch_epilogue_{f16,bf16} and the
+ * tiling helper qm_calc_cube_tiling
+ * (operators/quantmatmul/csrc/ops/quant_matmul/op_kernel/quant_matmul_launch.h:80-99).
+ *   x1 int8 [batch, M, K]; x2 int8 [batch, K, N] (W8A8_W_KN) or [batch, N, K]
+ *   (W8A8_W_NK); scale fp32|bf16 [1|N]; offset fp32 [1|N] or NULL; pertoken
+ *   fp32 [M] or NULL; bias per flags or NULL, optionally batched [batch, N]
+ *   (bias_batch_stride = N elements, else 0).
+ * K and N must be multiples of 16.
+ */
+int w8a8_quant_matmul(const int8_t* x1, const int8_t* x2, const void* scale, const float* offset,
+                      const float* pertoken, const void* bias, void* out, int64_t batch, int64_t M,
+                      int64_t N, int64_t K, int64_t flags, int out_dtype, int x2_layout,
+                      int64_t bias_batch_stride, void* stream);
+
+/*
+ * GroupedMatmulSwigluQuant: per expert g (rows [cumsum[g-1], cumsum[g])):
+ *   acc = x[rows_g] @ w[g]; l = (float(acc[:, :N/2]) * x_scale) * w_scale[g, :N/2];
+ *   u likewise for the right half; act = silu(l) * u;
+ *   y_scale = max(FLT_MIN, max|act|) * (1/127); y = narrow(clamp(act * (127/amax)))
+ * Replaces launch_gmsq_cube + launch_gmsq_vec and the gmsq_calc_* queries
+ * (operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_kernel/gmsq_launch.h:48-82).
+ * The reference carries at most 64 group ends by value; here `group_list` is
+ * an int64 cumulative list of length E in host memory (validated, then passed
+ * by value, E <= 1024) or in device memory (list_on_device = 1; validated on
+ * the device: an invalid list leaves y untouched and sets a flag readable
+ * with w8a8_workspace_error()).
+ *   x int8 [M, K]; w int8 [E, K, N] (W8A8_W_KN) or [E, N, K] (W8A8_W_NK);
+ *   w_scale fp32 [E, N]; x_scale fp32 [M]; y int8 [M, N/2]; y_scale fp32 [M].
+ * K a multiple of 16, N a multiple of 32.
+ */
+size_t w8a8_grouped_matmul_swiglu_quant_workspace_size(int64_t M, int64_t K, int64_t N, int64_t E);
+int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w, const float* w_scale,
+                                     const float* x_scale, int8_t* y, float* y_scale, int64_t M,
+                                     int64_t K, int64_t N, int64_t E, const int64_t* group_list,
+                                     int list_on_device, int w_layout, int flags, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+
+/*
+ * GroupedMatmul: y[rows_g] = x[rows_g] @ w[g] (+ bias[g]).
+ * Replaces launch_gmm and calc_gmm_workspace_size
+ * (operators/groupedmatmul/csrc/ops/grouped_matmul/op_kernel/grouped_matmul_launch.h:50-71).
+ *   dtype F16 / BF16: the reference's float path, fp32 accumulate, output in
+ *   dtype (x_scale, w_scale NULL).
+ *   dtype I8: the quantised down projection the reference operator lacks:
+ *   int32 accumulate, (float(acc) * w_scale[g, n]) * x_scale[m] (+ bias),
+ *   rounded to out_dtype.
+ * group_list as for grouped_matmul_swiglu_quant.
+ */
+size_t w8a8_grouped_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t E);
+int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y,
+                        const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K,
+                        int64_t E, const int64_t* group_list, int list_on_device, int dtype,
+                        int bias_dtype, int out_dtype, int w_layout, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Reads (synchronously, on `stream`) the device-side error word a grouped
+ * call left in its workspace: 0 = none, 1 = invalid device group list,
+ * 2 = a pipeline wait ran out. */
+int w8a8_workspace_error(const void* workspace, void* stream);
+
+/*
+ * Expert-parallel helpers (the layout contract of MoeReRouting and the
+ * arithmetic of MoeFinalizeRouting, which the reference keeps in separate
+ * operators: operators/moererouting/csrc/ops/moe_re_routing/op_kernel/moe_re_routing_launch.h:15-21,
+ * operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_kernel/moe_finalize_routing_kernel.cpp:15-25).
+ *
+ * w8a8_route_plan: stable counting sort of the T*topk (token, k) pairs by
+ * expert.  Writes count[E], the inclusive cumsum[E] (the group list) and
+ * expanded_pos[T*topk] (row of each pair in expert-major order), all int64.
+ * workspace: w8a8_route_plan_workspace_size(T, topk, E) bytes.
+ */
+size_t w8a8_route_plan_workspace_size(int64_t T, int64_t topk, int64_t E);
+int w8a8_route_plan(const int32_t* expert_idx, int64_t T, int64_t topk, int64_t E, int64_t* count,
+                    int64_t* cumsum, int64_t* expanded_pos, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* dst[pos[i*topk+k]] = src[i] for row payloads of row_bytes (int8 tokens) and
+ * dst_scale likewise for the fp32 per-token scales (may be NULL). */
+int w8a8_scatter_rows(const void* src, const float* src_scale, void* dst, float* dst_scale,
+                      const int64_t* expanded_pos, int64_t T, int64_t topk, int64_t row_bytes,
+                      void* stream);
+
+/* out[i, :] = sum_k probs[i, k] * rows[pos[i*topk+k], :], fp32, ascending k,
+ * rounded to dtype (F16 / BF16).  A negative position contributes nothing. */
+int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,
+                 int64_t T, int64_t topk, int64_t H, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W8A8FFN_H */
