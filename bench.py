@@ -1,0 +1,551 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 quantised-FFN hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One step is one pass of the operator over one batch of seeded synthetic input
+shaped like the configuration BASELINE.json quotes its metric on.  Workloads:
+
+    gmsq   grouped_matmul_swiglu_quant, E=256, 131072 rows (Zipf 1.1), K=7168, N=4096 (int8 TOPS)   [default]
+    ardq   add_rms_norm_dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
+    dq     dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
+    qmm    quant_matmul, M=8192 K=7168 N=18432 (int8 TOPS)
+
+Rank 0 prints ONE JSON line.  `value` is the device-timed throughput with
+inputs resident in HBM; `e2e` is the same metric through the operator call
+with HOST (pinned) buffers, host<->device copies inside the timed region;
+`roofline` is the dominant kernel against the measured peak; `cpu_baseline`
+is the CPU oracle timed on this machine's host cores on a bounded sample.
+`--impl reference` times the CPU oracle alone (the reference's kernels only
+build with the Ascend toolchain, so the oracle is the reference's CPU
+implementation of the path here).
+
+With N > 1 (torchrun) the grouped workload is expert-parallel: rank r owns
+experts [r*E/N, (r+1)*E/N) and their rows; there is no data-path collective,
+ranks only meet at the timing barriers.  Per-GPU work shrinks as N grows
+(strong scaling of the configuration's fixed total).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+INT8_PER_BF16 = 2.0  # tcgen05 kind::i8 issues twice the MACs of kind::f16 per instruction
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for p in self.samples:
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------
+def zipf_counts(rng, rows, experts, s=1.1):
+    p = np.arange(1, experts + 1, dtype=np.float64) ** (-s)
+    p /= p.sum()
+    return rng.multinomial(rows, p).astype(np.int64)
+
+
+class Workload:
+    name = ""
+    metric = ""
+    unit = ""
+    dtype = ""
+    bound = "hbm"
+
+    def gpu_setup(self, torch, rank, world):  # device-resident inputs
+        raise NotImplementedError
+
+    def gpu_step(self):
+        raise NotImplementedError
+
+    def units_per_step(self):  # numerator of the metric (bytes or ops), whole job share of this rank
+        raise NotImplementedError
+
+
+class ArdqWorkload(Workload):
+    """BASELINE configs[1]: x, residual bf16 [8192, 7168], gamma ~ N(1, 0.1), eps 1e-6."""
+    name, metric, unit, dtype, bound = "add_rms_norm_dynamic_quant", "rmsnorm_quant_hbm_gbs", "GB/s", "f32", "hbm"
+    rows, n = 8192, 7168
+    kernels_per_step = 1
+
+    def config(self, world):
+        return {"workload": "configs[1]: add_rms_norm_dynamic_quant [8192,7168] bf16, eps=1e-6",
+                "rows_per_gpu": self.rows, "hidden": self.n, "l2": "inputs (235 MB) larger than L2",
+                "parallelism": f"rows x{world}" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops = torch, pkg.ops
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        self.x1 = torch.randn((self.rows, self.n), generator=g, device="cuda").to(torch.bfloat16)
+        self.x2 = torch.randn((self.rows, self.n), generator=g, device="cuda").to(torch.bfloat16)
+        self.gamma = (1 + 0.1 * torch.randn((self.n,), generator=g, device="cuda")).to(torch.bfloat16)
+        self.scaling = "weak"
+
+    def gpu_step(self):
+        return self.ops.add_rms_norm_dynamic_quant(self.x1, self.x2, self.gamma, 1e-6)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def bytes_per_step(self):
+        return self.rows * (7 * self.n + 4) + 2 * self.n
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def roofline_units(self):
+        return self.bytes_per_step() / 1e9
+
+    def host_inputs(self):
+        t = self.torch
+        return [self.x1.cpu().pin_memory(), self.x2.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        t = self.torch
+        x1 = host[0].to("cuda", non_blocking=True)
+        x2 = host[1].to("cuda", non_blocking=True)
+        y, xo, sc = self.ops.add_rms_norm_dynamic_quant(x1, x2, self.gamma, 1e-6)
+        outs = [y.to("cpu", non_blocking=True), xo.to("cpu", non_blocking=True), sc.to("cpu", non_blocking=True)]
+        return (host[0].numel() * 2 + host[1].numel() * 2, sum(o.numel() * o.element_size() for o in outs))
+
+    def cpu_sample(self, O):
+        rows = 1024
+        rng = np.random.default_rng(0)
+        x1 = O.f32_to_bf16_bits(rng.standard_normal((rows, self.n)).astype(np.float32))
+        x2 = O.f32_to_bf16_bits(rng.standard_normal((rows, self.n)).astype(np.float32))
+        g = O.f32_to_bf16_bits((1 + 0.1 * rng.standard_normal(self.n)).astype(np.float32))
+        units = (rows * (7 * self.n + 4) + 2 * self.n) / 1e9
+        return (lambda: O.add_rms_norm_dynamic_quant(x1, x2, g, 1e-6, O.DT_BF16)), units, f"{rows} of 8192 rows"
+
+
+class DqWorkload(ArdqWorkload):
+    name, metric = "dynamic_quant", "dynamic_quant_hbm_gbs"
+
+    def config(self, world):
+        c = super().config(world)
+        c["workload"] = "configs[1]: standalone dynamic_quant [8192,7168] bf16"
+        c["l2"] = "input (117 MB) + output (59 MB) larger than L2"
+        return c
+
+    def gpu_step(self):
+        return self.ops.dynamic_quant(self.x1)
+
+    def bytes_per_step(self):
+        return self.rows * (3 * self.n + 4)
+
+    def host_inputs(self):
+        return [self.x1.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        y, s = self.ops.dynamic_quant(x)
+        outs = [y.to("cpu", non_blocking=True), s.to("cpu", non_blocking=True)]
+        return (host[0].numel() * 2, sum(o.numel() * o.element_size() for o in outs))
+
+    def cpu_sample(self, O):
+        rows = 2048
+        rng = np.random.default_rng(0)
+        x = O.f32_to_bf16_bits(rng.standard_normal((rows, self.n)).astype(np.float32))
+        return (lambda: O.dynamic_quant(x, O.DT_BF16)), rows * (3 * self.n + 4) / 1e9, f"{rows} of 8192 rows"
+
+
+class GmsqWorkload(Workload):
+    """BASELINE configs[3]: E=256, 131072 rows with Zipf(1.1) group sizes, K=7168, N=4096."""
+    name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "s8",
+                                        "tensor")
+    E, M, K, N = 256, 131072, 7168, 4096
+
+    def __init__(self, small=False):
+        if small:
+            self.E, self.M, self.K, self.N = 16, 4096, 1024, 1024
+
+    def config(self, world):
+        return {"workload": f"configs[3]: grouped_matmul_swiglu_quant E={self.E} rows={self.M} (Zipf 1.1) "
+                            f"K={self.K} N={self.N}, weights [E,K,N] int8",
+                "experts_per_gpu": self.E // world, "l2": "weights (7.5 GB) and activations larger than L2",
+                "parallelism": f"ep{world}" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
+        rng = np.random.default_rng(0)
+        counts = zipf_counts(rng, self.M, self.E)
+        # expert-parallel shard: a contiguous block of experts and the rows routed to them.  Interleaving the
+        # popularity ranks across ranks keeps the shards' row counts close (rank r takes experts r, r+N, ...).
+        mine = np.arange(rank, self.E, world)
+        self.counts = counts[mine]
+        self.gl = [int(v) for v in np.cumsum(self.counts)]
+        self.m = int(self.counts.sum())
+        self.e = len(mine)
+        self.total_rows = int(counts.sum())
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        self.x = torch.randint(-127, 128, (self.m, self.K), generator=g, device="cuda", dtype=torch.int8)
+        self.w = torch.randint(-127, 128, (self.e, self.K, self.N), generator=g, device="cuda", dtype=torch.int8)
+        self.ws = torch.empty((self.e, self.N), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+        self.xs = torch.empty((self.m,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+        need = self.L.load().w8a8_grouped_matmul_swiglu_quant_workspace_size(self.m, self.K, self.N, self.e)
+        self.wsb = torch.empty((need,), dtype=torch.uint8, device="cuda")
+        self.scaling = "strong"
+
+    def gpu_step(self):
+        return self.ops.grouped_matmul_swiglu_quant(self.x, self.w, self.ws, self.xs, self.gl, workspace=self.wsb)
+
+    def kernel_step(self):
+        """The tensor-core stage alone (plan + matmul with the fused dequant/SwiGLU/row-max epilogue)."""
+        lib = self.L.load()
+        t = self.torch
+        if not hasattr(self, "_y"):
+            self._y = t.empty((self.m, self.N // 2), dtype=t.int8, device="cuda")
+            self._ys = t.empty((self.m,), dtype=t.float32, device="cuda")
+            self._gl = t.tensor(self.gl, dtype=t.int64)
+        rc = lib.w8a8_grouped_matmul_swiglu_quant(self.x.data_ptr(), self.w.data_ptr(), self.ws.data_ptr(),
+                                                  self.xs.data_ptr(), self._y.data_ptr(), self._ys.data_ptr(), self.m,
+                                                  self.K, self.N, self.e, self._gl.data_ptr(), 0, self.L.W_KN,
+                                                  self.L.F_STAGE_MATMUL, self.wsb.data_ptr(), self.wsb.numel(),
+                                                  t.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
+    kernels_per_step = 4  # plan, row-max clear (memset), matmul, requant
+
+    def ops_per_step(self):
+        return 2.0 * self.m * self.K * self.N
+
+    def units_per_step(self):
+        return self.ops_per_step() / 1e12
+
+    def roofline_units(self):
+        return self.ops_per_step() / 1e12
+
+    def host_inputs(self):
+        return [self.x.cpu().pin_memory(), self.xs.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        xs = host[1].to("cuda", non_blocking=True)
+        y, ysc = self.ops.grouped_matmul_swiglu_quant(x, self.w, self.ws, xs, self.gl, workspace=self.wsb)
+        outs = [y.to("cpu", non_blocking=True), ysc.to("cpu", non_blocking=True)]
+        return (host[0].numel() + host[1].numel() * 4 + 8 * self.e, sum(o.numel() * o.element_size() for o in outs))
+
+    def cpu_sample(self, O):
+        e, rows_per = 4, 64
+        rng = np.random.default_rng(0)
+        m = e * rows_per
+        x = rng.integers(-127, 128, (m, self.K)).astype(np.int8)
+        w = rng.integers(-127, 128, (e, self.K, self.N)).astype(np.int8)
+        ws = rng.uniform(1e-3, 1e-2, (e, self.N)).astype(np.float32)
+        xs = rng.uniform(1e-3, 5e-2, m).astype(np.float32)
+        gl = [rows_per * (i + 1) for i in range(e)]
+        units = 2.0 * m * self.K * self.N / 1e12
+        return (lambda: O.grouped_matmul_swiglu_quant(x, w, ws, xs, gl)), units, \
+            f"{m} rows over {e} experts of the {self.M}-row, {self.E}-expert configuration"
+
+
+class QmmWorkload(Workload):
+    """BASELINE configs[2], M = 8192: dense W8A8 matmul K=7168 N=18432, bf16 output."""
+    name, metric, unit, dtype, bound = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "s8", "tensor"
+    M, K, N = 8192, 7168, 18432
+    kernels_per_step = 1
+
+    def config(self, world):
+        return {"workload": f"configs[2]: quant_matmul M={self.M} K={self.K} N={self.N // world} (N column-sharded)",
+                "l2": "weights (132 MB) + output (302 MB) larger than L2",
+                "parallelism": f"tp{world} over N" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops = torch, pkg.ops
+        self.n = self.N // world
+        g = torch.Generator(device="cuda").manual_seed(200 + rank)
+        self.x = torch.randint(-127, 128, (self.M, self.K), generator=g, device="cuda", dtype=torch.int8)
+        self.w = torch.randint(-127, 128, (self.K, self.n), generator=g, device="cuda", dtype=torch.int8)
+        self.sc = torch.empty((self.n,), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+        self.pt = torch.empty((self.M,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+        self.scaling = "strong"
+
+    def gpu_step(self):
+        return self.ops.quant_matmul(self.x, self.w, self.sc, pertoken_scale=self.pt, output_dtype="bfloat16")
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def units_per_step(self):
+        return 2.0 * self.M * self.K * self.n / 1e12
+
+    def roofline_units(self):
+        return self.units_per_step()
+
+    def host_inputs(self):
+        return [self.x.cpu().pin_memory(), self.pt.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        pt = host[1].to("cuda", non_blocking=True)
+        out = self.ops.quant_matmul(x, self.w, self.sc, pertoken_scale=pt, output_dtype="bfloat16")
+        o = out.to("cpu", non_blocking=True)
+        return (host[0].numel() + host[1].numel() * 4, o.numel() * 2)
+
+    def cpu_sample(self, O):
+        m, n = 64, 4608
+        rng = np.random.default_rng(0)
+        x = rng.integers(-127, 128, (m, self.K)).astype(np.int8)
+        w = rng.integers(-127, 128, (self.K, n)).astype(np.int8)
+        sc = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+        pt = rng.uniform(1e-3, 5e-2, m).astype(np.float32)
+        fl = O.QM_SCALE_PERCHAN | O.QM_HAS_PT
+        return (lambda: O.quant_matmul(x, w, sc, pertoken=pt, flags=fl, out_dtype=O.DT_BF16)), \
+            2.0 * m * self.K * n / 1e12, f"M={m}, N={n} slice of the M=8192, N=18432 problem"
+
+
+WORKLOADS = {"gmsq": GmsqWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload}
+
+
+# --------------------------------------------------------------------------
+# CPU legs
+# --------------------------------------------------------------------------
+def time_cpu(fn, units, min_seconds=3.0, max_reps=20):
+    fn()  # warm caches, build thread pool
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or reps >= max_reps:
+            break
+    return units * reps / dt, dt / reps
+
+
+def run_reference(args, wl):
+    """The reference arm: the CPU oracle (the reference's CPU implementation of the path on this box) on all host
+    threads, each step a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+
+    O.load()
+    fn, units, sample = wl.cpu_sample(O)
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = time.perf_counter() - t0
+    value = units * args.steps / dt
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
+        "config": wl.config(1),
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference's kernels need the Ascend toolchain; this arm times the CPU oracle that restates them",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gmsq")
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--small", action="store_true", help="reduced grouped workload (for profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    wl = WORKLOADS[args.workload](small=True) if (args.workload == "gmsq" and args.small) else WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    wl.gpu_setup(torch, rank, world)
+    for _ in range(args.warmup):
+        wl.gpu_step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-resident, whole step ----
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        wl.gpu_step()
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+
+    # ---- dominant kernel alone (same stream, CUDA events) ----
+    for _ in range(2):
+        wl.kernel_step()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(args.steps):
+        wl.kernel_step()
+    k1.record()
+    torch.cuda.synchronize()
+    ms_kernel = k0.elapsed_time(k1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end with host buffers ----
+    e2e_ms, h2d, d2h = None, 0, 0
+    if not args.no_e2e:
+        host = wl.host_inputs()
+        for _ in range(2):
+            wl.e2e_step(host)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_steps = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(e2e_steps):
+            h2d, d2h = wl.e2e_step(host)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- max over ranks ----
+    times = torch.tensor([ms_total, e2e_ms if e2e_ms is not None else 0.0], dtype=torch.float64, device="cuda")
+    units = torch.tensor([wl.units_per_step()], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(units, op=dist.ReduceOp.SUM)
+    ms_total = float(times[0])
+    e2e_ms = float(times[1]) if e2e_ms is not None else None
+    total_units = float(units[0])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms_total / args.steps
+        value = total_units / (ms_per_step * 1e-3)
+        if wl.bound == "hbm":
+            peak, punit = peaks["hbm_gbs"], "GB/s"
+            peak_note = f"{peaks['source']} STREAM-style copy"
+        else:
+            peak, punit = peaks["bf16_tflops"] * INT8_PER_BF16, "TOPS"
+            peak_note = f"2 x {peaks['source']} cuBLAS bf16 burst (int8 MMA rate is twice bf16's); nominal dense int8 is 4500"
+        achieved = wl.roofline_units() / (ms_kernel * 1e-3)
+        line = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
+            "config": wl.config(world), "clocks": clocks,
+            "gpu_launches": wl.kernels_per_step * args.steps,
+            "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": punit,
+                         "frac": achieved / peak, "traffic": None, "kernel_ms": ms_kernel, "peak_source": peak_note},
+        }
+        if e2e_ms is not None:
+            line["e2e"] = {"value": total_units / (e2e_ms * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": int(h2d),
+                           "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms}
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle as O
+
+            O.load()
+            fn, cpu_units, sample = wl.cpu_sample(O)
+            v, _ = time_cpu(fn, cpu_units)
+            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

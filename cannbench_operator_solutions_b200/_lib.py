@@ -15,6 +15,7 @@ OK = 0
 ERR_INVALID, ERR_ALIGN, ERR_GROUP_LIST, ERR_WORKSPACE, ERR_CUDA, ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
 DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
 F_ROUND_DIRECT = 1
+F_STAGE_MATMUL, F_STAGE_REQUANT = 2, 4
 W_KN, W_NK = 0, 1
 
 QM_SCALE_PERCHAN = 1 << 0
@@ -36,6 +37,7 @@ SIGNATURES = {
     "w8a8_add_rms_norm_dynamic_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _i32, _vp]),
     "w8a8_quant_matmul": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i64,
                                  _vp]),
+    "w8a8_matmul_i8_i32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_grouped_matmul_swiglu_quant_workspace_size": (_sz, [_i64, _i64, _i64, _i64]),
     "w8a8_grouped_matmul_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32,
                                                 _i32, _i32, _vp, _sz, _vp]),

@@ -1,0 +1,648 @@
+// Host side of the tensor-core operators: argument validation (mirroring the
+// reference plugins' checks), TMA tensor maps, the device-side group planner,
+// kernel selection, and the C-ABI entry points for quant_matmul,
+// grouped_matmul_swiglu_quant and grouped_matmul.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "gemm_kernel.cuh"
+
+namespace w8a8 {
+
+// ---------------------------------------------------------------------------
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the
+// library does not link libcuda directly).
+// ---------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+static CUtensorMapDataType tm_dtype(int kind)
+{
+    switch (kind) {
+    case KIND_F16:
+        return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    case KIND_BF16:
+        return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    default:
+        return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    }
+}
+
+// A: [rows, K] row-major.  Box = 128 bytes of K x 128 rows.
+static bool make_map_a(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int kind)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    const int elem = (kind == KIND_I8) ? 1 : 2;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * elem};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), 128};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, tm_dtype(kind), 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// B: [G, K, N] (mn_major) or [G, N, K].  Box = 128 bytes of the contiguous
+// dimension x 128 bytes-worth of K rows (mn_major: BLOCK_K rows) or 128 N rows.
+static bool make_map_b(CUtensorMap* m, const void* base, int64_t G, int64_t N, int64_t K, int kind, bool mn_major)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    const int elem = (kind == KIND_I8) ? 1 : 2;
+    const int64_t inner = mn_major ? N : K;
+    const int64_t outer = mn_major ? K : N;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(G)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(inner) * elem, static_cast<cuuint64_t>(inner) * outer * elem};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / elem), static_cast<cuuint32_t>(mn_major ? 128 / elem : 128), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, tm_dtype(kind), 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BLOCK_N>
+constexpr size_t gemm_smem_bytes()
+{
+    return static_cast<size_t>(GEMM_STAGES) * (GEMM_A_BYTES + BLOCK_N * GEMM_KBYTES) + 1024 /*alignment slack*/ +
+           256 /*barriers, tmem slot, abort flag*/;
+}
+
+template <int BLOCK_N, int KIND, int EPI, bool B_MN>
+static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int64_t max_tiles,
+                               cudaStream_t st)
+{
+    auto kern = gemm_tc_kernel<BLOCK_N, KIND, EPI, B_MN>;
+    constexpr size_t smem = gemm_smem_bytes<BLOCK_N>();
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    // the attribute is per device; set it on every call (cheap) so that multi-GPU processes are covered
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    (void)once;
+    if (attr_err != cudaSuccess) {
+        return attr_err;
+    }
+    int64_t grid = sm_count();
+    if (max_tiles < grid) {
+        grid = max_tiles;
+    }
+    if (grid < 1) {
+        grid = 1;
+    }
+    kern<<<static_cast<unsigned>(grid), GEMM_THREADS, smem, st>>>(ta, tb, p);
+    return cudaGetLastError();
+}
+
+template <int KIND, int EPI>
+static cudaError_t dispatch_gemm(int block_n, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
+                                 const GemmParams& p, int64_t max_tiles, cudaStream_t st)
+{
+    if constexpr (EPI == EPI_GMSQ) {
+        return b_mn ? launch_gemm<256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                    : launch_gemm<256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+    } else {
+        if (block_n == 128) {
+            return b_mn ? launch_gemm<128, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                        : launch_gemm<128, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+        }
+        return b_mn ? launch_gemm<256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                    : launch_gemm<256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Group planner: cumulative group list -> table of 128-row tiles.
+// The list arrives by value (host lists, validated by the caller) or from
+// device memory (validated here; an invalid list yields zero tiles and
+// error = 1).
+// ---------------------------------------------------------------------------
+constexpr int PLAN_MAX_BY_VALUE = 1024;
+struct GroupEndsByValue {
+    int32_t ends[PLAN_MAX_BY_VALUE];
+};
+
+__global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restrict__ dev_list,
+                                                          const GroupEndsByValue by_value, int use_by_value,
+                                                          int64_t E, int64_t M, GroupedHeader* header,
+                                                          TileEntry* tiles, int64_t max_tiles)
+{
+    extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
+    __shared__ int s_bad;
+    auto end_of = [&](int64_t g) -> int64_t {
+        return use_by_value ? static_cast<int64_t>(by_value.ends[g]) : dev_list[g];
+    };
+    if (threadIdx.x == 0) {
+        int bad = 0;
+        int64_t prev = 0;
+        int64_t run = 0;
+        for (int64_t g = 0; g < E; ++g) {
+            const int64_t e = end_of(g);
+            if (e < prev || e > M) {
+                bad = 1;
+                break;
+            }
+            s_first[g] = static_cast<int32_t>(run);
+            run += (e - prev + GEMM_BLOCK_M - 1) / GEMM_BLOCK_M;
+            prev = e;
+        }
+        if (!bad && prev != M) {
+            bad = 1;
+        }
+        if (!bad && run > max_tiles) {
+            bad = 1;
+        }
+        s_first[E] = static_cast<int32_t>(run);
+        s_bad = bad;
+        header->num_m_tiles = bad ? 0 : static_cast<int32_t>(run);
+        header->error = bad;
+    }
+    __syncthreads();
+    if (s_bad) {
+        return;
+    }
+    for (int64_t g = 0; g < E; ++g) {
+        const int64_t start = (g == 0) ? 0 : end_of(g - 1);
+        const int64_t rows = end_of(g) - start;
+        const int32_t first = s_first[g];
+        const int32_t cnt = s_first[g + 1] - first;
+        for (int32_t t = threadIdx.x; t < cnt; t += blockDim.x) {
+            TileEntry te;
+            te.group = static_cast<int32_t>(g);
+            te.m_start = static_cast<int32_t>(start + static_cast<int64_t>(t) * GEMM_BLOCK_M);
+            const int64_t left = rows - static_cast<int64_t>(t) * GEMM_BLOCK_M;
+            te.m_rows = static_cast<int32_t>(left < GEMM_BLOCK_M ? left : GEMM_BLOCK_M);
+            te.pad = 0;
+            tiles[first + t] = te;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Requantisation of the SwiGLU activations (second, bandwidth-bound half of
+// grouped_matmul_swiglu_quant): amax clamp at FLT_MIN, y_scale = amax*(1/127),
+// inv = 127/amax, clamp to [-128,127], two-step narrowing
+// (gmsq_vec_kernel.cpp:233-257).  One warp per row.
+// ---------------------------------------------------------------------------
+template <bool DIRECT>
+__global__ void __launch_bounds__(256) gmsq_requant_kernel(const float* __restrict__ act,
+                                                           const uint32_t* __restrict__ amax_bits,
+                                                           int8_t* __restrict__ y, float* __restrict__ y_scale,
+                                                           int64_t M, int64_t H, const GroupedHeader* header)
+{
+    if (header->error != 0) {
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    const int64_t n4 = H / 4;
+    for (int64_t row = warp_global; row < M; row += warps_total) {
+        float amax = __uint_as_float(amax_bits[row]);
+        if (!(amax > 1.1754944e-38f)) {
+            amax = 1.1754944e-38f;
+        }
+        if (lane == 0) {
+            y_scale[row] = __fmul_rn(amax, INV127);
+        }
+        const float inv = __fdiv_rn(127.0f, amax);
+        const float4* src = reinterpret_cast<const float4*>(act + row * H);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(y + row * H);
+        for (int64_t c = lane; c < n4; c += 32) {
+            const float4 a = __ldcs(src + c);
+            float v[4] = {__fmul_rn(a.x, inv), __fmul_rn(a.y, inv), __fmul_rn(a.z, inv), __fmul_rn(a.w, inv)};
+            bool any_nan = false;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                any_nan |= (v[j] != v[j]);
+                v[j] = fminf(fmaxf(v[j], -128.0f), 127.0f);
+            }
+            uint32_t packed = narrow4_fast<DIRECT>(v[0], v[1], v[2], v[3]);
+            if (any_nan) {
+                // a NaN activation narrows to 0 (fmaxf/fminf above turned it into a bound)
+                const float w[4] = {__fmul_rn(a.x, inv), __fmul_rn(a.y, inv), __fmul_rn(a.z, inv),
+                                    __fmul_rn(a.w, inv)};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (w[j] != w[j]) {
+                        packed &= ~(0xffu << (8 * j));
+                    }
+                }
+            }
+            __stcs(dst + c, packed);
+        }
+    }
+}
+
+static inline size_t align_up_sz(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct GroupedWorkspace {
+    GroupedHeader* header;
+    TileEntry* tiles;
+    int64_t max_tiles;
+    uint32_t* amax;
+    float* act;
+    size_t total;
+};
+
+static GroupedWorkspace carve_workspace(void* ws, int64_t M, int64_t E, int64_t act_cols)
+{
+    GroupedWorkspace g;
+    uint8_t* p = static_cast<uint8_t*>(ws);
+    size_t off = 0;
+    g.header = reinterpret_cast<GroupedHeader*>(p + off);
+    off += align_up_sz(sizeof(GroupedHeader), 256);
+    g.max_tiles = M / GEMM_BLOCK_M + E + 1;
+    g.tiles = reinterpret_cast<TileEntry*>(p + off);
+    off += align_up_sz(static_cast<size_t>(g.max_tiles) * sizeof(TileEntry), 256);
+    g.amax = reinterpret_cast<uint32_t*>(p + off);
+    off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * sizeof(uint32_t), 256) : 0;
+    g.act = reinterpret_cast<float*>(p + off);
+    off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * act_cols * sizeof(float), 256) : 0;
+    g.total = off;
+    return g;
+}
+
+// returns W8A8_OK or an error; launches the planner on `st`
+static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E, int64_t M,
+                       const GroupedWorkspace& g, cudaStream_t st)
+{
+    GroupEndsByValue bv;
+    int use_bv = 0;
+    const int64_t* dev_list = group_list;
+    if (!list_on_device) {
+        if (E > PLAN_MAX_BY_VALUE) {
+            return W8A8_ERR_UNSUPPORTED;
+        }
+        int64_t prev = 0;
+        for (int64_t i = 0; i < E; ++i) {
+            const int64_t v = group_list[i];
+            if (v < prev || v > M) {
+                return W8A8_ERR_GROUP_LIST;
+            }
+            bv.ends[i] = static_cast<int32_t>(v);
+            prev = v;
+        }
+        if (prev != M) {
+            return W8A8_ERR_GROUP_LIST;
+        }
+        for (int64_t i = E; i < PLAN_MAX_BY_VALUE; ++i) {
+            bv.ends[i] = 0;
+        }
+        use_bv = 1;
+        dev_list = nullptr;
+    }
+    const size_t smem = static_cast<size_t>(E + 1) * sizeof(int32_t);
+    if (smem > 48 * 1024) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, g.header, g.tiles, g.max_tiles);
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+}  // namespace w8a8
+
+using namespace w8a8;
+
+// ===========================================================================
+// quant_matmul
+// ===========================================================================
+static int quant_matmul_impl(const int8_t* x1, const int8_t* x2, const void* scale, const float* offset,
+                             const float* pertoken, const void* bias, void* out, int64_t batch, int64_t M, int64_t N,
+                             int64_t K, int64_t flags, int out_dtype, int x2_layout, int64_t bias_batch_stride,
+                             bool raw_i32, void* stream)
+{
+    if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
+        return W8A8_ERR_INVALID;  // quant_matmul_plugin.cpp:100 "requires non-empty shapes"
+    }
+    if (x1 == nullptr || x2 == nullptr || out == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    if (x2_layout != W8A8_W_KN && x2_layout != W8A8_W_NK) {
+        return W8A8_ERR_INVALID;
+    }
+    if (!raw_i32) {
+        if (scale == nullptr || (out_dtype != W8A8_DT_F16 && out_dtype != W8A8_DT_BF16)) {
+            return W8A8_ERR_INVALID;
+        }
+        const int64_t bias_kind = (flags & W8A8_QM_BIAS_MASK) >> W8A8_QM_BIAS_SHIFT;
+        if (bias_kind > W8A8_QM_BIAS_F32 || (bias_kind != W8A8_QM_BIAS_NONE && bias == nullptr)) {
+            return W8A8_ERR_INVALID;
+        }
+        if (((flags & W8A8_QM_HAS_OFFSET) && offset == nullptr) || ((flags & W8A8_QM_HAS_PT) && pertoken == nullptr)) {
+            return W8A8_ERR_INVALID;
+        }
+    }
+    if ((K % 16) != 0 || (N % 16) != 0) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    if (!is_aligned(x1, 16) || !is_aligned(x2, 16) || !is_aligned(out, 16)) {
+        return W8A8_ERR_ALIGN;
+    }
+    if (batch * M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool b_mn = (x2_layout == W8A8_W_KN);
+    CUtensorMap ta, tb;
+    if (!make_map_a(&ta, x1, batch * M, K, KIND_I8) || !make_map_b(&tb, x2, batch, N, K, KIND_I8, b_mn)) {
+        return W8A8_ERR_CUDA;
+    }
+    GemmParams p{};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.num_k_blocks = static_cast<int32_t>((K + GEMM_KBYTES - 1) / GEMM_KBYTES);
+    p.m_tiles_per_batch = static_cast<int32_t>((M + GEMM_BLOCK_M - 1) / GEMM_BLOCK_M);
+    p.batch = static_cast<int32_t>(batch);
+    p.grouped = 0;
+    p.scale = scale;
+    p.offset = offset;
+    p.row_scale = pertoken;
+    p.bias = bias;
+    p.out = out;
+    p.flags = flags;
+    p.out_dtype = out_dtype;
+    p.bias_batch_stride = bias_batch_stride;
+    // narrow tiles when wide ones would leave most SMs idle
+    const int64_t m_tiles = batch * p.m_tiles_per_batch;
+    const int64_t tiles256 = m_tiles * ((N + 255) / 256);
+    const int block_n = (tiles256 < sm_count()) ? 128 : 256;
+    p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
+    const int64_t total = m_tiles * p.n_tiles;
+    cudaError_t e;
+    if (raw_i32) {
+        e = dispatch_gemm<KIND_I8, EPI_RAW>(block_n, b_mn, ta, tb, p, total, st);
+    } else {
+        e = dispatch_gemm<KIND_I8, EPI_QMM>(block_n, b_mn, ta, tb, p, total, st);
+    }
+    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_quant_matmul(const int8_t* x1, const int8_t* x2, const void* scale, const float* offset,
+                                 const float* pertoken, const void* bias, void* out, int64_t batch, int64_t M,
+                                 int64_t N, int64_t K, int64_t flags, int out_dtype, int x2_layout,
+                                 int64_t bias_batch_stride, void* stream)
+{
+    return quant_matmul_impl(x1, x2, scale, offset, pertoken, bias, out, batch, M, N, K, flags, out_dtype, x2_layout,
+                             bias_batch_stride, false, stream);
+}
+
+extern "C" int w8a8_matmul_i8_i32(const int8_t* x1, const int8_t* x2, int32_t* c, int64_t batch, int64_t M, int64_t N,
+                                  int64_t K, int x2_layout, void* stream)
+{
+    return quant_matmul_impl(x1, x2, nullptr, nullptr, nullptr, nullptr, c, batch, M, N, K, 0, 0, x2_layout, 0, true,
+                             stream);
+}
+
+// ===========================================================================
+// grouped_matmul_swiglu_quant
+// ===========================================================================
+extern "C" size_t w8a8_grouped_matmul_swiglu_quant_workspace_size(int64_t M, int64_t K, int64_t N, int64_t E)
+{
+    (void)K;
+    if (M < 0 || N <= 0 || E <= 0) {
+        return 0;
+    }
+    return carve_workspace(nullptr, M, E, N / 2).total;
+}
+
+extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w, const float* w_scale,
+                                                const float* x_scale, int8_t* y, float* y_scale, int64_t M, int64_t K,
+                                                int64_t N, int64_t E, const int64_t* group_list, int list_on_device,
+                                                int w_layout, int flags, void* workspace, size_t workspace_bytes,
+                                                void* stream)
+{
+    if (M < 0 || K <= 0 || N <= 0 || E <= 0 || (N & 1) != 0) {
+        return W8A8_ERR_INVALID;  // gmsq_plugin.cpp:52 "N must be even"
+    }
+    if ((flags & ~(W8A8_F_ROUND_DIRECT | W8A8_F_STAGE_MATMUL | W8A8_F_STAGE_REQUANT)) != 0 ||
+        (w_layout != W8A8_W_KN && w_layout != W8A8_W_NK)) {
+        return W8A8_ERR_INVALID;
+    }
+    const int stages = flags & (W8A8_F_STAGE_MATMUL | W8A8_F_STAGE_REQUANT);
+    const bool run_matmul = (stages == 0) || (stages & W8A8_F_STAGE_MATMUL);
+    const bool run_requant = (stages == 0) || (stages & W8A8_F_STAGE_REQUANT);
+    if (M == 0) {
+        return W8A8_OK;  // gmsq_plugin.cpp:93-95
+    }
+    if (x == nullptr || w == nullptr || w_scale == nullptr || x_scale == nullptr || y == nullptr ||
+        y_scale == nullptr || group_list == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    if ((K % 16) != 0 || (N % 32) != 0) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    if (!is_aligned(x, 16) || !is_aligned(w, 16) || !is_aligned(w_scale, 16) || !is_aligned(y, 4)) {
+        return W8A8_ERR_ALIGN;
+    }
+    if (M >= (int64_t(1) << 31) - 256 || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    const int64_t H = N / 2;
+    const size_t need = w8a8_grouped_matmul_swiglu_quant_workspace_size(M, K, N, E);
+    if (workspace == nullptr || workspace_bytes < need) {
+        return W8A8_ERR_WORKSPACE;
+    }
+    if (!is_aligned(workspace, 256)) {
+        return W8A8_ERR_ALIGN;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const GroupedWorkspace g = carve_workspace(workspace, M, E, H);
+    if (run_matmul) {
+        const int rc = plan_groups(group_list, list_on_device, E, M, g, st);
+        if (rc != W8A8_OK) {
+            return rc;
+        }
+        if (cudaMemsetAsync(g.amax, 0, static_cast<size_t>(M) * sizeof(uint32_t), st) != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
+        const bool b_mn = (w_layout == W8A8_W_KN);
+        CUtensorMap ta, tb;
+        if (!make_map_a(&ta, x, M, K, KIND_I8) || !make_map_b(&tb, w, E, N, K, KIND_I8, b_mn)) {
+            return W8A8_ERR_CUDA;
+        }
+        GemmParams p{};
+        p.M = M;
+        p.N = N;
+        p.K = K;
+        p.num_k_blocks = static_cast<int32_t>((K + GEMM_KBYTES - 1) / GEMM_KBYTES);
+        p.n_tiles = static_cast<int32_t>((H + 127) / 128);
+        p.grouped = 1;
+        p.tiles = g.tiles;
+        p.header = g.header;
+        p.error = &g.header->error;
+        p.scale = w_scale;
+        p.row_scale = x_scale;
+        p.act = g.act;
+        p.amax = g.amax;
+        const int64_t max_total = g.max_tiles * p.n_tiles;
+        const cudaError_t e = dispatch_gemm<KIND_I8, EPI_GMSQ>(256, b_mn, ta, tb, p, max_total, st);
+        if (e != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
+    }
+    if (!run_requant) {
+        return W8A8_OK;
+    }
+    const int64_t warps_needed = M;
+    int64_t blocks = (warps_needed + 7) / 8;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (blocks > cap) {
+        blocks = cap;
+    }
+    if (flags & W8A8_F_ROUND_DIRECT) {
+        gmsq_requant_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(g.act, g.amax, y, y_scale, M, H,
+                                                                                g.header);
+    } else {
+        gmsq_requant_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(g.act, g.amax, y, y_scale, M, H,
+                                                                                 g.header);
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+// ===========================================================================
+// grouped_matmul
+// ===========================================================================
+extern "C" size_t w8a8_grouped_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t E)
+{
+    (void)N;
+    (void)K;
+    if (M < 0 || E <= 0) {
+        return 0;
+    }
+    return carve_workspace(nullptr, M, E, 0).total;
+}
+
+extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y, const float* x_scale,
+                                   const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
+                                   const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
+                                   int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (M < 0 || K <= 0 || N <= 0 || E <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (w_layout != W8A8_W_KN && w_layout != W8A8_W_NK) {
+        return W8A8_ERR_INVALID;
+    }
+    int kind;
+    if (dtype == W8A8_DT_I8) {
+        kind = KIND_I8;
+        if (x_scale == nullptr || w_scale == nullptr) {
+            return W8A8_ERR_INVALID;
+        }
+        if (out_dtype != W8A8_DT_F16 && out_dtype != W8A8_DT_BF16) {
+            return W8A8_ERR_INVALID;
+        }
+    } else if (dtype == W8A8_DT_F16 || dtype == W8A8_DT_BF16) {
+        kind = (dtype == W8A8_DT_F16) ? KIND_F16 : KIND_BF16;
+        if (out_dtype != dtype) {
+            return W8A8_ERR_INVALID;  // the reference's output takes x's dtype
+        }
+    } else if (dtype == W8A8_DT_F32) {
+        return W8A8_ERR_UNSUPPORTED;  // fp32 operands have no exact tensor-core path
+    } else {
+        return W8A8_ERR_INVALID;
+    }
+    if (bias != nullptr && bias_dtype != W8A8_DT_F16 && bias_dtype != W8A8_DT_BF16 && bias_dtype != W8A8_DT_F32) {
+        return W8A8_ERR_INVALID;
+    }
+    if (M == 0) {
+        return W8A8_OK;
+    }
+    if (x == nullptr || w == nullptr || y == nullptr || group_list == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    const int elem = (kind == KIND_I8) ? 1 : 2;
+    if ((K * elem) % 16 != 0 || (N * elem) % 16 != 0 || (N % 8) != 0) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    if (!is_aligned(x, 16) || !is_aligned(w, 16) || !is_aligned(y, 16)) {
+        return W8A8_ERR_ALIGN;
+    }
+    if (M >= (int64_t(1) << 31) - 256 || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    const size_t need = w8a8_grouped_matmul_workspace_size(M, N, K, E);
+    if (workspace == nullptr || workspace_bytes < need) {
+        return W8A8_ERR_WORKSPACE;
+    }
+    if (!is_aligned(workspace, 256)) {
+        return W8A8_ERR_ALIGN;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const GroupedWorkspace g = carve_workspace(workspace, M, E, 0);
+    const int rc = plan_groups(group_list, list_on_device, E, M, g, st);
+    if (rc != W8A8_OK) {
+        return rc;
+    }
+    const bool b_mn = (w_layout == W8A8_W_KN);
+    CUtensorMap ta, tb;
+    if (!make_map_a(&ta, x, M, K, kind) || !make_map_b(&tb, w, E, N, K, kind, b_mn)) {
+        return W8A8_ERR_CUDA;
+    }
+    GemmParams p{};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    const int block_k = GEMM_KBYTES / elem;
+    p.num_k_blocks = static_cast<int32_t>((K + block_k - 1) / block_k);
+    p.grouped = 1;
+    p.tiles = g.tiles;
+    p.header = g.header;
+    p.error = &g.header->error;
+    p.scale = w_scale;
+    p.row_scale = x_scale;
+    p.bias = bias;
+    p.out = y;
+    p.flags = (bias != nullptr ? 4 : 0) | (bias_dtype & 3);
+    p.out_dtype = out_dtype;
+    const int block_n = 256;
+    p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
+    const int64_t max_total = g.max_tiles * p.n_tiles;
+    cudaError_t e;
+    if (kind == KIND_I8) {
+        e = dispatch_gemm<KIND_I8, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+    } else if (kind == KIND_F16) {
+        e = dispatch_gemm<KIND_F16, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+    } else {
+        e = dispatch_gemm<KIND_BF16, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+    }
+    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_workspace_error(const void* workspace, void* stream)
+{
+    if (workspace == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    GroupedHeader h;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&h, workspace, sizeof(int32_t) * 2, cudaMemcpyDeviceToHost, st) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    if (cudaStreamSynchronize(st) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    return h.error;
+}

@@ -210,12 +210,13 @@ def grouped_matmul_swiglu_quant(x: torch.Tensor, weight: torch.Tensor, weight_sc
     _check(weight.dtype == torch.int8, "grouped_matmul_swiglu_quant: weight must be int8")
     _check(weight_scale.dtype == torch.float32, "grouped_matmul_swiglu_quant: weight_scale must be float32")
     _check(x_scale.dtype == torch.float32, "grouped_matmul_swiglu_quant: x_scale must be float32")
+    _check((weight.size(1) if transpose_weight else weight.size(2)) % 2 == 0,
+           "grouped_matmul_swiglu_quant: N must be even")
     _need_cuda(x, weight, weight_scale, x_scale)
     xc, wc, wsc, xsc = x.contiguous(), weight.contiguous(), weight_scale.contiguous(), x_scale.contiguous()
     m, k = xc.shape
     e = wc.size(0)
     n = wc.size(1) if transpose_weight else wc.size(2)
-    _check(n % 2 == 0, "grouped_matmul_swiglu_quant: N must be even")
     y = torch.empty((m, n // 2), dtype=torch.int8, device=xc.device)
     y_scale = torch.empty((m,), dtype=torch.float32, device=xc.device)
     if m == 0 or n == 0 or e == 0:

@@ -51,6 +51,13 @@ extern "C" {
 #define W8A8_F_ROUND_DIRECT 1 /* fp32 -> int8 in one rounding instead of the
                                  reference's fp32 -> fp16 -> int8 */
 
+/* grouped_matmul_swiglu_quant only: run one of its two stages, which the
+ * reference exposes as two launchers (launch_gmsq_cube, launch_gmsq_vec).
+ * Neither bit set = both stages.  The workspace carries the activations and
+ * row maxima from the first stage to the second. */
+#define W8A8_F_STAGE_MATMUL 2  /* plan + tensor-core matmul + fused dequant/SwiGLU/row-max */
+#define W8A8_F_STAGE_REQUANT 4 /* per-row requantisation of the stored activations        */
+
 /* weight layout of the matmuls */
 #define W8A8_W_KN 0 /* [.., K, N], N contiguous: the reference's layout       */
 #define W8A8_W_NK 1 /* [.., N, K], K contiguous: transpose_weight=True layout */
@@ -113,6 +120,16 @@ int w8a8_quant_matmul(const int8_t* x1, const int8_t* x2, const void* scale, con
                       const float* pertoken, const void* bias, void* out, int64_t batch, int64_t M,
                       int64_t N, int64_t K, int64_t flags, int out_dtype, int x2_layout,
                       int64_t bias_batch_stride, void* stream);
+
+/*
+ * The bare tensor-core stage: c[b] = x1[b] @ x2[b] as exact int32 (no
+ * epilogue).  Counterpart of qm_launch_cube_i32
+ * (operators/quantmatmul/csrc/ops/quant_matmul/op_kernel/quant_matmul_launch.h:88-90)
+ * and launch_gmsq_cube; the fused operators never materialise this matrix,
+ * the entry point exists for callers that want the raw accumulators.
+ */
+int w8a8_matmul_i8_i32(const int8_t* x1, const int8_t* x2, int32_t* c, int64_t batch, int64_t M, int64_t N,
+                       int64_t K, int x2_layout, void* stream);
 
 /*
  * GroupedMatmulSwigluQuant: per expert g (rows [cumsum[g-1], cumsum[g])):

@@ -1,0 +1,58 @@
+"""The torch plugin (torch.ops.cann_bench.*, C++ host code over the C-ABI) gives the
+same results as the ctypes operator functions."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cb(ops):
+    import cannbench_operator_solutions_b200 as pkg
+
+    pkg.load_torch_plugin()
+    return torch.ops.cann_bench
+
+
+def test_plugin_matches_ctypes_operators(cb, ops):
+    rng = np.random.default_rng(21)
+    x1 = torch.from_numpy(rng.standard_normal((130, 512)).astype(np.float32)).to(torch.bfloat16).cuda()
+    x2 = torch.from_numpy(rng.standard_normal((130, 512)).astype(np.float32)).to(torch.bfloat16).cuda()
+    gamma = torch.ones(512, dtype=torch.bfloat16, device="cuda")
+    for a, b in zip(cb.dynamic_quant(x1), ops.dynamic_quant(x1)):
+        assert torch.equal(a, b)
+    q = cb.add_rms_norm_dynamic_quant(x1, x2, gamma, 1e-6)
+    for a, b in zip(q, ops.add_rms_norm_dynamic_quant(x1, x2, gamma, 1e-6)):
+        assert torch.equal(a, b)
+    w = torch.from_numpy(rng.integers(-127, 128, (512, 256)).astype(np.int8)).cuda()
+    sc = torch.from_numpy(rng.uniform(1e-3, 1e-2, 256).astype(np.float32)).cuda()
+    a = cb.quant_matmul(q[0], w, sc, pertoken_scale=q[2], output_dtype="bfloat16")
+    b = ops.quant_matmul(q[0], w, sc, pertoken_scale=q[2], output_dtype="bfloat16")
+    assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+    assert cb.quant_matmul(q[0], w, sc).dtype == torch.float16
+    we = torch.from_numpy(rng.integers(-127, 128, (3, 512, 256)).astype(np.int8)).cuda()
+    se = torch.from_numpy(rng.uniform(1e-3, 1e-2, (3, 256)).astype(np.float32)).cuda()
+    gl = [60, 60, 130]
+    h = cb.grouped_matmul_swiglu_quant(q[0], we, se, q[2], gl)
+    for a, b in zip(h, ops.grouped_matmul_swiglu_quant(q[0], we, se, q[2], gl)):
+        assert torch.equal(a, b)
+    wd = torch.from_numpy(rng.integers(-127, 128, (3, 128, 512)).astype(np.int8)).cuda()
+    sd = torch.from_numpy(rng.uniform(1e-3, 1e-2, (3, 512)).astype(np.float32)).cuda()
+    outs = cb.grouped_matmul(h[0], wd, gl, None, 0, False, h[1], sd)
+    ref = ops.grouped_matmul(h[0], wd, gl, None, 0, False, x_scale=h[1], weight_scale=sd)
+    assert len(outs) == 3 and all(torch.equal(a, b) for a, b in zip(outs, ref))
+    xb = torch.from_numpy(rng.standard_normal((130, 128)).astype(np.float32)).to(torch.bfloat16).cuda()
+    wb = torch.from_numpy(rng.standard_normal((3, 128, 64)).astype(np.float32)).to(torch.bfloat16).cuda()
+    assert torch.equal(cb.grouped_matmul(xb, wb, gl, None, 2)[0], ops.grouped_matmul(xb, wb, gl, None, 2)[0])
+
+
+def test_plugin_errors_are_torch_checks(cb):
+    x = torch.zeros((4, 64), dtype=torch.float32, device="cuda")
+    with pytest.raises(RuntimeError, match="float16 / bfloat16"):
+        cb.dynamic_quant(x)
+    with pytest.raises(RuntimeError, match="must equal M"):
+        cb.grouped_matmul(torch.zeros((8, 32), dtype=torch.bfloat16, device="cuda"),
+                          torch.zeros((2, 32, 16), dtype=torch.bfloat16, device="cuda"), [3, 7])
+    y, s = cb.dynamic_quant(torch.empty((0, 64), dtype=torch.bfloat16, device="cuda"))
+    assert y.shape == (0, 64)
