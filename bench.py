@@ -148,7 +148,7 @@ class ArdqWorkload(Workload):
 
     def gpu_setup(self, torch, rank, world):
         import cannbench_operator_solutions_b200 as pkg
-        self.torch, self.ops = torch, pkg.ops
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
         g = torch.Generator(device="cuda").manual_seed(rank)
         self.x1 = torch.randn((self.rows, self.n), generator=g, device="cuda").to(torch.bfloat16)
         self.x2 = torch.randn((self.rows, self.n), generator=g, device="cuda").to(torch.bfloat16)
@@ -156,7 +156,17 @@ class ArdqWorkload(Workload):
         self.scaling = "weak"
 
     def gpu_step(self):
-        return self.ops.add_rms_norm_dynamic_quant(self.x1, self.x2, self.gamma, 1e-6)
+        """One C-ABI call into caller-owned output buffers (allocated once)."""
+        t, L = self.torch, self.L
+        if not hasattr(self, "_y"):
+            self._y = t.empty((self.rows, self.n), dtype=t.int8, device="cuda")
+            self._xo = t.empty((self.rows, self.n), dtype=t.bfloat16, device="cuda")
+            self._sc = t.empty((self.rows,), dtype=t.float32, device="cuda")
+            self._fn = L.load().w8a8_add_rms_norm_dynamic_quant
+            self._args = (self.x1.data_ptr(), self.x2.data_ptr(), self.gamma.data_ptr(), self._y.data_ptr(),
+                          self._xo.data_ptr(), self._sc.data_ptr(), self.rows, self.n, 1e-6, L.DT_BF16, 0)
+        rc = self._fn(*self._args, t.cuda.current_stream().cuda_stream)
+        assert rc == 0, L.status_string(rc)
 
     def kernel_step(self):
         return self.gpu_step()
@@ -202,7 +212,14 @@ class DqWorkload(ArdqWorkload):
         return c
 
     def gpu_step(self):
-        return self.ops.dynamic_quant(self.x1)
+        t, L = self.torch, self.L
+        if not hasattr(self, "_y"):
+            self._y = t.empty((self.rows, self.n), dtype=t.int8, device="cuda")
+            self._sc = t.empty((self.rows,), dtype=t.float32, device="cuda")
+            self._fn = L.load().w8a8_dynamic_quant
+            self._args = (self.x1.data_ptr(), self._y.data_ptr(), self._sc.data_ptr(), self.rows, self.n, L.DT_BF16, 0)
+        rc = self._fn(*self._args, t.cuda.current_stream().cuda_stream)
+        assert rc == 0, L.status_string(rc)
 
     def bytes_per_step(self):
         return self.rows * (3 * self.n + 4)
@@ -225,13 +242,13 @@ class DqWorkload(ArdqWorkload):
 
 class GmsqWorkload(Workload):
     """BASELINE configs[3]: E=256, 131072 rows with Zipf(1.1) group sizes, K=7168, N=4096."""
-    name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "s8",
+    name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "int8",
                                         "tensor")
     E, M, K, N = 256, 131072, 7168, 4096
 
     def __init__(self, small=False):
-        if small:
-            self.E, self.M, self.K, self.N = 16, 4096, 1024, 1024
+        if small:  # a slice of the configuration small enough for a profiler capture
+            self.E, self.M = 32, 16384
 
     def config(self, world):
         return {"workload": f"configs[3]: grouped_matmul_swiglu_quant E={self.E} rows={self.M} (Zipf 1.1) "
@@ -261,11 +278,7 @@ class GmsqWorkload(Workload):
         self.wsb = torch.empty((need,), dtype=torch.uint8, device="cuda")
         self.scaling = "strong"
 
-    def gpu_step(self):
-        return self.ops.grouped_matmul_swiglu_quant(self.x, self.w, self.ws, self.xs, self.gl, workspace=self.wsb)
-
-    def kernel_step(self):
-        """The tensor-core stage alone (plan + matmul with the fused dequant/SwiGLU/row-max epilogue)."""
+    def _call(self, flags):
         lib = self.L.load()
         t = self.torch
         if not hasattr(self, "_y"):
@@ -275,9 +288,17 @@ class GmsqWorkload(Workload):
         rc = lib.w8a8_grouped_matmul_swiglu_quant(self.x.data_ptr(), self.w.data_ptr(), self.ws.data_ptr(),
                                                   self.xs.data_ptr(), self._y.data_ptr(), self._ys.data_ptr(), self.m,
                                                   self.K, self.N, self.e, self._gl.data_ptr(), 0, self.L.W_KN,
-                                                  self.L.F_STAGE_MATMUL, self.wsb.data_ptr(), self.wsb.numel(),
+                                                  flags, self.wsb.data_ptr(), self.wsb.numel(),
                                                   t.cuda.current_stream().cuda_stream)
         assert rc == 0, self.L.status_string(rc)
+
+    def gpu_step(self):
+        """The whole operator (both stages), one C-ABI call into caller-owned buffers."""
+        self._call(0)
+
+    def kernel_step(self):
+        """The tensor-core stage alone (plan + matmul with the fused dequant/SwiGLU/row-max epilogue)."""
+        self._call(self.L.F_STAGE_MATMUL)
 
     kernels_per_step = 4  # plan, row-max clear (memset), matmul, requant
 
@@ -316,7 +337,7 @@ class GmsqWorkload(Workload):
 
 class QmmWorkload(Workload):
     """BASELINE configs[2], M = 8192: dense W8A8 matmul K=7168 N=18432, bf16 output."""
-    name, metric, unit, dtype, bound = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "s8", "tensor"
+    name, metric, unit, dtype, bound = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "int8", "tensor"
     M, K, N = 8192, 7168, 18432
     kernels_per_step = 1
 
@@ -327,7 +348,7 @@ class QmmWorkload(Workload):
 
     def gpu_setup(self, torch, rank, world):
         import cannbench_operator_solutions_b200 as pkg
-        self.torch, self.ops = torch, pkg.ops
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
         self.n = self.N // world
         g = torch.Generator(device="cuda").manual_seed(200 + rank)
         self.x = torch.randint(-127, 128, (self.M, self.K), generator=g, device="cuda", dtype=torch.int8)
@@ -337,7 +358,15 @@ class QmmWorkload(Workload):
         self.scaling = "strong"
 
     def gpu_step(self):
-        return self.ops.quant_matmul(self.x, self.w, self.sc, pertoken_scale=self.pt, output_dtype="bfloat16")
+        t, L = self.torch, self.L
+        if not hasattr(self, "_out"):
+            self._out = t.empty((self.M, self.n), dtype=t.bfloat16, device="cuda")
+            self._fn = L.load().w8a8_quant_matmul
+            self._args = (self.x.data_ptr(), self.w.data_ptr(), self.sc.data_ptr(), None, self.pt.data_ptr(), None,
+                          self._out.data_ptr(), 1, self.M, self.n, self.K, L.QM_SCALE_PERCHAN | L.QM_HAS_PT,
+                          L.DT_BF16, L.W_KN, 0)
+        rc = self._fn(*self._args, t.cuda.current_stream().cuda_stream)
+        assert rc == 0, L.status_string(rc)
 
     def kernel_step(self):
         return self.gpu_step()
@@ -376,7 +405,7 @@ WORKLOADS = {"gmsq": GmsqWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm"
 # --------------------------------------------------------------------------
 # CPU legs
 # --------------------------------------------------------------------------
-def time_cpu(fn, units, min_seconds=3.0, max_reps=20):
+def time_cpu(fn, units, min_seconds=10.0, max_reps=50):
     fn()  # warm caches, build thread pool
     reps, t0 = 0, time.perf_counter()
     while True:
@@ -426,12 +455,15 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gmsq")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--small", action="store_true", help="reduced grouped workload (for profiling captures)")
+    ap.add_argument("--qmm-m", type=int, default=8192, help="rows of the dense quant_matmul workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     wl = WORKLOADS[args.workload](small=True) if (args.workload == "gmsq" and args.small) else WORKLOADS[args.workload]()
+    if args.workload == "qmm":
+        wl.M = args.qmm_m
     if args.impl == "reference":
         run_reference(args, wl)
         return
@@ -454,16 +486,25 @@ def main():
         torch.cuda.synchronize()
 
     wl.gpu_setup(torch, rank, world)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         wl.gpu_step()
     barrier()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    def hold(seconds):
+        """Keep the GPU under the same load so that nvidia-smi (100 ms period) sees the clocks of the timed
+        region, which itself may last only a few milliseconds."""
+        t_end = time.perf_counter() + seconds
+        while time.perf_counter() < t_end:
+            for _ in range(8):
+                wl.gpu_step()
+            torch.cuda.synchronize()
 
-    # ---- device-resident, whole step ----
+    # ---- device-resident, whole step (timed K steps in the middle of a sustained-load window) ----
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    hold(0.6)
     barrier()
     ev0.record()
     for _ in range(args.steps):
@@ -471,6 +512,7 @@ def main():
     ev1.record()
     barrier()
     ms_total = ev0.elapsed_time(ev1)
+    hold(0.4)
 
     # ---- dominant kernel alone (same stream, CUDA events) ----
     for _ in range(2):

@@ -48,6 +48,7 @@ SIGNATURES = {
     "w8a8_route_plan_workspace_size": (_sz, [_i64, _i64, _i64]),
     "w8a8_route_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "w8a8_scatter_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "w8a8_permute_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
 }
 

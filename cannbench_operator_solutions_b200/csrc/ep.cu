@@ -126,6 +126,38 @@ __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __rest
     }
 }
 
+// dst[d] = src[index[d]] for whole rows (and their fp32 scales): the regroup
+// step after an all-to-all (rank-major -> expert-major) and its inverse.
+template <bool VEC>
+__global__ void __launch_bounds__(256) permute_rows_kernel(const uint8_t* __restrict__ src,
+                                                           const float* __restrict__ src_scale,
+                                                           uint8_t* __restrict__ dst, float* __restrict__ dst_scale,
+                                                           const int64_t* __restrict__ index, int64_t rows,
+                                                           int64_t row_bytes)
+{
+    for (int64_t d = blockIdx.x; d < rows; d += gridDim.x) {
+        const int64_t s = index[d];
+        if (s < 0) {
+            continue;
+        }
+        if constexpr (VEC) {
+            const uint4* sp = reinterpret_cast<const uint4*>(src + s * row_bytes);
+            uint4* dp = reinterpret_cast<uint4*>(dst + d * row_bytes);
+            const int64_t n16 = row_bytes / 16;
+            for (int64_t c = threadIdx.x; c < n16; c += blockDim.x) {
+                __stcs(dp + c, __ldcs(sp + c));
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < row_bytes; c += blockDim.x) {
+                dst[d * row_bytes + c] = src[s * row_bytes + c];
+            }
+        }
+        if (threadIdx.x == 0 && src_scale != nullptr && dst_scale != nullptr) {
+            dst_scale[d] = src_scale[s];
+        }
+    }
+}
+
 // One CTA per token; each thread owns 8-element chunks of the hidden row.
 template <int DT, bool VEC>
 __global__ void __launch_bounds__(256) combine_kernel(const uint16_t* __restrict__ rows,
@@ -246,6 +278,34 @@ extern "C" int w8a8_scatter_rows(const void* src, const float* src_scale, void* 
         w8a8::scatter_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                               static_cast<uint8_t*>(dst), dst_scale, expanded_pos, T,
                                                               static_cast<int>(topk), row_bytes);
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_permute_rows(const void* src, const float* src_scale, void* dst, float* dst_scale,
+                                 const int64_t* index, int64_t rows, int64_t row_bytes, void* stream)
+{
+    if (rows < 0 || row_bytes <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (rows == 0) {
+        return W8A8_OK;
+    }
+    if (src == nullptr || dst == nullptr || index == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool vec = (row_bytes % 16 == 0) && w8a8::is_aligned(src, 16) && w8a8::is_aligned(dst, 16);
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
+    if (vec) {
+        w8a8::permute_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
+                                                             static_cast<uint8_t*>(dst), dst_scale, index, rows,
+                                                             row_bytes);
+    } else {
+        w8a8::permute_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
+                                                              static_cast<uint8_t*>(dst), dst_scale, index, rows,
+                                                              row_bytes);
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

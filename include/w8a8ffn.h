@@ -199,6 +199,13 @@ int w8a8_scatter_rows(const void* src, const float* src_scale, void* dst, float*
                       const int64_t* expanded_pos, int64_t T, int64_t topk, int64_t row_bytes,
                       void* stream);
 
+/* dst[d] = src[index[d]] for rows of row_bytes (and dst_scale[d] = src_scale[index[d]] when both scale
+ * pointers are given); a negative index leaves the row untouched.  This is the data movement of
+ * MoeReRouting (rank-major -> expert-major after an all-to-all) with the permutation supplied by the
+ * caller (operators/moererouting/csrc/ops/moe_re_routing/op_kernel/moe_re_routing_kernel.cpp:15-24). */
+int w8a8_permute_rows(const void* src, const float* src_scale, void* dst, float* dst_scale,
+                      const int64_t* index, int64_t rows, int64_t row_bytes, void* stream);
+
 /* out[i, :] = sum_k probs[i, k] * rows[pos[i*topk+k], :], fp32, ascending k,
  * rounded to dtype (F16 / BF16).  A negative position contributes nothing. */
 int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,
