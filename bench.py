@@ -352,7 +352,8 @@ class QmmWorkload(Workload):
         self.n = self.N // world
         g = torch.Generator(device="cuda").manual_seed(200 + rank)
         self.x = torch.randint(-127, 128, (self.M, self.K), generator=g, device="cuda", dtype=torch.int8)
-        self.w = torch.randint(-127, 128, (self.K, self.n), generator=g, device="cuda", dtype=torch.int8)
+        wshape = (self.n, self.K) if getattr(self, "layout_nk", False) else (self.K, self.n)
+        self.w = torch.randint(-127, 128, wshape, generator=g, device="cuda", dtype=torch.int8)
         self.sc = torch.empty((self.n,), device="cuda").uniform_(1e-3, 1e-2, generator=g)
         self.pt = torch.empty((self.M,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
         self.scaling = "strong"
@@ -364,7 +365,7 @@ class QmmWorkload(Workload):
             self._fn = L.load().w8a8_quant_matmul
             self._args = (self.x.data_ptr(), self.w.data_ptr(), self.sc.data_ptr(), None, self.pt.data_ptr(), None,
                           self._out.data_ptr(), 1, self.M, self.n, self.K, L.QM_SCALE_PERCHAN | L.QM_HAS_PT,
-                          L.DT_BF16, L.W_KN, 0)
+                          L.DT_BF16, L.W_NK if getattr(self, "layout_nk", False) else L.W_KN, 0)
         rc = self._fn(*self._args, t.cuda.current_stream().cuda_stream)
         assert rc == 0, L.status_string(rc)
 
@@ -383,7 +384,8 @@ class QmmWorkload(Workload):
     def e2e_step(self, host):
         x = host[0].to("cuda", non_blocking=True)
         pt = host[1].to("cuda", non_blocking=True)
-        out = self.ops.quant_matmul(x, self.w, self.sc, pertoken_scale=pt, output_dtype="bfloat16")
+        out = self.ops.quant_matmul(x, self.w, self.sc, pertoken_scale=pt, output_dtype="bfloat16",
+                                    transpose_x2=getattr(self, "layout_nk", False))
         o = out.to("cpu", non_blocking=True)
         return (host[0].numel() + host[1].numel() * 4, o.numel() * 2)
 
@@ -456,6 +458,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--small", action="store_true", help="reduced grouped workload (for profiling captures)")
     ap.add_argument("--qmm-m", type=int, default=8192, help="rows of the dense quant_matmul workload")
+    ap.add_argument("--layout", choices=["kn", "nk"], default="kn", help="weight layout of the matmul workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -464,6 +467,7 @@ def main():
     wl = WORKLOADS[args.workload](small=True) if (args.workload == "gmsq" and args.small) else WORKLOADS[args.workload]()
     if args.workload == "qmm":
         wl.M = args.qmm_m
+    wl.layout_nk = (args.layout == "nk")
     if args.impl == "reference":
         run_reference(args, wl)
         return

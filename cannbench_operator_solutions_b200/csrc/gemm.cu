@@ -4,6 +4,7 @@
 // grouped_matmul_swiglu_quant and grouped_matmul.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_kernel.cuh"
@@ -82,53 +83,87 @@ static bool make_map_b(CUtensorMap* m, const void* base, int64_t G, int64_t N, i
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N>
+template <int CG, int BLOCK_N>
 constexpr size_t gemm_smem_bytes()
 {
-    return static_cast<size_t>(GEMM_STAGES) * (GEMM_A_BYTES + BLOCK_N * GEMM_KBYTES) + 1024 /*alignment slack*/ +
-           256 /*barriers, tmem slot, abort flag*/;
+    return static_cast<size_t>(gemm_stages(CG, BLOCK_N)) * (GEMM_A_BYTES + (BLOCK_N / CG) * GEMM_KBYTES) +
+           1024 /*alignment slack*/ + 256 /*barriers, tmem slot, abort flag*/;
 }
 
-template <int BLOCK_N, int KIND, int EPI, bool B_MN>
+// number of workers (CTAs, or CTA pairs) a persistent launch uses
+template <int CG>
+static int64_t worker_count(int64_t max_tiles)
+{
+    int64_t workers = sm_count() / CG;
+    if (max_tiles < workers) {
+        workers = max_tiles;
+    }
+    return workers < 1 ? 1 : workers;
+}
+
+template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN>
 static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int64_t max_tiles,
                                cudaStream_t st)
 {
-    auto kern = gemm_tc_kernel<BLOCK_N, KIND, EPI, B_MN>;
-    constexpr size_t smem = gemm_smem_bytes<BLOCK_N>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    // the attribute is per device; set it on every call (cheap) so that multi-GPU processes are covered
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    (void)once;
-    if (attr_err != cudaSuccess) {
-        return attr_err;
+    auto kern = gemm_tc_kernel<CG, BLOCK_N, KIND, EPI, B_MN>;
+    constexpr size_t smem = gemm_smem_bytes<CG, BLOCK_N>();
+    // the attribute is per device; setting it on every call is cheap and covers multi-GPU processes
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) {
+        return e;
     }
-    int64_t grid = sm_count();
-    if (max_tiles < grid) {
-        grid = max_tiles;
+    const int64_t workers = worker_count<CG>(max_tiles);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(workers * CG), 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
     }
-    if (grid < 1) {
-        grid = 1;
-    }
-    kern<<<static_cast<unsigned>(grid), GEMM_THREADS, smem, st>>>(ta, tb, p);
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
 }
 
 template <int KIND, int EPI>
-static cudaError_t dispatch_gemm(int block_n, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
+static cudaError_t dispatch_gemm(int cta_group, int block_n, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
                                  const GemmParams& p, int64_t max_tiles, cudaStream_t st)
 {
-    if constexpr (EPI == EPI_GMSQ) {
-        return b_mn ? launch_gemm<256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
-                    : launch_gemm<256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
-    } else {
-        if (block_n == 128) {
-            return b_mn ? launch_gemm<128, KIND, EPI, true>(ta, tb, p, max_tiles, st)
-                        : launch_gemm<128, KIND, EPI, false>(ta, tb, p, max_tiles, st);
-        }
-        return b_mn ? launch_gemm<256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
-                    : launch_gemm<256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+    if (cta_group == 2) {
+        return b_mn ? launch_gemm<2, 256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                    : launch_gemm<2, 256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
     }
+    if constexpr (EPI != EPI_GMSQ) {
+        if (block_n == 128) {
+            return b_mn ? launch_gemm<1, 128, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                        : launch_gemm<1, 128, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+        }
+    }
+    return b_mn ? launch_gemm<1, 256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
+                : launch_gemm<1, 256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
+}
+
+// Kernel shape: CTA pairs for dense problems with enough rows to fill 256-row tiles.  The environment variable
+// W8A8_GEMM_CTA_GROUP (1 or 2) overrides the choice; the tests use it to run every case on both shapes.
+static int choose_cta_group(int64_t rows, bool grouped)
+{
+    if (const char* env = getenv("W8A8_GEMM_CTA_GROUP")) {
+        const int v = atoi(env);
+        if (v == 1 || v == 2) {
+            return v;
+        }
+    }
+    // Grouped problems keep 128-row tiles: with skewed group sizes the rows a 256-row tile pads at the end of
+    // every group cost more than pairing gains (measured on the 256-expert Zipf configuration).
+    if (grouped) {
+        return 1;
+    }
+    return rows >= 256 ? 2 : 1;
 }
 
 // ---------------------------------------------------------------------------
@@ -145,7 +180,7 @@ struct GroupEndsByValue {
 __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restrict__ dev_list,
                                                           const GroupEndsByValue by_value, int use_by_value,
                                                           int64_t E, int64_t M, GroupedHeader* header,
-                                                          TileEntry* tiles, int64_t max_tiles)
+                                                          TileEntry* tiles, int64_t max_tiles, int tile_m)
 {
     extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
     __shared__ int s_bad;
@@ -163,7 +198,7 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
                 break;
             }
             s_first[g] = static_cast<int32_t>(run);
-            run += (e - prev + GEMM_BLOCK_M - 1) / GEMM_BLOCK_M;
+            run += (e - prev + tile_m - 1) / tile_m;
             prev = e;
         }
         if (!bad && prev != M) {
@@ -189,9 +224,9 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
         for (int32_t t = threadIdx.x; t < cnt; t += blockDim.x) {
             TileEntry te;
             te.group = static_cast<int32_t>(g);
-            te.m_start = static_cast<int32_t>(start + static_cast<int64_t>(t) * GEMM_BLOCK_M);
-            const int64_t left = rows - static_cast<int64_t>(t) * GEMM_BLOCK_M;
-            te.m_rows = static_cast<int32_t>(left < GEMM_BLOCK_M ? left : GEMM_BLOCK_M);
+            te.m_start = static_cast<int32_t>(start + static_cast<int64_t>(t) * tile_m);
+            const int64_t left = rows - static_cast<int64_t>(t) * tile_m;
+            te.m_rows = static_cast<int32_t>(left < tile_m ? left : tile_m);
             te.pad = 0;
             tiles[first + t] = te;
         }
@@ -285,7 +320,7 @@ static GroupedWorkspace carve_workspace(void* ws, int64_t M, int64_t E, int64_t 
 
 // returns W8A8_OK or an error; launches the planner on `st`
 static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E, int64_t M,
-                       const GroupedWorkspace& g, cudaStream_t st)
+                       const GroupedWorkspace& g, int tile_m, cudaStream_t st)
 {
     GroupEndsByValue bv;
     int use_bv = 0;
@@ -316,7 +351,7 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
     if (smem > 48 * 1024) {
         return W8A8_ERR_UNSUPPORTED;
     }
-    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, g.header, g.tiles, g.max_tiles);
+    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, g.header, g.tiles, g.max_tiles, tile_m);
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -384,17 +419,23 @@ static int quant_matmul_impl(const int8_t* x1, const int8_t* x2, const void* sca
     p.flags = flags;
     p.out_dtype = out_dtype;
     p.bias_batch_stride = bias_batch_stride;
-    // narrow tiles when wide ones would leave most SMs idle
+    if (const char* dbg = getenv("W8A8_GEMM_DEBUG")) {
+        p.debug = atoi(dbg);
+    }
+    const int cg = choose_cta_group(M, false);
+    const int tile_m = 128 * cg;
+    p.m_tiles_per_batch = static_cast<int32_t>((M + tile_m - 1) / tile_m);
+    // narrow tiles when wide ones would leave most SMs idle (single-CTA tiles only)
     const int64_t m_tiles = batch * p.m_tiles_per_batch;
     const int64_t tiles256 = m_tiles * ((N + 255) / 256);
-    const int block_n = (tiles256 < sm_count()) ? 128 : 256;
+    const int block_n = (cg == 1 && tiles256 < sm_count()) ? 128 : 256;
     p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
     const int64_t total = m_tiles * p.n_tiles;
     cudaError_t e;
     if (raw_i32) {
-        e = dispatch_gemm<KIND_I8, EPI_RAW>(block_n, b_mn, ta, tb, p, total, st);
+        e = dispatch_gemm<KIND_I8, EPI_RAW>(cg, block_n, b_mn, ta, tb, p, total, st);
     } else {
-        e = dispatch_gemm<KIND_I8, EPI_QMM>(block_n, b_mn, ta, tb, p, total, st);
+        e = dispatch_gemm<KIND_I8, EPI_QMM>(cg, block_n, b_mn, ta, tb, p, total, st);
     }
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -470,7 +511,8 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GroupedWorkspace g = carve_workspace(workspace, M, E, H);
     if (run_matmul) {
-        const int rc = plan_groups(group_list, list_on_device, E, M, g, st);
+        const int cg = choose_cta_group(M, true);
+        const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * cg, st);
         if (rc != W8A8_OK) {
             return rc;
         }
@@ -496,8 +538,11 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.row_scale = x_scale;
         p.act = g.act;
         p.amax = g.amax;
+        if (const char* dbg = getenv("W8A8_GEMM_DEBUG")) {
+            p.debug = atoi(dbg);
+        }
         const int64_t max_total = g.max_tiles * p.n_tiles;
-        const cudaError_t e = dispatch_gemm<KIND_I8, EPI_GMSQ>(256, b_mn, ta, tb, p, max_total, st);
+        const cudaError_t e = dispatch_gemm<KIND_I8, EPI_GMSQ>(cg, 256, b_mn, ta, tb, p, max_total, st);
         if (e != cudaSuccess) {
             return W8A8_ERR_CUDA;
         }
@@ -592,7 +637,8 @@ extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bia
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GroupedWorkspace g = carve_workspace(workspace, M, E, 0);
-    const int rc = plan_groups(group_list, list_on_device, E, M, g, st);
+    const int cg = choose_cta_group(M, true);
+    const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * cg, st);
     if (rc != W8A8_OK) {
         return rc;
     }
@@ -622,11 +668,11 @@ extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bia
     const int64_t max_total = g.max_tiles * p.n_tiles;
     cudaError_t e;
     if (kind == KIND_I8) {
-        e = dispatch_gemm<KIND_I8, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+        e = dispatch_gemm<KIND_I8, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
     } else if (kind == KIND_F16) {
-        e = dispatch_gemm<KIND_F16, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+        e = dispatch_gemm<KIND_F16, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
     } else {
-        e = dispatch_gemm<KIND_BF16, EPI_GMM>(block_n, b_mn, ta, tb, p, max_total, st);
+        e = dispatch_gemm<KIND_BF16, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
     }
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

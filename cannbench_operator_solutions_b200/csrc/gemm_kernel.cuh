@@ -1,27 +1,40 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused epilogues.
 //
-// One CTA per SM, 192 threads:
-//   warp 0      TMA producer: fills a 4-deep ring of {A 128x128B, B BLOCK_N x128B}
-//               shared-memory stages (128-byte swizzle), one mbarrier per stage.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (UMMA 128 x BLOCK_N x 32B)
-//               into one of two TMEM accumulator stages; tcgen05.commit releases
-//               the shared-memory stage and finally publishes the accumulator.
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (each warp owns the 32 TMEM
-//               lanes its index selects), apply the operator's dequant chain,
-//               store.  Double-buffered TMEM lets the epilogue of tile i overlap
-//               the main loop of tile i+1.
+// One CTA per SM, 320 threads:
+//   warp 0      TMA producer: fills a ring of shared-memory stages (128-byte
+//               swizzle) with A and B tiles, one mbarrier per stage.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma into one of two TMEM
+//               accumulator stages; tcgen05.commit releases the shared-memory
+//               stage and finally publishes the accumulator.
+//   warps 2-9   epilogue: tcgen05.ld the accumulator (a warp may read the 32 TMEM
+//               lanes its index modulo 4 selects; two warps share each lane
+//               quarter and split the columns), apply the operator's dequant
+//               chain, store.  Double-buffered TMEM lets the epilogue of tile i
+//               overlap the main loop of tile i+1.
+//
+// Two shapes of the same kernel (template parameter CG):
+//   CG = 1  one CTA per tile of 128 rows x BLOCK_N columns, 4 stages of
+//           {A 128x128 B, B BLOCK_N x128 B}.  Used for small row counts.
+//   CG = 2  a pair of CTAs (cluster of 2, tcgen05 cta_group::2) per tile of 256
+//           rows x 256 columns.  Each CTA loads its 128 rows of A and its 128
+//           columns of B (6 stages of 32 KB), the even CTA issues the MMAs for
+//           both, each CTA's tensor memory receives its 128 rows of the
+//           accumulator and each CTA runs its own epilogue.  Halving the B bytes
+//           per CTA takes shared-memory and L2->SM traffic per MMA from 96 to 64
+//           bytes per clock, which is what lets the tensor pipe stay busy.  No
+//           load is multicast: each CTA fetches exactly what it stores.
 //
 // A is always K-major ([rows, K], K contiguous).  B is either K-major
 // ([.., N, K]) or MN-major ([.., K, N], the reference catalog's weight layout);
 // both are consumed directly by the tensor core through the descriptor's
 // major bit, no transposition pass.
 //
-// Tiles: 128 rows x BLOCK_N columns.  Dense problems enumerate (row tile, column
-// tile) with the row index fastest so that concurrently running CTAs share a B
-// column block in L2.  Grouped problems read a tile table built on the device
-// from the cumulative group list (tiles never straddle groups; rows past a
-// group's end inside a tile are computed and discarded) with the column index
-// fastest, so the A tile and the expert's weights stay L2-resident.
+// Dense problems enumerate (row tile, column tile) with the row index fastest
+// so that concurrently running CTAs share a B column block in L2.  Grouped
+// problems read a tile table built on the device from the cumulative group
+// list (tiles never straddle groups; rows past a group's end inside a tile
+// are computed and discarded) with the column index fastest, so the A tile
+// and the expert's weights stay L2-resident.
 #pragma once
 
 #include "common.cuh"
@@ -29,11 +42,16 @@
 
 namespace w8a8 {
 
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int GEMM_BLOCK_M = 128;
-constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_KBYTES = 128;  // bytes of K per stage row (one swizzle atom)
 constexpr int GEMM_A_BYTES = GEMM_BLOCK_M * GEMM_KBYTES;
+
+// pipeline depth: as many 1 KB-aligned stages as fit beside the barriers
+__host__ __device__ constexpr int gemm_stages(int cg, int block_n)
+{
+    return (GEMM_A_BYTES + (block_n / cg) * GEMM_KBYTES) <= 32768 ? 6 : 4;
+}
 
 enum GemmKind { KIND_I8 = 0, KIND_F16 = 1, KIND_BF16 = 2 };
 enum GemmEpi { EPI_RAW = 0, EPI_QMM = 1, EPI_GMSQ = 2, EPI_GMM = 3 };
@@ -74,6 +92,7 @@ struct GemmParams {
     int64_t bias_batch_stride;
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
+    int32_t debug;    // experiments only, bit mask: 1 = no MMA, 2 = no TMA, 4 = no epilogue work
 };
 
 // fp32 exp shared with the CPU oracle: Cody-Waite reduction by ln2 in two
@@ -129,49 +148,313 @@ __device__ __forceinline__ float vec_elem_as_float(const void* p, int64_t i, int
     }
 }
 
-template <int BLOCK_N, int KIND, int EPI, bool B_MN>
+// 32 consecutive per-channel values starting at element `idx0` (16-byte aligned
+// for every kind because idx0 is a multiple of 16), widened to fp32; a vector
+// that is not per-channel broadcasts element 0.  `valid` is 32 or 16.
+__device__ __forceinline__ void load_vec32(const void* base, int64_t idx0, int kind, bool perchan, int valid,
+                                           float (&out)[32])
+{
+    if (!perchan) {
+        const float s = vec_elem_as_float(base, 0, kind);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            out[j] = s;
+        }
+        return;
+    }
+    if (kind == W8A8_QM_BIAS_F32 || kind == W8A8_QM_BIAS_I32) {
+        const uint4* p4 = reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(base) + idx0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            uint4 t = make_uint4(0, 0, 0, 0);
+            if (q * 4 < valid) {
+                t = __ldg(p4 + q);
+            }
+            if (kind == W8A8_QM_BIAS_I32) {
+                out[q * 4 + 0] = static_cast<float>(static_cast<int32_t>(t.x));
+                out[q * 4 + 1] = static_cast<float>(static_cast<int32_t>(t.y));
+                out[q * 4 + 2] = static_cast<float>(static_cast<int32_t>(t.z));
+                out[q * 4 + 3] = static_cast<float>(static_cast<int32_t>(t.w));
+            } else {
+                out[q * 4 + 0] = __uint_as_float(t.x);
+                out[q * 4 + 1] = __uint_as_float(t.y);
+                out[q * 4 + 2] = __uint_as_float(t.z);
+                out[q * 4 + 3] = __uint_as_float(t.w);
+            }
+        }
+    } else {
+        const uint4* p4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + idx0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 t = make_uint4(0, 0, 0, 0);
+            if (q * 8 < valid) {
+                t = __ldg(p4 + q);
+            }
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (kind == W8A8_QM_BIAS_BF16) {
+                    unpack2<W8A8_DT_BF16>(w[i], out[q * 8 + 2 * i], out[q * 8 + 2 * i + 1]);
+                } else {
+                    unpack2<W8A8_DT_F16>(w[i], out[q * 8 + 2 * i], out[q * 8 + 2 * i + 1]);
+                }
+            }
+        }
+    }
+}
+
+
+struct TileInfo {
+    int32_t a_row0;  // first row this CTA loads and owns (global row index)
+    int32_t m_rows;  // valid rows among this CTA's 128
+    int32_t group;   // expert / batch (B's outermost coordinate)
+    int32_t nt;      // column tile
+};
+
+// The work of one epilogue thread on one tile: row `row_in_tile` of this CTA's
+// accumulator, columns [col_half * BLOCK_N/2, (col_half+1) * BLOCK_N/2).
+template <int BLOCK_N, int KIND, int EPI>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& tl, uint32_t t_addr,
+                                              int row_in_tile, int col_half, int64_t H, bool no_epilogue)
+{
+    const bool row_ok = (row_in_tile < tl.m_rows) && !no_epilogue;
+    const int64_t row = static_cast<int64_t>(tl.a_row0) + row_in_tile;  // global row (A and output)
+    if constexpr (EPI == EPI_GMSQ) {
+        const float xs = row_ok ? p.row_scale[row] : 0.0f;
+        const float* wsg = static_cast<const float*>(p.scale) + static_cast<int64_t>(tl.group) * p.N;
+        float local_max = 0.0f;
+        constexpr int HALF_COLS = 64;  // act columns per epilogue warp
+#pragma unroll 1
+        for (int cc = 0; cc < HALF_COLS; cc += 32) {
+            const int c = col_half * HALF_COLS + cc;
+            uint32_t g[32], u[32];
+            tc::tmem_ld_32x32(t_addr + c, g);
+            tc::tmem_ld_32x32(t_addr + 128 + c, u);
+            tc::tmem_ld_wait();
+            const int64_t col0 = static_cast<int64_t>(tl.nt) * 128 + c;  // column in [0, H)
+            if (row_ok) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int64_t col = col0 + q * 4;
+                    if (col < H) {
+                        const float4 wg = __ldg(reinterpret_cast<const float4*>(wsg + col));
+                        const float4 wu = __ldg(reinterpret_cast<const float4*>(wsg + H + col));
+                        const float wga[4] = {wg.x, wg.y, wg.z, wg.w};
+                        const float wua[4] = {wu.x, wu.y, wu.z, wu.w};
+                        float a[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float l = __fmul_rn(
+                                __fmul_rn(static_cast<float>(static_cast<int32_t>(g[q * 4 + j])), xs), wga[j]);
+                            const float r = __fmul_rn(
+                                __fmul_rn(static_cast<float>(static_cast<int32_t>(u[q * 4 + j])), xs), wua[j]);
+                            a[j] = __fmul_rn(canonical_silu(l), r);
+                            local_max = fmaxf(local_max, fabsf(a[j]));
+                        }
+                        *reinterpret_cast<float4*>(p.act + row * H + col) = make_float4(a[0], a[1], a[2], a[3]);
+                    }
+                }
+            }
+        }
+        if (row_ok) {
+            atomicMax(reinterpret_cast<int*>(p.amax + row), __float_as_int(local_max));
+        }
+    } else {
+        // per-tile invariants of the dequant chain, hoisted out of the column loops
+        float row_mul = 1.0f;
+        bool has_pt = false;
+        int bias_kind = W8A8_QM_BIAS_NONE;
+        bool bias_perchan = false, scale_perchan = true, scale_bf16 = false, has_offset = false,
+             offset_perchan = false;
+        const void* bias = p.bias;
+        int64_t vec_base = 0;  // first element of the per-channel vectors for this tile's group
+        if constexpr (EPI == EPI_QMM) {
+            const int64_t f = p.flags;
+            has_pt = (f & W8A8_QM_HAS_PT) != 0;
+            if (has_pt && row_ok) {
+                // the plugin's layouts make (row mod M) the token index in every case
+                row_mul = p.row_scale[(tl.group == 0) ? row : (row - static_cast<int64_t>(tl.group) * p.M)];
+            }
+            bias_kind = static_cast<int>((f & W8A8_QM_BIAS_MASK) >> W8A8_QM_BIAS_SHIFT);
+            bias_perchan = (f & W8A8_QM_BIAS_PERCHAN) != 0;
+            scale_perchan = (f & W8A8_QM_SCALE_PERCHAN) != 0;
+            scale_bf16 = (f & W8A8_QM_SCALE_BF16) != 0;
+            has_offset = (f & W8A8_QM_HAS_OFFSET) != 0;
+            offset_perchan = (f & W8A8_QM_OFFSET_PERCHAN) != 0;
+            if (bias != nullptr && p.bias_batch_stride != 0) {
+                const int64_t esz = (bias_kind == W8A8_QM_BIAS_F16 || bias_kind == W8A8_QM_BIAS_BF16) ? 2 : 4;
+                bias = static_cast<const uint8_t*>(bias) + tl.group * p.bias_batch_stride * esz;
+            }
+        } else if constexpr (EPI == EPI_GMM) {
+            if constexpr (KIND == KIND_I8) {
+                row_mul = row_ok ? p.row_scale[row] : 0.0f;
+            }
+            vec_base = static_cast<int64_t>(tl.group) * p.N;
+            if (p.flags & 4) {
+                const int bdt = static_cast<int>(p.flags & 3);
+                bias_kind = (bdt == W8A8_DT_F16) ? W8A8_QM_BIAS_F16
+                                                  : (bdt == W8A8_DT_BF16 ? W8A8_QM_BIAS_BF16 : W8A8_QM_BIAS_F32);
+                bias_perchan = true;
+            }
+        }
+        constexpr int HALF_COLS = BLOCK_N / 2;
+#pragma unroll 1
+        for (int cc = 0; cc < HALF_COLS; cc += 32) {
+            const int c = col_half * HALF_COLS + cc;
+            uint32_t r[32];
+            tc::tmem_ld_32x32(t_addr + c, r);
+            tc::tmem_ld_wait();
+            const int64_t col0 = static_cast<int64_t>(tl.nt) * BLOCK_N + c;
+            if (!row_ok || col0 >= p.N) {
+                continue;
+            }
+            // N is a multiple of 16: a chunk holds 32 or 16 valid columns
+            const int valid = (col0 + 32 <= p.N) ? 32 : 16;
+            if constexpr (EPI == EPI_RAW) {
+                int32_t* dst = static_cast<int32_t*>(p.out) + row * p.N + col0;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (q * 4 < valid) {
+                        *reinterpret_cast<uint4*>(dst + q * 4) =
+                            make_uint4(r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+                    }
+                }
+            } else {
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if constexpr (KIND == KIND_I8) {
+                        v[j] = static_cast<float>(static_cast<int32_t>(r[j]));
+                    } else {
+                        v[j] = __uint_as_float(r[j]);
+                    }
+                }
+                float w[32];
+                if constexpr (EPI == EPI_QMM) {
+                    if (bias_kind == W8A8_QM_BIAS_I32) {
+                        load_vec32(bias, col0, bias_kind, bias_perchan, valid, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fadd_rn(v[j], w[j]);
+                        }
+                    }
+                    load_vec32(p.scale, col0, scale_bf16 ? W8A8_QM_BIAS_BF16 : W8A8_QM_BIAS_F32, scale_perchan,
+                               valid, w);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __fmul_rn(v[j], w[j]);
+                    }
+                    if (has_offset) {
+                        load_vec32(p.offset, col0, W8A8_QM_BIAS_F32, offset_perchan, valid, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fadd_rn(v[j], w[j]);
+                        }
+                    }
+                    if (has_pt) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fmul_rn(v[j], row_mul);
+                        }
+                    }
+                    if (bias_kind >= W8A8_QM_BIAS_F16) {
+                        load_vec32(bias, col0, bias_kind, bias_perchan, valid, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fadd_rn(v[j], w[j]);
+                        }
+                    }
+                } else {  // EPI_GMM
+                    if constexpr (KIND == KIND_I8) {
+                        load_vec32(p.scale, vec_base + col0, W8A8_QM_BIAS_F32, true, valid, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fmul_rn(__fmul_rn(v[j], w[j]), row_mul);
+                        }
+                    }
+                    if (bias_kind != W8A8_QM_BIAS_NONE) {
+                        load_vec32(bias, vec_base + col0, bias_kind, true, valid, w);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __fadd_rn(v[j], w[j]);
+                        }
+                    }
+                }
+                // 32 outputs -> four 16-byte stores of 16-bit values
+                uint16_t* dst = static_cast<uint16_t*>(p.out) + row * p.N + col0;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (q * 8 < valid) {
+                        uint4 o;
+                        if (p.out_dtype == W8A8_DT_BF16) {
+                            o = make_uint4(pack2<W8A8_DT_BF16>(v[q * 8], v[q * 8 + 1]),
+                                           pack2<W8A8_DT_BF16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                           pack2<W8A8_DT_BF16>(v[q * 8 + 4], v[q * 8 + 5]),
+                                           pack2<W8A8_DT_BF16>(v[q * 8 + 6], v[q * 8 + 7]));
+                        } else {
+                            o = make_uint4(pack2<W8A8_DT_F16>(v[q * 8], v[q * 8 + 1]),
+                                           pack2<W8A8_DT_F16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                           pack2<W8A8_DT_F16>(v[q * 8 + 4], v[q * 8 + 5]),
+                                           pack2<W8A8_DT_F16>(v[q * 8 + 6], v[q * 8 + 7]));
+                        }
+                        *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const GemmParams p)
 {
     constexpr int ELEM = (KIND == KIND_I8) ? 1 : 2;
-    constexpr int BLOCK_K = GEMM_KBYTES / ELEM;   // elements of K per stage
-    constexpr int UMMA_K = 32 / ELEM;             // elements of K per instruction
-    constexpr int NBOX = BLOCK_N * ELEM / 128;    // MN-major: 128-byte-wide column blocks per tile
-    constexpr int B_BYTES = BLOCK_N * GEMM_KBYTES;
+    constexpr int BLOCK_K = GEMM_KBYTES / ELEM;    // elements of K per stage
+    constexpr int UMMA_K = 32 / ELEM;              // elements of K per instruction
+    constexpr int CTA_N = BLOCK_N / CG;            // B columns this CTA loads
+    constexpr int NBOX = CTA_N * ELEM / 128;       // MN-major: 128-byte-wide column blocks this CTA loads
+    constexpr int B_BYTES = CTA_N * GEMM_KBYTES;
     constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 256 or 512: power of two
+    constexpr int STAGES = gemm_stages(CG, BLOCK_N);
+    constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;    // 256 or 512: power of two
+    constexpr uint32_t UMMA_M = 128 * CG;
     constexpr uint32_t IDESC =
-        (KIND == KIND_I8) ? tc::instr_desc(2u, 1u, B_MN ? 1u : 0u, GEMM_BLOCK_M, BLOCK_N)
-                          : tc::instr_desc(1u, (KIND == KIND_BF16) ? 1u : 0u, B_MN ? 1u : 0u, GEMM_BLOCK_M, BLOCK_N);
+        (KIND == KIND_I8) ? tc::instr_desc(2u, 1u, B_MN ? 1u : 0u, UMMA_M, BLOCK_N)
+                          : tc::instr_desc(1u, (KIND == KIND_BF16) ? 1u : 0u, B_MN ? 1u : 0u, UMMA_M, BLOCK_N);
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
+    static_assert(CG == 1 || BLOCK_N == 256, "CTA pairs use 256-column tiles");
     static_assert(EPI != EPI_GMSQ || BLOCK_N == 256, "the SwiGLU epilogue pairs 128 gate with 128 up columns");
 
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment: required by the 128-byte swizzle atoms
+    // 1024-byte alignment: required by the 128-byte swizzle atoms.  The dynamic shared memory window starts at
+    // the same offset in both CTAs of a pair, so the layout below is identical in both.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GEMM_STAGES * STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GEMM_STAGES + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CG == 2) ? tc::cluster_ctarank() : 0u;
+    const bool leader = (cta_rank == 0);
     const uint32_t smem_base = tc::smem_u32(smem);
     const uint32_t bar_base = tc::smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (GEMM_STAGES + s); };
-    auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * GEMM_STAGES + s); };
-    auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * GEMM_STAGES + 2 + s); };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+    auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < GEMM_STAGES; ++s) {
-            tc::mbar_init(full_bar(s), 1);
-            tc::mbar_init(empty_bar(s), 1);
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(full_bar(s), 1);   // the (leader's) producer's arrive.expect_tx; bytes from every CTA of the tile
+            tc::mbar_init(empty_bar(s), 1);  // one commit (multicast to both CTAs of a pair)
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(tfull_bar(s), 1);
-            tc::mbar_init(tempty_bar(s), 128);
+            tc::mbar_init(tempty_bar(s), 8 * CG);  // one arrival per epilogue warp of every CTA on the tile
         }
         *abort_flag = 0;
         tc::fence_mbar_init();
@@ -179,63 +462,73 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tc::prefetch_tensormap(&tm_b);
     }
     if (warp == 1) {
+        // each CTA allocates its own tensor memory; a pair asks for all 512 columns in both CTAs, so the
+        // accumulator has the same column address in both, as the paired MMA requires
         tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
         tc::tmem_relinquish();
     }
     tc::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) {
+        // both CTAs' barriers must be initialised before either signals the other
+        tc::cluster_arrive();
+        tc::cluster_wait();
+    }
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // ---- tile enumeration (identical in every role) ----
+    // ---- tile enumeration (identical in every role and in both CTAs of a pair) ----
+    constexpr int TILE_M = 128 * CG;
     int64_t total_tiles;
     int32_t dense_m_tiles = 0;
     if (p.grouped) {
-        const int32_t nmt = p.header->num_m_tiles;
-        total_tiles = static_cast<int64_t>(nmt) * p.n_tiles;
+        total_tiles = static_cast<int64_t>(p.header->num_m_tiles) * p.n_tiles;
     } else {
         dense_m_tiles = p.batch * p.m_tiles_per_batch;
         total_tiles = static_cast<int64_t>(dense_m_tiles) * p.n_tiles;
     }
     const int64_t H = p.N / 2;  // GMSQ half width
+    const int64_t worker = blockIdx.x / CG;
+    const int64_t num_workers = gridDim.x / CG;
 
-    struct Tile {
-        int32_t a_row0;   // first row of the A tile (global row index)
-        int32_t m_rows;   // valid rows
-        int32_t group;    // expert / batch (B's outermost coordinate)
-        int32_t nt;       // column tile
-    };
     auto decode = [&](int64_t t) {
-        Tile tl;
+        TileInfo tl;
+        int64_t tile_row0;
+        int32_t tile_rows;
         if (p.grouped) {
             const int32_t mt = static_cast<int32_t>(t / p.n_tiles);
             tl.nt = static_cast<int32_t>(t % p.n_tiles);
             const TileEntry e = p.tiles[mt];
-            tl.a_row0 = e.m_start;
-            tl.m_rows = e.m_rows;
+            tile_row0 = e.m_start;
+            tile_rows = e.m_rows;
             tl.group = e.group;
         } else {
             const int32_t mg = static_cast<int32_t>(t % dense_m_tiles);
             tl.nt = static_cast<int32_t>(t / dense_m_tiles);
             const int32_t b = mg / p.m_tiles_per_batch;
             const int32_t mt = mg % p.m_tiles_per_batch;
-            const int64_t m0 = static_cast<int64_t>(mt) * GEMM_BLOCK_M;
-            tl.a_row0 = static_cast<int32_t>(b * p.M + m0);
+            const int64_t m0 = static_cast<int64_t>(mt) * TILE_M;
+            tile_row0 = b * p.M + m0;
             const int64_t left = p.M - m0;
-            tl.m_rows = static_cast<int32_t>(left < GEMM_BLOCK_M ? left : GEMM_BLOCK_M);
+            tile_rows = static_cast<int32_t>(left < TILE_M ? left : TILE_M);
             tl.group = b;
         }
+        tl.a_row0 = static_cast<int32_t>(tile_row0 + 128 * static_cast<int64_t>(cta_rank));
+        int32_t mine = tile_rows - 128 * static_cast<int32_t>(cta_rank);
+        tl.m_rows = mine < 0 ? 0 : (mine > 128 ? 128 : mine);
         return tl;
     };
-    // first column of 128-element column block `i` of column tile nt
-    auto box_col = [&](int32_t nt, int i) -> int32_t {
+    // first column (MN-major) / first N row (K-major) of block `i` among the blocks THIS CTA loads for column
+    // tile nt.  With the SwiGLU epilogue the first half of the tile's columns are gate columns and the second
+    // half the matching up columns, H apart in the weight.
+    auto b_block_origin = [&](int32_t nt, int i, int block_width) -> int32_t {
+        const int g = static_cast<int>(cta_rank) * (CTA_N / block_width) + i;  // block index within the full tile
+        const int per_half = (BLOCK_N / 2) / block_width;
         if constexpr (EPI == EPI_GMSQ) {
-            // 128-byte blocks [0, NBOX/2) are gate columns, the rest the matching up columns
-            constexpr int HB = NBOX / 2;
-            const int32_t within = (i % HB) * (128 / ELEM);
-            return static_cast<int32_t>((i < HB ? 0 : H) + static_cast<int64_t>(nt) * (BLOCK_N / 2) + within);
+            const int64_t base = (g < per_half ? 0 : H) + static_cast<int64_t>(nt) * (BLOCK_N / 2);
+            return static_cast<int32_t>(base + (g % per_half) * block_width);
         } else {
-            return nt * BLOCK_N + i * (128 / ELEM);
+            return nt * BLOCK_N + g * block_width;
         }
     };
 
@@ -245,42 +538,64 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                const Tile tl = decode(t);
+            // a pair credits both CTAs' bytes to the leader's barrier
+            const uint32_t full0 = (CG == 2) ? tc::map_to_cta(full_bar(0), 0) : full_bar(0);
+            for (int64_t t = worker; ok && t < total_tiles; t += num_workers) {
+                const TileInfo tl = decode(t);
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + GEMM_A_BYTES;
-                    tc::mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
-                    tc::tma_load_2d(a_dst, &tm_a, full_bar(stage), kb * BLOCK_K, tl.a_row0);
-                    if constexpr (B_MN) {
-                        // boxes of {128 bytes of N, BLOCK_K rows of K}
-                        constexpr int BOX_BYTES = BLOCK_K * 128;
-#pragma unroll
-                        for (int i = 0; i < NBOX; ++i) {
-                            tc::tma_load_3d(b_dst + i * BOX_BYTES, &tm_b, full_bar(stage), box_col(tl.nt, i),
-                                            kb * BLOCK_K, tl.group);
+                    const uint32_t fb = full0 + 8u * stage;
+                    if (p.debug & 2) {
+                        if (leader) {
+                            tc::mbar_arrive(full_bar(stage));
                         }
                     } else {
-                        // boxes of {128 bytes of K, 128 rows of N}
-                        constexpr int ROWS_PER_BOX = 128;
-                        constexpr int BOXES = BLOCK_N / ROWS_PER_BOX;
+                        const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+                        const uint32_t b_dst = a_dst + GEMM_A_BYTES;
+                        // Only the leader announces the bytes (its own and its partner's).  The partner's copies may
+                        // complete first: the barrier's phase cannot end before the leader's arrival, and a
+                        // transaction count may run ahead of its announcement.
+                        if (leader) {
+                            tc::mbar_arrive_expect_tx(full_bar(stage), CG * STAGE_BYTES);
+                        }
+                        if constexpr (CG == 2) {
+                            tc::tma_load_2d_pair(a_dst, &tm_a, fb, kb * BLOCK_K, tl.a_row0);
+                        } else {
+                            tc::tma_load_2d(a_dst, &tm_a, fb, kb * BLOCK_K, tl.a_row0);
+                        }
+                        if constexpr (B_MN) {
+                            // boxes of {128 bytes of N, BLOCK_K rows of K}
+                            constexpr int BOX_BYTES = BLOCK_K * 128;
+                            constexpr int BOX_COLS = 128 / ELEM;
 #pragma unroll
-                        for (int i = 0; i < BOXES; ++i) {
-                            int32_t n_row;
-                            if constexpr (EPI == EPI_GMSQ) {
-                                n_row = static_cast<int32_t>((i == 0 ? 0 : H) + static_cast<int64_t>(tl.nt) * 128);
-                            } else {
-                                n_row = tl.nt * BLOCK_N + i * ROWS_PER_BOX;
+                            for (int i = 0; i < NBOX; ++i) {
+                                const int32_t col = b_block_origin(tl.nt, i, BOX_COLS);
+                                if constexpr (CG == 2) {
+                                    tc::tma_load_3d_pair(b_dst + i * BOX_BYTES, &tm_b, fb, col, kb * BLOCK_K, tl.group);
+                                } else {
+                                    tc::tma_load_3d(b_dst + i * BOX_BYTES, &tm_b, fb, col, kb * BLOCK_K, tl.group);
+                                }
                             }
-                            tc::tma_load_3d(b_dst + i * ROWS_PER_BOX * GEMM_KBYTES, &tm_b, full_bar(stage),
-                                            kb * BLOCK_K, n_row, tl.group);
+                        } else {
+                            // boxes of {128 bytes of K, 128 rows of N}
+                            constexpr int BOXES = CTA_N / 128;
+#pragma unroll
+                            for (int i = 0; i < BOXES; ++i) {
+                                const int32_t n_row = b_block_origin(tl.nt, i, 128);
+                                if constexpr (CG == 2) {
+                                    tc::tma_load_3d_pair(b_dst + i * 128 * GEMM_KBYTES, &tm_b, fb, kb * BLOCK_K, n_row,
+                                                         tl.group);
+                                } else {
+                                    tc::tma_load_3d(b_dst + i * 128 * GEMM_KBYTES, &tm_b, fb, kb * BLOCK_K, n_row,
+                                                    tl.group);
+                                }
+                            }
                         }
                     }
-                    if (++stage == GEMM_STAGES) {
+                    if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
@@ -289,66 +604,89 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ===================== MMA issuer =====================
-        if (lane == 0) {
+        // ===================== MMA issuer (leader CTA only) =====================
+        if (lane == 0 && leader) {
+            // Descriptors as {lo, hi}: hi is loop invariant; a byte offset adds (offset >> 4) to lo.
+            const uint64_t a_desc0 = tc::smem_desc_sw128(smem_base, 16, 1024);
+            const uint64_t b_desc0 = B_MN ? tc::smem_desc_sw128(smem_base + GEMM_A_BYTES, BLOCK_K * 128, 1024)
+                                          : tc::smem_desc_sw128(smem_base + GEMM_A_BYTES, 16, 1024);
+            const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32);
+            const uint32_t b_hi = static_cast<uint32_t>(b_desc0 >> 32);
+            const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0);
+            const uint32_t b_lo0 = static_cast<uint32_t>(b_desc0);
+            constexpr uint32_t STAGE_STEP = STAGE_BYTES >> 4;
+            constexpr uint32_t A_KSTEP = 32 >> 4;                                   // 32 bytes of K
+            constexpr uint32_t B_KSTEP = B_MN ? ((UMMA_K * 128) >> 4) : (32 >> 4);  // UMMA_K rows of 128 bytes, or 32 bytes
+            constexpr int KSTEPS = BLOCK_K / UMMA_K;
             int stage = 0;
             uint32_t phase = 0;
             int64_t it = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+            for (int64_t t = worker; ok && t < total_tiles; t += num_workers, ++it) {
                 const int acc = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-                if (!tc::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+                if (!tc::mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+                uint32_t accumulate = 0;
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    if (!tc::mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    if (!tc::mbar_wait_cluster(full_bar(stage), phase, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc::tc_fence_after_sync();
-                    const uint32_t a_src = smem_base + stage * STAGE_BYTES;
-                    const uint32_t b_src = a_src + GEMM_A_BYTES;
-#pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint64_t a_desc = tc::smem_desc_sw128(a_src + k * 32, 16, 1024);
-                        uint64_t b_desc;
-                        if constexpr (B_MN) {
-                            // K advances by UMMA_K rows of 128 bytes; column blocks are BLOCK_K rows apart
-                            b_desc = tc::smem_desc_sw128(b_src + k * UMMA_K * 128, BLOCK_K * 128, 1024);
+                    if (p.debug & 1) {
+                        if constexpr (CG == 2) {
+                            tc::mbar_arrive_cluster(tc::map_to_cta(empty_bar(stage), 0));
+                            tc::mbar_arrive_cluster(tc::map_to_cta(empty_bar(stage), 1));
                         } else {
-                            b_desc = tc::smem_desc_sw128(b_src + k * 32, 16, 1024);
+                            tc::mbar_arrive(empty_bar(stage));
                         }
-                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-                        if constexpr (KIND == KIND_I8) {
-                            tc::mma_i8(d_tmem, a_desc, b_desc, IDESC, accumulate);
+                    } else {
+                        const uint32_t a_lo = a_lo0 + stage * STAGE_STEP;
+                        const uint32_t b_lo = b_lo0 + stage * STAGE_STEP;
+#pragma unroll
+                        for (int k = 0; k < KSTEPS; ++k) {
+                            tc::mma_lohi<CG, KIND == KIND_I8>(d_tmem, a_lo + k * A_KSTEP, a_hi, b_lo + k * B_KSTEP, b_hi,
+                                                             IDESC, accumulate);
+                            accumulate = 1;
+                        }
+                        if constexpr (CG == 2) {
+                            tc::tc_commit_pair(empty_bar(stage));
                         } else {
-                            tc::mma_f16(d_tmem, a_desc, b_desc, IDESC, accumulate);
+                            tc::tc_commit(empty_bar(stage));
                         }
                     }
-                    tc::tc_commit(empty_bar(stage));
-                    if (++stage == GEMM_STAGES) {
+                    if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (ok) {
-                    tc::tc_commit(tfull_bar(acc));
+                    if constexpr (CG == 2) {
+                        tc::tc_commit_pair(tfull_bar(acc));
+                    } else {
+                        tc::tc_commit(tfull_bar(acc));
+                    }
                 }
             }
         }
         __syncwarp();
     } else {
-        // ===================== epilogue (warps 2..5) =====================
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+        // ===================== epilogue (warps 2..9) =====================
+        // Two warps per TMEM lane quarter; they split the tile's columns in halves.
+        const int quarter = warp & 3;          // TMEM lanes [32*quarter, 32*quarter+32)
+        const int col_half = (warp - 2) >> 2;  // 0 or 1
         const int row_in_tile = quarter * 32 + lane;
+        const bool no_epilogue = (p.debug & 4) != 0;
+        const uint32_t tempty0 = (CG == 2) ? tc::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         int64_t it = 0;
         bool ok = true;
-        for (int64_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
-            const Tile tl = decode(t);
+        for (int64_t t = worker; ok && t < total_tiles; t += num_workers, ++it) {
+            const TileInfo tl = decode(t);
             const int acc = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             if (!tc::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
@@ -358,171 +696,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             tc::tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                     static_cast<uint32_t>(acc * BLOCK_N);
-            const bool row_ok = row_in_tile < tl.m_rows;
-            const int64_t row = static_cast<int64_t>(tl.a_row0) + row_in_tile;  // global row (A and output)
-
-            if constexpr (EPI == EPI_GMSQ) {
-                const float xs = row_ok ? p.row_scale[row] : 0.0f;
-                const float* wsg = static_cast<const float*>(p.scale) + static_cast<int64_t>(tl.group) * p.N;
-                float local_max = 0.0f;
-#pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
-                    uint32_t g[32], u[32];
-                    tc::tmem_ld_32x32(t_addr + c, g);
-                    tc::tmem_ld_32x32(t_addr + 128 + c, u);
-                    tc::tmem_ld_wait();
-                    const int64_t col0 = static_cast<int64_t>(tl.nt) * 128 + c;  // column in [0, H)
-                    if (row_ok) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const int64_t col = col0 + q * 4;
-                            if (col < H) {
-                                const float4 wg = __ldg(reinterpret_cast<const float4*>(wsg + col));
-                                const float4 wu = __ldg(reinterpret_cast<const float4*>(wsg + H + col));
-                                const float wga[4] = {wg.x, wg.y, wg.z, wg.w};
-                                const float wua[4] = {wu.x, wu.y, wu.z, wu.w};
-                                float a[4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const float l = __fmul_rn(
-                                        __fmul_rn(static_cast<float>(static_cast<int32_t>(g[q * 4 + j])), xs), wga[j]);
-                                    const float r = __fmul_rn(
-                                        __fmul_rn(static_cast<float>(static_cast<int32_t>(u[q * 4 + j])), xs), wua[j]);
-                                    a[j] = __fmul_rn(canonical_silu(l), r);
-                                    local_max = fmaxf(local_max, fabsf(a[j]));
-                                }
-                                *reinterpret_cast<float4*>(p.act + row * H + col) = make_float4(a[0], a[1], a[2], a[3]);
-                            }
-                        }
-                    }
-                }
-                if (row_ok) {
-                    atomicMax(reinterpret_cast<int*>(p.amax + row), __float_as_int(local_max));
-                }
-            } else {
-                float row_mul = 1.0f;
-                if constexpr (EPI == EPI_QMM) {
-                    if ((p.flags & W8A8_QM_HAS_PT) && row_ok) {
-                        // the plugin's layouts make (row mod M) the token index in every case
-                        row_mul = p.row_scale[row % p.M];
-                    }
-                } else if constexpr (EPI == EPI_GMM && KIND == KIND_I8) {
-                    row_mul = row_ok ? p.row_scale[row] : 0.0f;
-                }
-#pragma unroll 1
-                for (int c = 0; c < BLOCK_N; c += 32) {
-                    uint32_t r[32];
-                    tc::tmem_ld_32x32(t_addr + c, r);
-                    tc::tmem_ld_wait();
-                    const int64_t col0 = static_cast<int64_t>(tl.nt) * BLOCK_N + c;
-                    if (!row_ok || col0 >= p.N) {
-                        continue;
-                    }
-                    if constexpr (EPI == EPI_RAW) {
-                        int32_t* dst = static_cast<int32_t*>(p.out) + row * p.N + col0;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            if (col0 + q * 4 < p.N) {
-                                *reinterpret_cast<uint4*>(dst + q * 4) =
-                                    make_uint4(r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
-                            }
-                        }
-                    } else {
-                        float v[32];
-                        if constexpr (EPI == EPI_QMM) {
-                            const int64_t f = p.flags;
-                            const int bias_kind = static_cast<int>((f & W8A8_QM_BIAS_MASK) >> W8A8_QM_BIAS_SHIFT);
-                            const void* bias = p.bias;
-                            if (bias != nullptr && p.bias_batch_stride != 0) {
-                                const int64_t esz = (bias_kind == W8A8_QM_BIAS_F16 || bias_kind == W8A8_QM_BIAS_BF16) ? 2 : 4;
-                                bias = static_cast<const uint8_t*>(bias) + tl.group * p.bias_batch_stride * esz;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int64_t col = col0 + j;
-                                float x = static_cast<float>(static_cast<int32_t>(r[j]));
-                                if (col < p.N) {
-                                    if (bias_kind == W8A8_QM_BIAS_I32) {
-                                        x = __fadd_rn(x, vec_elem_as_float(bias, (f & W8A8_QM_BIAS_PERCHAN) ? col : 0,
-                                                                           bias_kind));
-                                    }
-                                    const int64_t si = (f & W8A8_QM_SCALE_PERCHAN) ? col : 0;
-                                    const float sc = (f & W8A8_QM_SCALE_BF16)
-                                                         ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.scale)[si])
-                                                         : static_cast<const float*>(p.scale)[si];
-                                    x = __fmul_rn(x, sc);
-                                    if (f & W8A8_QM_HAS_OFFSET) {
-                                        x = __fadd_rn(x, p.offset[(f & W8A8_QM_OFFSET_PERCHAN) ? col : 0]);
-                                    }
-                                    if (f & W8A8_QM_HAS_PT) {
-                                        x = __fmul_rn(x, row_mul);
-                                    }
-                                    if (bias_kind >= W8A8_QM_BIAS_F16) {
-                                        x = __fadd_rn(x, vec_elem_as_float(bias, (f & W8A8_QM_BIAS_PERCHAN) ? col : 0,
-                                                                           bias_kind));
-                                    }
-                                }
-                                v[j] = x;
-                            }
-                        } else {  // EPI_GMM
-                            const int has_bias = static_cast<int>(p.flags & 4);
-                            const int bias_dt = static_cast<int>(p.flags & 3);
-                            const int64_t gbase = static_cast<int64_t>(tl.group) * p.N;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const int64_t col = col0 + j;
-                                float x;
-                                if constexpr (KIND == KIND_I8) {
-                                    x = static_cast<float>(static_cast<int32_t>(r[j]));
-                                } else {
-                                    x = __uint_as_float(r[j]);
-                                }
-                                if (col < p.N) {
-                                    if constexpr (KIND == KIND_I8) {
-                                        x = __fmul_rn(__fmul_rn(x, static_cast<const float*>(p.scale)[gbase + col]),
-                                                      row_mul);
-                                    }
-                                    if (has_bias) {
-                                        float bv;
-                                        if (bias_dt == W8A8_DT_F16) {
-                                            bv = __half2float(static_cast<const __half*>(p.bias)[gbase + col]);
-                                        } else if (bias_dt == W8A8_DT_BF16) {
-                                            bv = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[gbase + col]);
-                                        } else {
-                                            bv = static_cast<const float*>(p.bias)[gbase + col];
-                                        }
-                                        x = __fadd_rn(x, bv);
-                                    }
-                                }
-                                v[j] = x;
-                            }
-                        }
-                        // 32 outputs -> four 16-byte stores of 16-bit values
-                        uint16_t* dst = static_cast<uint16_t*>(p.out) + row * p.N + col0;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            if (col0 + q * 8 < p.N) {
-                                uint4 o;
-                                if (p.out_dtype == W8A8_DT_BF16) {
-                                    o = make_uint4(pack2<W8A8_DT_BF16>(v[q * 8], v[q * 8 + 1]),
-                                                   pack2<W8A8_DT_BF16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                                   pack2<W8A8_DT_BF16>(v[q * 8 + 4], v[q * 8 + 5]),
-                                                   pack2<W8A8_DT_BF16>(v[q * 8 + 6], v[q * 8 + 7]));
-                                } else {
-                                    o = make_uint4(pack2<W8A8_DT_F16>(v[q * 8], v[q * 8 + 1]),
-                                                   pack2<W8A8_DT_F16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                                   pack2<W8A8_DT_F16>(v[q * 8 + 4], v[q * 8 + 5]),
-                                                   pack2<W8A8_DT_F16>(v[q * 8 + 6], v[q * 8 + 7]));
-                                }
-                                *reinterpret_cast<uint4*>(dst + q * 8) = o;
-                            }
-                        }
-                    }
+            epilogue_tile<BLOCK_N, KIND, EPI>(p, tl, t_addr, row_in_tile, col_half, H, no_epilogue);
+            // accumulator stage drained: hand it back to the MMA issuer (one arrival per warp)
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CG == 2) {
+                    tc::mbar_arrive_cluster(tempty0 + 8u * acc);
+                } else {
+                    tc::mbar_arrive(tempty0 + 8u * acc);
                 }
             }
-            // accumulator stage drained: hand it back to the MMA issuer
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(tempty_bar(acc));
         }
     }
 
@@ -531,16 +715,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncthreads();
     if (*abort_flag != 0) {
         // a wait ran out: record it, then give copies still in flight time to land
-        if (threadIdx.x == 0) {
-            if (p.error != nullptr) {
-                atomicExch(p.error, 2);
-            }
+        if (threadIdx.x == 0 && p.error != nullptr) {
+            atomicExch(p.error, 2);
         }
-        const unsigned long long t0 = tc::global_ns();
-        while (tc::global_ns() - t0 < 200000ull) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000ll) {
             __nanosleep(1000);
         }
         __syncthreads();
+    }
+    if constexpr (CG == 2) {
+        // neither CTA may release tensor memory or exit while its partner can still signal it
+        tc::cluster_arrive();
+        tc::cluster_wait();
     }
     if (warp == 1) {
         tc::tc_fence_after_sync();

@@ -2,7 +2,7 @@
 // mbarriers, TMA tiled loads, tensor-memory allocation, tcgen05 MMA / commit /
 // load, and the shared-memory and instruction descriptors they consume.
 //
-// Every wait is bounded: a wait that does not complete within WAIT_LIMIT_NS
+// Every wait is bounded: a wait that does not complete within WAIT_LIMIT_CYCLES
 // raises the CTA's abort flag and returns false, so a kernel built on these
 // helpers ends with an error status instead of spinning.
 #pragma once
@@ -14,7 +14,7 @@
 namespace w8a8 {
 namespace tc {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about 2 s of SM clock
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
@@ -65,21 +65,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.
+// The fast path is a bare try_wait loop: no timer is read until a wait has
+// already spun for a while (the global timer is slow to read), and the limit
+// is then checked against the SM clock.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
     }
-    const unsigned long long t0 = global_ns();
+    const long long t0 = clock64();
+#pragma unroll 1
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) {
             return true;
         }
-        if ((i & 255u) == 0u) {
+        if ((i & 1023u) == 0u) {
             if (*abort_flag != 0) {
                 return false;
             }
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
                 return false;
             }
@@ -193,6 +200,158 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 2i and 2i+1) drive one 256-row MMA: each holds
+// 128 rows of A and half of B's columns in its own shared memory and 128 rows
+// of the accumulator in its own tensor memory.  The even-ranked CTA (the
+// leader) issues the MMAs and owns the barriers the MMAs wait on.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_arrive()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// arrivals on a barrier that may live in the peer CTA (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
+                 "r"(bytes)
+                 : "memory");
+}
+
+// try_wait with cluster-scope acquire: the barrier is local, the arrivals may be remote
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) {
+            return true;
+        }
+    }
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) {
+            return true;
+        }
+        if ((i & 1023u) == 0u) {
+            if (*abort_flag != 0) {
+                return false;
+            }
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Tiled loads (no multicast) whose completion is signalled on a barrier that
+// may belong to the peer CTA of the pair: data lands in THIS CTA's shared
+// memory, the byte count is credited to `cluster_bar`.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                 int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                 int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the
+// pair once every MMA issued so far has finished.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(mask)
+        : "memory");
+}
+
+// Descriptors as {lo, hi} register pairs: the high word is loop invariant and
+// advancing the operand by `bytes` adds bytes >> 4 to the low word.
+template <int CG, bool I8>
+__device__ __forceinline__ void mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                         uint32_t idesc, uint32_t accumulate)
+{
+    if constexpr (CG == 1 && I8) {
+        asm volatile(
+            "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if constexpr (CG == 1 && !I8) {
+        asm volatile(
+            "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else if constexpr (CG == 2 && I8) {
+        asm volatile(
+            "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n.reg .pred p;\n.reg .b64 da, db;\nsetp.ne.b32 p, %6, 0;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 // ------------------------------------------------------------- descriptors

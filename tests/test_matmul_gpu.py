@@ -17,6 +17,19 @@ pytestmark = pytest.mark.gpu
 F = np.float32
 
 
+@pytest.fixture(autouse=True, params=["auto", "single", "pair"])
+def cta_group(request, monkeypatch):
+    """Every test runs with the library's own choice of kernel shape, with single-CTA tiles forced and with
+    CTA-pair (cta_group::2) tiles forced: all three must give identical results."""
+    if request.param == "single":
+        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "1")
+    elif request.param == "pair":
+        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "2")
+    else:
+        monkeypatch.delenv("W8A8_GEMM_CTA_GROUP", raising=False)
+    return request.param
+
+
 def _i8(rng, shape):
     return torch.from_numpy(rng.integers(-127, 128, shape).astype(np.int8)).cuda()
 
