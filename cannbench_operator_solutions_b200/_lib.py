@@ -12,7 +12,8 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libw8a8ffn.so")
 
 OK = 0
-ERR_INVALID, ERR_ALIGN, ERR_GROUP_LIST, ERR_WORKSPACE, ERR_CUDA, ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
+ERR_INVALID, ERR_ALIGN, ERR_GROUP_LIST, ERR_WORKSPACE, ERR_CUDA, ERR_UNSUPPORTED, ERR_LIMIT = -1, -2, -3, -4, -5, -6, -7
+STATIC_SCRATCH_BYTES = (8 << 20) + (64 << 10)
 DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
 F_ROUND_DIRECT = 1
 F_STAGE_MATMUL, F_STAGE_REQUANT = 2, 4
@@ -41,6 +42,8 @@ SIGNATURES = {
     "w8a8_grouped_matmul_swiglu_quant_workspace_size": (_sz, [_i64, _i64, _i64, _i64]),
     "w8a8_grouped_matmul_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32,
                                                 _i32, _i32, _vp, _sz, _vp]),
+    "w8a8_grouped_matmul_swiglu_quant_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32,
+                                                       _i32, _i32, _vp]),
     "w8a8_grouped_matmul_workspace_size": (_sz, [_i64, _i64, _i64, _i64]),
     "w8a8_grouped_matmul": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32,
                                    _i32, _vp, _sz, _vp]),

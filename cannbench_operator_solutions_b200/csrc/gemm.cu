@@ -692,3 +692,46 @@ extern "C" int w8a8_workspace_error(const void* workspace, void* stream)
     }
     return h.error;
 }
+
+// ===========================================================================
+// grouped_matmul_swiglu_quant without a caller workspace
+// ===========================================================================
+// Scratch for w8a8_grouped_matmul_swiglu_quant_static: lives in the library's
+// device image, so every GPU that loads the library sets these bytes aside
+// until the process exits.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is never a device address by itself.
+static __device__ __align__(256) unsigned char g_gmsq_static_scratch[W8A8_STATIC_SCRATCH_BYTES];
+
+extern "C" int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const int8_t* w, const float* w_scale,
+                                                       const float* x_scale, int8_t* y, float* y_scale, int64_t M,
+                                                       int64_t K, int64_t N, int64_t E, const int64_t* group_list,
+                                                       int list_on_device, int w_layout, int flags, void* stream)
+{
+    if (M < 0 || K <= 0 || N <= 0 || E <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    // the built-in scratch is fixed: refuse anything whose workspace would not fit
+    const size_t need = w8a8_grouped_matmul_swiglu_quant_workspace_size(M, K, N, E);
+    if (need == 0 || need > static_cast<size_t>(W8A8_STATIC_SCRATCH_BYTES)) {
+        return W8A8_ERR_LIMIT;
+    }
+    // One address lookup per device, made with that device current.  Racing first calls store the same value.
+    static void* scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        return W8A8_ERR_CUDA;
+    }
+    void* scratch = scratch_of_device[dev];
+    if (scratch == nullptr) {
+        if (cudaGetSymbolAddress(&scratch, g_gmsq_static_scratch) != cudaSuccess || scratch == nullptr) {
+            return W8A8_ERR_CUDA;
+        }
+        scratch_of_device[dev] = scratch;
+    }
+    // From here on this is the ordinary operator with the built-in bytes as its workspace.  That path rewrites
+    // the header and tile table and zeroes the row maxima on the stream before it uses them, so whatever the
+    // previous call left behind is never read.
+    return w8a8_grouped_matmul_swiglu_quant(x, w, w_scale, x_scale, y, y_scale, M, K, N, E, group_list, list_on_device,
+                                            w_layout, flags, scratch, static_cast<size_t>(W8A8_STATIC_SCRATCH_BYTES),
+                                            stream);
+}

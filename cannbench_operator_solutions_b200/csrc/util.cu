@@ -42,6 +42,8 @@ extern "C" const char* w8a8_status_string(int status)
         return "CUDA runtime or driver call failed";
     case W8A8_ERR_UNSUPPORTED:
         return "configuration not supported by this build";
+    case W8A8_ERR_LIMIT:
+        return "problem exceeds the fixed capacity of this entry point (see W8A8_STATIC_SCRATCH_BYTES)";
     default:
         return "unknown status";
     }

@@ -41,6 +41,7 @@ extern "C" {
 #define W8A8_ERR_WORKSPACE (-4)   /* workspace missing or too small                   */
 #define W8A8_ERR_CUDA (-5)        /* a CUDA runtime / driver call failed              */
 #define W8A8_ERR_UNSUPPORTED (-6) /* valid in the reference, not implemented here     */
+#define W8A8_ERR_LIMIT (-7)       /* problem larger than a fixed built-in capacity     */
 
 #define W8A8_DT_F16 0
 #define W8A8_DT_BF16 1
@@ -153,6 +154,43 @@ int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w, const flo
                                      int64_t K, int64_t N, int64_t E, const int64_t* group_list,
                                      int list_on_device, int w_layout, int flags, void* workspace,
                                      size_t workspace_bytes, void* stream);
+
+/*
+ * GroupedMatmulSwigluQuant for callers that cannot hand the library a workspace.
+ * (No counterpart in the reference: its plugin always allocates the matmul
+ * intermediate itself.)
+ *
+ * Some callers have no way to obtain device memory at the point where they run
+ * the operator: code inside a region being captured into a CUDA graph (an
+ * allocation there is an error), a serving loop whose memory was handed out
+ * once at start-up and whose latency budget cannot absorb the device-wide
+ * synchronisation an allocation may cause, or a host that embeds the library
+ * behind an interface with no allocator to call back into.  For them this entry
+ * point does the same work as w8a8_grouped_matmul_swiglu_quant with the same
+ * arguments minus the workspace, using W8A8_STATIC_SCRATCH_BYTES of device
+ * memory that are part of the library image.  It calls no allocation routine.
+ *
+ * Limit: w8a8_grouped_matmul_swiglu_quant_workspace_size(M, K, N, E) must not
+ * exceed W8A8_STATIC_SCRATCH_BYTES (for example 1024 rows at N = 4096, or 2048
+ * rows at N = 2048, with up to a few hundred experts); larger problems return
+ * W8A8_ERR_LIMIT and do nothing.  Every GPU that loads the library holds those
+ * bytes until the process exits.
+ *
+ * The first call on each device looks up the address of the built-in memory
+ * (cudaGetSymbolAddress, with that device current).  Make that first call
+ * outside any stream capture.
+ *
+ * All calls on a device share the one scratch area.  A call overwrites what the
+ * previous one left and clears what it needs cleared, so back-to-back calls on
+ * one stream are fine; two calls whose kernels can overlap on the GPU (different
+ * streams without an ordering between them, or several host threads) race on it
+ * and give wrong results.  Use the workspace variant for concurrent calls.
+ */
+#define W8A8_STATIC_SCRATCH_BYTES ((8 << 20) + (64 << 10))
+int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const int8_t* w, const float* w_scale,
+                                            const float* x_scale, int8_t* y, float* y_scale, int64_t M,
+                                            int64_t K, int64_t N, int64_t E, const int64_t* group_list,
+                                            int list_on_device, int w_layout, int flags, void* stream);
 
 /*
  * GroupedMatmul: y[rows_g] = x[rows_g] @ w[g] (+ bias[g]).
