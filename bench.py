@@ -10,6 +10,7 @@ shaped like the configuration BASELINE.json quotes its metric on.  Workloads:
     ardq   add_rms_norm_dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
     dq     dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
     qmm    quant_matmul, M=8192 K=7168 N=18432 (int8 TOPS)
+    chain  the full expert-parallel MoE FFN chain, T=65536 tokens (tokens/s; the all-to-all workload for N > 1)
 
 Rank 0 prints ONE JSON line.  `value` is the device-timed throughput with
 inputs resident in HBM; `e2e` is the same metric through the operator call
@@ -401,7 +402,94 @@ class QmmWorkload(Workload):
             2.0 * m * self.K * n / 1e12, f"M={m}, N={n} slice of the M=8192, N=18432 problem"
 
 
-WORKLOADS = {"gmsq": GmsqWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload}
+class ChainWorkload(Workload):
+    """BASELINE configs[4]: the full W8A8 MoE FFN chain, expert-parallel.  T=65536 tokens, hidden 7168, E=256,
+    top-8 of softmax(N(0,1) logits), inter 2048: add_rms_norm_dynamic_quant -> all-to-all dispatch (int8 rows +
+    fp32 scales) -> grouped_matmul_swiglu_quant -> grouped_matmul int8 down projection -> all-to-all combine ->
+    weighted sum.  Rank r owns T/N tokens and experts [r*E/N, (r+1)*E/N)."""
+    name, metric, unit, dtype, bound = "moe_ffn_chain", "moe_ffn_chain_tokens_per_s", "tokens/s", "int8", "tensor"
+    T, HID, INTER, E, TOPK = 65536, 7168, 2048, 256, 8
+    kernels_per_step = 16
+
+    def __init__(self, small=False):
+        if small:
+            self.T = 8192
+
+    def config(self, world):
+        return {"workload": f"configs[4]: W8A8 MoE FFN chain T={self.T} hidden={self.HID} inter={self.INTER} "
+                            f"E={self.E} top-{self.TOPK}", "tokens_per_gpu": self.T // world,
+                "experts_per_gpu": self.E // world, "l2": "weights (11.3 GB) and activations larger than L2",
+                "parallelism": f"ep{world} (NCCL all-to-all dispatch/combine)" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        from cannbench_operator_solutions_b200.ep import ExpertShard, MoeFfnChain
+        self.torch = torch
+        self.world = world
+        t_local, e_local = self.T // world, self.E // world
+        g = torch.Generator(device="cuda").manual_seed(300 + rank)
+        self.x = torch.randn((t_local, self.HID), generator=g, device="cuda").to(torch.bfloat16)
+        self.res = torch.randn((t_local, self.HID), generator=g, device="cuda").to(torch.bfloat16)
+        self.gamma = (1 + 0.1 * torch.randn((self.HID,), generator=g, device="cuda")).to(torch.bfloat16)
+        logits = torch.randn((t_local, self.E), generator=g, device="cuda")
+        probs = torch.softmax(logits, dim=-1)
+        top_p, top_i = torch.topk(probs, self.TOPK, dim=-1)
+        self.probs = top_p.contiguous()
+        self.idx = top_i.to(torch.int32).contiguous()
+        shard = ExpertShard(
+            torch.randint(-127, 128, (e_local, self.HID, 2 * self.INTER), generator=g, device="cuda",
+                          dtype=torch.int8),
+            torch.empty((e_local, 2 * self.INTER), device="cuda").uniform_(1e-3, 1e-2, generator=g),
+            torch.randint(-127, 128, (e_local, self.INTER, self.HID), generator=g, device="cuda", dtype=torch.int8),
+            torch.empty((e_local, self.HID), device="cuda").uniform_(1e-3, 1e-2, generator=g))
+        self.chain = MoeFfnChain(self.E, shard)
+        self.scaling = "strong"
+
+    def gpu_step(self):
+        return self.chain.forward(self.x, self.res, self.gamma, 1e-6, self.idx, self.probs)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def units_per_step(self):
+        return float(self.T // self.world)  # tokens of this rank; summed over ranks by the caller
+
+    def roofline_units(self):
+        # tensor work of this rank's share in TOPS terms: up + down projection, top-k expanded rows
+        rows = (self.T // self.world) * self.TOPK
+        return 2.0 * rows * (self.HID * 2 * self.INTER + self.INTER * self.HID) / 1e12
+
+    def host_inputs(self):
+        return [self.x.cpu().pin_memory(), self.res.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        res = host[1].to("cuda", non_blocking=True)
+        out, x_out = self.chain.forward(x, res, self.gamma, 1e-6, self.idx, self.probs)
+        outs = [out.to("cpu", non_blocking=True), x_out.to("cpu", non_blocking=True)]
+        return (host[0].numel() * 2 * 2, sum(o.numel() * o.element_size() for o in outs))
+
+    def cpu_sample(self, O):
+        """The chain's two matmuls on 8 tokens' expanded rows (64 rows over 4 experts)."""
+        e, rows_per = 4, 16
+        rng = np.random.default_rng(0)
+        m = e * rows_per
+        x = rng.integers(-127, 128, (m, self.HID)).astype(np.int8)
+        wu = rng.integers(-127, 128, (e, self.HID, 2 * self.INTER)).astype(np.int8)
+        su = rng.uniform(1e-3, 1e-2, (e, 2 * self.INTER)).astype(np.float32)
+        wd = rng.integers(-127, 128, (e, self.INTER, self.HID)).astype(np.int8)
+        sd = rng.uniform(1e-3, 1e-2, (e, self.HID)).astype(np.float32)
+        xs = rng.uniform(1e-3, 5e-2, m).astype(np.float32)
+        gl = [rows_per * (i + 1) for i in range(e)]
+
+        def run():
+            h, hs = O.grouped_matmul_swiglu_quant(x, wu, su, xs, gl)
+            O.grouped_matmul(h, wd, gl, dtype=O.DT_I8, x_scale=hs, w_scale=sd)
+        return run, m / self.TOPK, f"the two grouped matmuls of {m // self.TOPK} tokens ({m} expanded rows, {e} experts)"
+
+
+WORKLOADS = {"gmsq": GmsqWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
+             "chain": ChainWorkload}
 
 
 # --------------------------------------------------------------------------
@@ -464,7 +552,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
-    wl = WORKLOADS[args.workload](small=True) if (args.workload == "gmsq" and args.small) else WORKLOADS[args.workload]()
+    wl = (WORKLOADS[args.workload](small=True) if (args.workload in ("gmsq", "chain") and args.small)
+          else WORKLOADS[args.workload]())
     if args.workload == "qmm":
         wl.M = args.qmm_m
     wl.layout_nk = (args.layout == "nk")
@@ -567,7 +656,7 @@ def main():
         else:
             peak, punit = peaks["bf16_tflops"] * INT8_PER_BF16, "TOPS"
             peak_note = f"2 x {peaks['source']} cuBLAS bf16 burst (int8 MMA rate is twice bf16's); nominal dense int8 is 4500"
-        achieved = wl.roofline_units() / (ms_kernel * 1e-3)
+        achieved = wl.roofline_units() / (ms_kernel * 1e-3)  # TOPS or GB/s of the rank-0 share
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,

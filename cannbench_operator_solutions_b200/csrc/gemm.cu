@@ -183,45 +183,77 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
                                                           TileEntry* tiles, int64_t max_tiles, int tile_m)
 {
     extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
+    __shared__ int32_t s_warp_sum[8];
     __shared__ int s_bad;
+    __shared__ int32_t s_carry;
     auto end_of = [&](int64_t g) -> int64_t {
         return use_by_value ? static_cast<int64_t>(by_value.ends[g]) : dev_list[g];
     };
-    if (threadIdx.x == 0) {
-        int bad = 0;
-        int64_t prev = 0;
-        int64_t run = 0;
-        for (int64_t g = 0; g < E; ++g) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    if (tid == 0) {
+        s_bad = 0;
+        s_carry = 0;
+    }
+    __syncthreads();
+    // groups in chunks of 256: validate, count tiles, block-wide exclusive scan
+    for (int64_t base = 0; base < E; base += 256) {
+        const int64_t g = base + tid;
+        int32_t cnt = 0;
+        if (g < E) {
+            const int64_t prev = (g == 0) ? 0 : end_of(g - 1);
             const int64_t e = end_of(g);
-            if (e < prev || e > M) {
-                bad = 1;
-                break;
+            if (e < prev || e > M || (g == E - 1 && e != M)) {
+                s_bad = 1;
+            } else {
+                cnt = static_cast<int32_t>((static_cast<uint32_t>(e - prev) + tile_m - 1) / static_cast<uint32_t>(tile_m));
             }
-            s_first[g] = static_cast<int32_t>(run);
-            run += (e - prev + tile_m - 1) / tile_m;
-            prev = e;
         }
-        if (!bad && prev != M) {
-            bad = 1;
+        int32_t incl = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) {
+                incl += v;
+            }
         }
-        if (!bad && run > max_tiles) {
-            bad = 1;
+        if (lane == 31) {
+            s_warp_sum[wid] = incl;
         }
-        s_first[E] = static_cast<int32_t>(run);
-        s_bad = bad;
-        header->num_m_tiles = bad ? 0 : static_cast<int32_t>(run);
+        __syncthreads();
+        int32_t warp_off = 0;
+        for (int w = 0; w < wid; ++w) {
+            warp_off += s_warp_sum[w];
+        }
+        const int32_t carry = s_carry;
+        if (g < E) {
+            s_first[g] = carry + warp_off + incl - cnt;
+        }
+        __syncthreads();
+        if (tid == 255) {
+            s_carry = carry + warp_off + incl;
+        }
+        __syncthreads();
+    }
+    const int32_t total = s_carry;
+    const int bad = (s_bad != 0 || total > max_tiles) ? 1 : 0;
+    if (tid == 0) {
+        s_first[E] = total;
+        header->num_m_tiles = bad ? 0 : total;
         header->error = bad;
     }
     __syncthreads();
-    if (s_bad) {
+    if (bad) {
         return;
     }
-    for (int64_t g = 0; g < E; ++g) {
+    // one warp per group at a time fills that group's tile entries
+    for (int64_t g = wid; g < E; g += 8) {
         const int64_t start = (g == 0) ? 0 : end_of(g - 1);
         const int64_t rows = end_of(g) - start;
         const int32_t first = s_first[g];
         const int32_t cnt = s_first[g + 1] - first;
-        for (int32_t t = threadIdx.x; t < cnt; t += blockDim.x) {
+        for (int32_t t = lane; t < cnt; t += 32) {
             TileEntry te;
             te.group = static_cast<int32_t>(g);
             te.m_start = static_cast<int32_t>(start + static_cast<int64_t>(t) * tile_m);
