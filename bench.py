@@ -141,6 +141,8 @@ class ArdqWorkload(Workload):
     name, metric, unit, dtype, bound = "add_rms_norm_dynamic_quant", "rmsnorm_quant_hbm_gbs", "GB/s", "f32", "hbm"
     rows, n = 8192, 7168
     kernels_per_step = 1
+    traffic = 363.5e6  # dram__bytes_read.sum + dram__bytes_write.sum of one launch
+    traffic_source = "profiles/ardq_rows_kernel_cfg2.md"
 
     def config(self, world):
         return {"workload": "configs[1]: add_rms_norm_dynamic_quant [8192,7168] bf16, eps=1e-6",
@@ -205,6 +207,8 @@ class ArdqWorkload(Workload):
 
 class DqWorkload(ArdqWorkload):
     name, metric = "dynamic_quant", "dynamic_quant_hbm_gbs"
+    traffic = 137.7e6
+    traffic_source = "profiles/dq_rows_kernel_cfg2.md"
 
     def config(self, world):
         c = super().config(world)
@@ -246,6 +250,8 @@ class GmsqWorkload(Workload):
     name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "int8",
                                         "tensor")
     E, M, K, N = 256, 131072, 7168, 4096
+    traffic = 10.66e9  # E=32 / 16384-row capture (1.333 GB per launch) scaled by 8 in rows and experts
+    traffic_source = "profiles/gemm_tc_kernel_gmsq_e32.md"
 
     def __init__(self, small=False):
         if small:  # a slice of the configuration small enough for a profiler capture
@@ -419,7 +425,8 @@ class ChainWorkload(Workload):
         return {"workload": f"configs[4]: W8A8 MoE FFN chain T={self.T} hidden={self.HID} inter={self.INTER} "
                             f"E={self.E} top-{self.TOPK}", "tokens_per_gpu": self.T // world,
                 "experts_per_gpu": self.E // world, "l2": "weights (11.3 GB) and activations larger than L2",
-                "parallelism": f"ep{world} (NCCL all-to-all dispatch/combine)" if world > 1 else "single GPU"}
+                "parallelism": (f"ep{world} ({getattr(self, 'transport', 'p2p')} dispatch/combine)" if world > 1
+                                else "single GPU")}
 
     def gpu_setup(self, torch, rank, world):
         import cannbench_operator_solutions_b200 as pkg
@@ -442,7 +449,7 @@ class ChainWorkload(Workload):
             torch.empty((e_local, 2 * self.INTER), device="cuda").uniform_(1e-3, 1e-2, generator=g),
             torch.randint(-127, 128, (e_local, self.INTER, self.HID), generator=g, device="cuda", dtype=torch.int8),
             torch.empty((e_local, self.HID), device="cuda").uniform_(1e-3, 1e-2, generator=g))
-        self.chain = MoeFfnChain(self.E, shard)
+        self.chain = MoeFfnChain(self.E, shard, transport=getattr(self, "transport", "p2p"))
         self.scaling = "strong"
 
     def gpu_step(self):
@@ -547,6 +554,10 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced grouped workload (for profiling captures)")
     ap.add_argument("--qmm-m", type=int, default=8192, help="rows of the dense quant_matmul workload")
     ap.add_argument("--layout", choices=["kn", "nk"], default="kn", help="weight layout of the matmul workloads")
+    ap.add_argument("--transport", choices=["p2p", "nccl"], default="p2p",
+                    help="chain workload: fused peer-memory stores or NCCL all-to-all for dispatch / combine")
+    ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
+                    help="time the K steps as one CUDA-graph replay (auto: the bandwidth-bound workloads)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -557,6 +568,7 @@ def main():
     if args.workload == "qmm":
         wl.M = args.qmm_m
     wl.layout_nk = (args.layout == "nk")
+    wl.transport = args.transport
     if args.impl == "reference":
         run_reference(args, wl)
         return
@@ -596,12 +608,27 @@ def main():
             torch.cuda.synchronize()
 
     # ---- device-resident, whole step (timed K steps in the middle of a sustained-load window) ----
+    # The bandwidth-bound operators run for tens of microseconds, comparable to a launch gap, so their K steps are
+    # captured once into a CUDA graph (K calls through the C-ABI) and the replay is what is timed.
+    use_graph = (args.graph == "on") or (args.graph == "auto" and wl.bound == "hbm")
+    graph = None
+    if use_graph:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.steps):
+                wl.gpu_step()
+        graph.replay()
+        torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     hold(0.6)
     barrier()
     ev0.record()
-    for _ in range(args.steps):
-        wl.gpu_step()
+    if graph is not None:
+        graph.replay()
+    else:
+        for _ in range(args.steps):
+            wl.gpu_step()
     ev1.record()
     barrier()
     ms_total = ev0.elapsed_time(ev1)
@@ -613,8 +640,11 @@ def main():
     torch.cuda.synchronize()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record()
-    for _ in range(args.steps):
-        wl.kernel_step()
+    if graph is not None:
+        graph.replay()  # for these workloads the step is the kernel
+    else:
+        for _ in range(args.steps):
+            wl.kernel_step()
     k1.record()
     torch.cuda.synchronize()
     ms_kernel = k0.elapsed_time(k1) / args.steps
@@ -664,7 +694,9 @@ def main():
             "config": wl.config(world), "clocks": clocks,
             "gpu_launches": wl.kernels_per_step * args.steps,
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": punit,
-                         "frac": achieved / peak, "traffic": None, "kernel_ms": ms_kernel, "peak_source": peak_note},
+                         "frac": achieved / peak, "traffic": getattr(wl, "traffic", None),
+                         "traffic_source": getattr(wl, "traffic_source", None), "kernel_ms": ms_kernel,
+                         "peak_source": peak_note},
         }
         if e2e_ms is not None:
             line["e2e"] = {"value": total_units / (e2e_ms * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": int(h2d),

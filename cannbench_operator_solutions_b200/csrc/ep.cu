@@ -158,6 +158,88 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint8_t* __rest
     }
 }
 
+// Fused dispatch: the quantised row of token i is written straight to the row it will occupy in the
+// expert-major buffer of the rank that owns expert idx[i, k] -- a plain store, over NVLink when that rank is a
+// peer.  row_dst[e] / scale_dst[e] point at the first row / scale this rank may write for expert e in the
+// owner's buffer, my_base[e] is the position of this rank's first pair for expert e in its own expert-major
+// order, pos[i, k] that pair's position: destination row = row_dst[e] + (pos - my_base[e]) rows.
+// This replaces pack + all-to-all + regroup with one pass; the row is read once and stored topk times.
+template <bool VEC>
+__global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __restrict__ src,
+                                                            const float* __restrict__ src_scale,
+                                                            const int32_t* __restrict__ expert_idx,
+                                                            const int64_t* __restrict__ pos,
+                                                            const uint64_t* __restrict__ row_dst,
+                                                            const uint64_t* __restrict__ scale_dst,
+                                                            const int64_t* __restrict__ my_base, int64_t T, int topk,
+                                                            int64_t row_bytes)
+{
+    __shared__ uint64_t s_dst[64];
+    for (int64_t i = blockIdx.x; i < T; i += gridDim.x) {
+        __syncthreads();
+        if (static_cast<int>(threadIdx.x) < topk) {
+            const int64_t pr = i * topk + threadIdx.x;
+            const int32_t e = expert_idx[pr];
+            const int64_t p = pos[pr];
+            uint64_t d = 0;
+            if (p >= 0) {
+                const int64_t off = p - my_base[e];
+                d = row_dst[e] + static_cast<uint64_t>(off) * static_cast<uint64_t>(row_bytes);
+                if (src_scale != nullptr) {
+                    reinterpret_cast<float*>(scale_dst[e])[off] = src_scale[i];
+                }
+            }
+            s_dst[threadIdx.x] = d;
+        }
+        __syncthreads();
+        const uint8_t* s = src + i * row_bytes;
+        if constexpr (VEC) {
+            const int64_t n16 = row_bytes / 16;
+            for (int64_t c = threadIdx.x; c < n16; c += blockDim.x) {
+                const uint4 v = __ldcs(reinterpret_cast<const uint4*>(s) + c);
+                for (int k = 0; k < topk; ++k) {
+                    const uint64_t d = s_dst[k];
+                    if (d != 0) {
+                        reinterpret_cast<uint4*>(d)[c] = v;
+                    }
+                }
+            }
+        } else {
+            for (int64_t c = threadIdx.x; c < row_bytes; c += blockDim.x) {
+                const uint8_t v = s[c];
+                for (int k = 0; k < topk; ++k) {
+                    const uint64_t d = s_dst[k];
+                    if (d != 0) {
+                        reinterpret_cast<uint8_t*>(d)[c] = v;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// out[r] = seg_ptr[s] + (r - seg_first[s]) * row_bytes for the segment s with seg_first[s] <= r < seg_first[s+1]
+__global__ void __launch_bounds__(256) expand_row_pointers_kernel(const int64_t* __restrict__ seg_first,
+                                                                  const uint64_t* __restrict__ seg_ptr, int nseg,
+                                                                  int64_t rows, int64_t row_bytes,
+                                                                  uint64_t* __restrict__ out)
+{
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= rows) {
+        return;
+    }
+    int lo = 0, hi = nseg;  // last segment whose first row is <= r (empty segments share a first row)
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (seg_first[mid] <= r) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    out[r] = seg_ptr[lo] + static_cast<uint64_t>(r - seg_first[lo]) * static_cast<uint64_t>(row_bytes);
+}
+
 // One CTA per token; each thread owns 8-element chunks of the hidden row.
 template <int DT, bool VEC>
 __global__ void __launch_bounds__(256) combine_kernel(const uint16_t* __restrict__ rows,
@@ -307,6 +389,56 @@ extern "C" int w8a8_permute_rows(const void* src, const float* src_scale, void* 
                                                               static_cast<uint8_t*>(dst), dst_scale, index, rows,
                                                               row_bytes);
     }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_dispatch_rows(const void* src, const float* src_scale, const int32_t* expert_idx,
+                                  const int64_t* expanded_pos, const uint64_t* row_dst, const uint64_t* scale_dst,
+                                  const int64_t* my_base, int64_t T, int64_t topk, int64_t row_bytes, void* stream)
+{
+    if (T < 0 || topk <= 0 || topk > 64 || row_bytes <= 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (T == 0) {
+        return W8A8_OK;
+    }
+    if (src == nullptr || expert_idx == nullptr || expanded_pos == nullptr || row_dst == nullptr ||
+        my_base == nullptr || (src_scale != nullptr && scale_dst == nullptr)) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // destination rows are row_bytes apart from 16-byte aligned bases when the sources are
+    const bool vec = (row_bytes % 16 == 0) && w8a8::is_aligned(src, 16);
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(T < cap ? T : cap);
+    if (vec) {
+        w8a8::dispatch_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale, expert_idx,
+                                                              expanded_pos, row_dst, scale_dst, my_base, T,
+                                                              static_cast<int>(topk), row_bytes);
+    } else {
+        w8a8::dispatch_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
+                                                               expert_idx, expanded_pos, row_dst, scale_dst, my_base,
+                                                               T, static_cast<int>(topk), row_bytes);
+    }
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_expand_row_pointers(const int64_t* seg_first, const uint64_t* seg_ptr, int64_t nseg, int64_t rows,
+                                        int64_t row_bytes, uint64_t* out, void* stream)
+{
+    if (nseg <= 0 || rows < 0 || row_bytes <= 0 || nseg >= (int64_t(1) << 30)) {
+        return W8A8_ERR_INVALID;
+    }
+    if (rows == 0) {
+        return W8A8_OK;
+    }
+    if (seg_first == nullptr || seg_ptr == nullptr || out == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>((rows + 255) / 256);
+    w8a8::expand_row_pointers_kernel<<<grid, 256, 0, st>>>(seg_first, seg_ptr, static_cast<int>(nseg), rows, row_bytes,
+                                                           out);
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 

@@ -611,10 +611,10 @@ extern "C" size_t w8a8_grouped_matmul_workspace_size(int64_t M, int64_t N, int64
     return carve_workspace(nullptr, M, E, 0).total;
 }
 
-extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y, const float* x_scale,
-                                   const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
-                                   const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
-                                   int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream)
+static int grouped_matmul_impl(const void* x, const void* w, const void* bias, void* y, const uint64_t* out_row_ptrs,
+                               const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
+                               const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
+                               int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream)
 {
     if (M < 0 || K <= 0 || N <= 0 || E <= 0) {
         return W8A8_ERR_INVALID;
@@ -647,14 +647,14 @@ extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bia
     if (M == 0) {
         return W8A8_OK;
     }
-    if (x == nullptr || w == nullptr || y == nullptr || group_list == nullptr) {
+    if (x == nullptr || w == nullptr || (y == nullptr && out_row_ptrs == nullptr) || group_list == nullptr) {
         return W8A8_ERR_INVALID;
     }
     const int elem = (kind == KIND_I8) ? 1 : 2;
     if ((K * elem) % 16 != 0 || (N * elem) % 16 != 0 || (N % 8) != 0) {
         return W8A8_ERR_UNSUPPORTED;
     }
-    if (!is_aligned(x, 16) || !is_aligned(w, 16) || !is_aligned(y, 16)) {
+    if (!is_aligned(x, 16) || !is_aligned(w, 16) || (y != nullptr && !is_aligned(y, 16))) {
         return W8A8_ERR_ALIGN;
     }
     if (M >= (int64_t(1) << 31) - 256 || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) {
@@ -693,6 +693,7 @@ extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bia
     p.row_scale = x_scale;
     p.bias = bias;
     p.out = y;
+    p.out_row_ptrs = out_row_ptrs;
     p.flags = (bias != nullptr ? 4 : 0) | (bias_dtype & 3);
     p.out_dtype = out_dtype;
     const int block_n = 256;
@@ -707,6 +708,29 @@ extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bia
         e = dispatch_gemm<KIND_BF16, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
     }
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y, const float* x_scale,
+                                   const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
+                                   const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
+                                   int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream)
+{
+    return grouped_matmul_impl(x, w, bias, y, nullptr, x_scale, w_scale, M, N, K, E, group_list, list_on_device, dtype,
+                               bias_dtype, out_dtype, w_layout, workspace, workspace_bytes, stream);
+}
+
+extern "C" int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const void* bias,
+                                           const uint64_t* out_row_ptrs, const float* x_scale, const float* w_scale,
+                                           int64_t M, int64_t N, int64_t K, int64_t E, const int64_t* group_list,
+                                           int list_on_device, int dtype, int bias_dtype, int out_dtype, int w_layout,
+                                           void* workspace, size_t workspace_bytes, void* stream)
+{
+    if (out_row_ptrs == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    return grouped_matmul_impl(x, w, bias, nullptr, out_row_ptrs, x_scale, w_scale, M, N, K, E, group_list,
+                               list_on_device, dtype, bias_dtype, out_dtype, w_layout, workspace, workspace_bytes,
+                               stream);
 }
 
 extern "C" int w8a8_workspace_error(const void* workspace, void* stream)

@@ -90,6 +90,7 @@ struct GemmParams {
     int64_t flags;  // QMM flag word; GMM: bias dtype in bits 0-1, bit 2 = has bias
     int32_t out_dtype;
     int64_t bias_batch_stride;
+    const uint64_t* out_row_ptrs;  // GMM: when set, row r is stored at this address instead of out + r*N
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
     int32_t debug;    // experiments only, bit mask: 1 = no MMA, 2 = no TMA, 4 = no epilogue work
@@ -382,6 +383,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
                 }
                 // 32 outputs -> four 16-byte stores of 16-bit values
                 uint16_t* dst = static_cast<uint16_t*>(p.out) + row * p.N + col0;
+                if constexpr (EPI == EPI_GMM) {
+                    if (p.out_row_ptrs != nullptr) {
+                        // the row's home may be another GPU's memory: plain peer stores over NVLink
+                        dst = reinterpret_cast<uint16_t*>(p.out_row_ptrs[row]) + col0;
+                    }
+                }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     if (q * 8 < valid) {

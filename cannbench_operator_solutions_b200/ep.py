@@ -11,6 +11,16 @@ One process per GPU; rank r owns experts [r*E/P, (r+1)*E/P) and T/P tokens.
     inverse regroup, all-to-all back                (combine transport)
     weighted sum over the top-k copies              (MoeFinalizeRouting's arithmetic)
 
+Two transports for the two exchanges:
+
+    "nccl"  pack -> all_to_all_single -> regroup kernel on the way in; un-permute kernel -> all_to_all_single on
+            the way back.  Works on any backend (gloo in the CPU tests).
+    "p2p"   the exchanges are fused into the kernels on either side of them: the dispatch kernel stores every
+            quantised row directly at its final expert-major position in the owning rank's buffer, and the down
+            projection's epilogue stores every output row directly where its home rank's combine reads it.  The
+            stores are plain peer stores over NVLink into symmetric buffers (torch symmetric memory supplies the
+            peer pointers); the only collectives left are the small count all-gather and two stream barriers.
+
 The compute steps go through a backend object: `CudaBackend` (the product:
 libw8a8ffn.so through the C-ABI) or, in the CPU tests of this host logic, a
 backend the test supplies.  The collectives are `all_to_all_single` on the
@@ -125,6 +135,36 @@ class CudaBackend:
     def grouped_matmul_int8(self, x, w, group_list, x_scale, w_scale):
         return self.ops.grouped_matmul(x, w, group_list, None, 3, False, x_scale=x_scale, weight_scale=w_scale)[0]
 
+    def dispatch_rows(self, src, src_scale, expert_idx, pos, row_dst, scale_dst, my_base):
+        t, topk = pos.shape
+        rc = self.lib.w8a8_dispatch_rows(src.data_ptr(), src_scale.data_ptr(), expert_idx.data_ptr(), pos.data_ptr(),
+                                         row_dst.data_ptr(), scale_dst.data_ptr(), my_base.data_ptr(), t, topk,
+                                         src.shape[1] * src.element_size(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"dispatch_rows: {self.L.status_string(rc)}")
+
+    def expand_row_pointers(self, seg_first, seg_ptr, rows, row_bytes):
+        out = torch.empty((max(rows, 1),), dtype=torch.int64, device=seg_first.device)
+        rc = self.lib.w8a8_expand_row_pointers(seg_first.data_ptr(), seg_ptr.data_ptr(), seg_ptr.numel(), rows,
+                                               row_bytes, out.data_ptr(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"expand_row_pointers: {self.L.status_string(rc)}")
+        return out
+
+    def grouped_matmul_int8_to_rows(self, x, w, group_list, x_scale, w_scale, out_row_ptrs, out_dtype):
+        m, k = x.shape
+        e, _, n = w.shape
+        lib, L = self.lib, self.L
+        need = lib.w8a8_grouped_matmul_workspace_size(m, n, k, e)
+        ws = torch.empty((max(need, 1),), dtype=torch.uint8, device=x.device)
+        gl = torch.tensor([int(v) for v in group_list], dtype=torch.int64)
+        code = L.DT_BF16 if out_dtype == torch.bfloat16 else L.DT_F16
+        rc = lib.w8a8_grouped_matmul_to_rows(x.data_ptr(), w.data_ptr(), None, out_row_ptrs.data_ptr(),
+                                             x_scale.data_ptr(), w_scale.data_ptr(), m, n, k, e, gl.data_ptr(), 0,
+                                             L.DT_I8, L.DT_F32, code, L.W_KN, ws.data_ptr(), need, self._st())
+        if rc != 0:
+            raise RuntimeError(f"grouped_matmul_to_rows: {L.status_string(rc)}")
+
     def combine(self, rows, probs, pos):
         t, topk = probs.shape
         out = torch.empty((t, rows.shape[1]), dtype=rows.dtype, device=rows.device)
@@ -146,9 +186,47 @@ class ExpertShard:
     s_down: torch.Tensor
 
 
+def _align(v: int, a: int = 256) -> int:
+    return (v + a - 1) // a * a
+
+
+class PeerBuffers:
+    """One symmetric allocation per rank holding the expert-major receive buffer (int8 rows + fp32 scales) and
+    the combine receive buffer (16-bit rows), plus every rank's pointer to it."""
+
+    def __init__(self, cap_rows: int, hidden: int, home_rows: int, device, world: int, group):
+        self.cap_rows, self.hidden, self.home_rows = cap_rows, hidden, home_rows
+        self.off_x = 0
+        self.off_s = _align(cap_rows * hidden)
+        self.off_back = self.off_s + _align(cap_rows * 4)
+        total = self.off_back + _align(home_rows * hidden * 2)
+        if world == 1:
+            self.buf = torch.empty((total,), dtype=torch.uint8, device=device)
+            self.ptrs = [self.buf.data_ptr()]
+        else:
+            import os
+
+            import torch.distributed._symmetric_memory as symm_mem
+
+            # plain peer loads / stores only: no NVLink multicast object is bound to these buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            self.buf = symm_mem.empty((total,), dtype=torch.uint8, device=device)
+            name = group.group_name if group is not None else dist.group.WORLD.group_name
+            self.handle = symm_mem.rendezvous(self.buf, name)
+            self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.xe = self.buf[self.off_x:self.off_x + cap_rows * hidden].view(torch.int8).view(cap_rows, hidden)
+        self.xs = self.buf[self.off_s:self.off_s + cap_rows * 4].view(torch.float32)
+
+
 class MoeFfnChain:
-    def __init__(self, num_experts: int, shard: ExpertShard, backend=None, group=None):
+    def __init__(self, num_experts: int, shard: ExpertShard, backend=None, group=None, transport: str = "nccl",
+                 capacity_rows: Optional[int] = None):
         self.group = group
+        if transport not in ("nccl", "p2p"):
+            raise ValueError("transport must be 'nccl' or 'p2p'")
+        self.transport = transport
+        self.capacity_rows = capacity_rows
+        self.peer: Optional[PeerBuffers] = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if num_experts % self.world != 0:
@@ -180,10 +258,87 @@ class MoeFfnChain:
         return recv.cpu().numpy()
 
     # -- the chain ----------------------------------------------------------
+    def _barrier(self, device) -> None:
+        """All ranks' kernels issued so far are complete, stream-ordered (no host synchronisation)."""
+        if self.world > 1:
+            token = torch.zeros((1,), dtype=torch.int32, device=device)
+            dist.all_reduce(token, group=self.group)
+
+    def _forward_p2p(self, x, residual, gamma, eps, expert_idx, probs):
+        b = self.backend
+        dev = x.device
+        t, topk = expert_idx.shape
+        hidden = x.shape[1]
+        xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)
+        count, _cumsum, pos = b.route_plan(expert_idx, self.E)
+
+        # every rank learns every rank's per-expert counts (P x E integers), then all index arithmetic is local
+        if self.world > 1:
+            gathered = torch.empty((self.world, self.E), dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(gathered, count, group=self.group)
+            C = gathered.cpu().numpy()
+        else:
+            C = count.cpu().numpy().reshape(1, self.E)
+        self.last_counts = C[:, self.rank * self.e_local:(self.rank + 1) * self.e_local]
+        col = C.sum(0)                                               # rows per expert over all ranks
+        base_of_rank = np.cumsum(C, 1) - C                            # [P, E]: rank i's own expert-major positions
+        owner = np.arange(self.E) // self.e_local
+        ex_incl = np.cumsum(col.reshape(self.world, self.e_local), 1)
+        ex_base = (ex_incl - col.reshape(self.world, self.e_local)).reshape(-1)   # expert's first row at its owner
+        before_me = C[:self.rank].sum(0)                              # rows of lower ranks inside each expert
+        rows_on = ex_incl[:, -1]                                      # rows each owner receives
+        if self.peer is None:
+            cap = self.capacity_rows
+            if cap is None:
+                # room for 1.5x a balanced share; routing more skewed than that needs an explicit capacity
+                cap = int(1.5 * t * topk) + 1024
+            self.peer = PeerBuffers(cap, hidden, t * topk, dev, self.world, self.group)
+        pb = self.peer
+        if int(rows_on.max()) > pb.cap_rows or t * topk > pb.home_rows:
+            raise RuntimeError("expert-parallel receive buffer too small for this routing: raise capacity_rows")
+
+        dst_row = ex_base + before_me
+        ptrs = np.asarray(pb.ptrs, dtype=np.uint64)
+        row_dst = ptrs[owner] + np.uint64(pb.off_x) + dst_row.astype(np.uint64) * np.uint64(hidden)
+        scale_dst = ptrs[owner] + np.uint64(pb.off_s) + dst_row.astype(np.uint64) * np.uint64(4)
+        tables = np.stack([row_dst.view(np.int64), scale_dst.view(np.int64), base_of_rank[self.rank].astype(np.int64)])
+        tables_dev = torch.from_numpy(tables).to(dev)
+
+        self._barrier(dev)   # nobody is still reading last step's buffers
+        b.dispatch_rows(xq, xs, expert_idx, pos, tables_dev[0], tables_dev[1], tables_dev[2])
+        self._barrier(dev)   # every rank's rows have landed
+
+        mine = slice(self.rank * self.e_local, (self.rank + 1) * self.e_local)
+        rows_me = int(rows_on[self.rank])
+        gl = [int(v) for v in ex_incl[self.rank]]
+        xe = pb.xe[:rows_me]
+        h, hs = b.grouped_matmul_swiglu_quant(xe, self.shard.w_up, self.shard.s_up, pb.xs[:rows_me], gl)
+
+        # one segment per (local expert, source rank): where its rows start here, and where they go home
+        cm = C[:, mine]                                               # [P, E_loc]
+        seg_len = cm.T.reshape(-1)                                    # ordered (expert, source rank)
+        seg_first = np.concatenate([[0], np.cumsum(seg_len)]).astype(np.int64)
+        home = base_of_rank[:, mine].T.reshape(-1).astype(np.uint64)  # row in the source rank's send order
+        src_rank = np.tile(np.arange(self.world), self.e_local)
+        elem = x.element_size()
+        seg_ptr = ptrs[src_rank] + np.uint64(pb.off_back) + home * np.uint64(hidden * elem)
+        seg_dev = torch.from_numpy(np.concatenate([seg_first, seg_ptr.view(np.int64)])).to(dev)
+        nseg = seg_len.size
+        out_ptrs = b.expand_row_pointers(seg_dev[:nseg + 1], seg_dev[nseg + 1:], rows_me, hidden * elem)
+        if rows_me > 0:
+            b.grouped_matmul_int8_to_rows(h, self.shard.w_down, gl, hs, self.shard.s_down, out_ptrs, x.dtype)
+        self._barrier(dev)   # every rank's output rows have landed at home
+
+        back = pb.buf[pb.off_back:pb.off_back + t * topk * hidden * elem].view(x.dtype).view(t * topk, hidden)
+        out = b.combine(back, probs, pos)
+        return out, x_out
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
                 expert_idx: torch.Tensor, probs: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """x, residual [T_local, hidden] fp16/bf16; expert_idx int32 [T_local, topk]; probs fp32 [T_local, topk].
         Returns (ffn_out [T_local, hidden], residual_out [T_local, hidden])."""
+        if self.transport == "p2p":
+            return self._forward_p2p(x, residual, gamma, eps, expert_idx, probs)
         b = self.backend
         t, topk = expert_idx.shape
         xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)

@@ -244,6 +244,37 @@ int w8a8_scatter_rows(const void* src, const float* src_scale, void* dst, float*
 int w8a8_permute_rows(const void* src, const float* src_scale, void* dst, float* dst_scale,
                       const int64_t* index, int64_t rows, int64_t row_bytes, void* stream);
 
+/*
+ * Fused dispatch (no reference counterpart: the reference is single-device).  Instead of packing rows, running
+ * an all-to-all and regrouping the result, every quantised token row is stored directly at the row it occupies in
+ * the expert-major buffer of the rank that owns its expert -- a peer pointer when that rank is another GPU
+ * (plain stores over NVLink).  Per expert e: row_dst[e] / scale_dst[e] are the addresses of the first row / scale
+ * this rank may write for e in the owner's buffers, my_base[e] the position of this rank's first (token, k) pair
+ * for e in its own expert-major order (the exclusive cumsum of w8a8_route_plan's count).  The caller synchronises
+ * the ranks before the owners read.
+ */
+int w8a8_dispatch_rows(const void* src, const float* src_scale, const int32_t* expert_idx,
+                       const int64_t* expanded_pos, const uint64_t* row_dst, const uint64_t* scale_dst,
+                       const int64_t* my_base, int64_t T, int64_t topk, int64_t row_bytes, void* stream);
+
+/* out[r] = seg_ptr[s] + (r - seg_first[s]) * row_bytes for the segment s containing row r (seg_first has
+ * nseg + 1 non-decreasing entries): turns a (source rank, expert) segment table into one destination address per
+ * row for w8a8_grouped_matmul_to_rows. */
+int w8a8_expand_row_pointers(const int64_t* seg_first, const uint64_t* seg_ptr, int64_t nseg, int64_t rows,
+                             int64_t row_bytes, uint64_t* out, void* stream);
+
+/*
+ * GroupedMatmul whose epilogue is the combine transport: identical to w8a8_grouped_matmul except that output row
+ * r is stored at out_row_ptrs[r] (N contiguous elements, 16-byte aligned), which may lie in another GPU's memory.
+ * The down projection then needs neither an un-permute pass nor an all-to-all: each row lands where its home
+ * rank's w8a8_combine will read it.
+ */
+int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const void* bias, const uint64_t* out_row_ptrs,
+                                const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K,
+                                int64_t E, const int64_t* group_list, int list_on_device, int dtype,
+                                int bias_dtype, int out_dtype, int w_layout, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* out[i, :] = sum_k probs[i, k] * rows[pos[i*topk+k], :], fp32, ascending k,
  * rounded to dtype (F16 / BF16).  A negative position contributes nothing. */
 int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,

@@ -78,3 +78,23 @@ def test_single_gpu_chain_matches_oracle_chain(ops, oracle):
     got, got_x = gpu_chain.forward(x.to(dev), res.to(dev), gamma.to(dev), 1e-6, idx.to(dev), probs.to(dev))
     assert np.array_equal(bits(got_x), bits(want_x))
     assert np.array_equal(bits(got), bits(want))
+
+
+def test_single_gpu_chain_peer_transport_equals_collective_transport(ops):
+    """The fused transport (dispatch kernel and down-projection epilogue store rows at their final positions)
+    gives the same bits as pack / all-to-all / regroup; with one rank the 'peer' buffers are this GPU's own."""
+    from test_ep_cpu import _problem
+
+    from cannbench_operator_solutions_b200.ep import ExpertShard, MoeFfnChain
+
+    experts = 16
+    x, res, gamma, idx, probs, w_up, s_up, w_dn, s_dn = _problem(seed=5, tokens=300, hidden=512, inter=256,
+                                                                 experts=experts, topk=4)
+    dev = "cuda"
+    shard = ExpertShard(w_up.to(dev), s_up.to(dev), w_dn.to(dev), s_dn.to(dev))
+    args = (x.to(dev), res.to(dev), gamma.to(dev), 1e-6, idx.to(dev), probs.to(dev))
+    a, ax = MoeFfnChain(experts, shard, transport="nccl").forward(*args)
+    chain = MoeFfnChain(experts, shard, transport="p2p")
+    for _ in range(2):  # the second pass reuses the buffers of the first
+        b, bx = chain.forward(*args)
+        assert torch.equal(a, b) and torch.equal(ax, bx)
