@@ -87,7 +87,7 @@ template <int CG, int BLOCK_N>
 constexpr size_t gemm_smem_bytes()
 {
     return static_cast<size_t>(gemm_stages(CG, BLOCK_N)) * (GEMM_A_BYTES + (BLOCK_N / CG) * GEMM_KBYTES) +
-           1024 /*alignment slack*/ + 256 /*barriers, tmem slot, abort flag*/;
+           1024 /*alignment slack*/ + 512 /*barriers, tmem slot, abort flag*/ + 8 * 4096 /*epilogue store patches*/;
 }
 
 // number of workers (CTAs, or CTA pairs) a persistent launch uses

@@ -216,7 +216,8 @@ struct TileInfo {
 // accumulator, columns [col_half * BLOCK_N/2, (col_half+1) * BLOCK_N/2).
 template <int BLOCK_N, int KIND, int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& tl, uint32_t t_addr,
-                                              int row_in_tile, int col_half, int64_t H, bool no_epilogue)
+                                              int row_in_tile, int col_half, int64_t H, bool no_epilogue,
+                                              uint4* stage)
 {
     const bool row_ok = (row_in_tile < tl.m_rows) && !no_epilogue;
     const int64_t row = static_cast<int64_t>(tl.a_row0) + row_in_tile;  // global row (A and output)
@@ -299,6 +300,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
             }
         }
         constexpr int HALF_COLS = BLOCK_N / 2;
+        // byte address of this thread's output row (16-bit outputs)
+        uint64_t row_ptr = reinterpret_cast<uint64_t>(p.out) + static_cast<uint64_t>(row) * p.N * 2;
+        if constexpr (EPI == EPI_GMM) {
+            if (p.out_row_ptrs != nullptr) {
+                // the row's home may be another GPU's memory: plain peer stores over NVLink
+                row_ptr = (row_in_tile < tl.m_rows) ? p.out_row_ptrs[row] : 0;
+            }
+        }
 #pragma unroll 1
         for (int cc = 0; cc < HALF_COLS; cc += 32) {
             const int c = col_half * HALF_COLS + cc;
@@ -306,11 +315,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
             tc::tmem_ld_32x32(t_addr + c, r);
             tc::tmem_ld_wait();
             const int64_t col0 = static_cast<int64_t>(tl.nt) * BLOCK_N + c;
-            if (!row_ok || col0 >= p.N) {
-                continue;
+            if constexpr (EPI == EPI_RAW) {
+                if (!row_ok || col0 >= p.N) {
+                    continue;
+                }
             }
-            // N is a multiple of 16: a chunk holds 32 or 16 valid columns
-            const int valid = (col0 + 32 <= p.N) ? 32 : 16;
+            // N is a multiple of 16: a chunk holds 32, 16 or no valid columns
+            const int valid = (col0 >= p.N) ? 0 : ((col0 + 32 <= p.N) ? 32 : 16);
             if constexpr (EPI == EPI_RAW) {
                 int32_t* dst = static_cast<int32_t*>(p.out) + row * p.N + col0;
 #pragma unroll
@@ -381,31 +392,49 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
                         }
                     }
                 }
-                // 32 outputs -> four 16-byte stores of 16-bit values
-                uint16_t* dst = static_cast<uint16_t*>(p.out) + row * p.N + col0;
-                if constexpr (EPI == EPI_GMM) {
-                    if (p.out_row_ptrs != nullptr) {
-                        // the row's home may be another GPU's memory: plain peer stores over NVLink
-                        dst = reinterpret_cast<uint16_t*>(p.out_row_ptrs[row]) + col0;
-                    }
-                }
+                // 32 outputs = 64 bytes of this thread's row.  They are not stored from here (every lane would
+                // write 16-byte pieces of a different row): the warp parks two such chunks, 128 bytes per row, in
+                // its private shared-memory patch and then writes whole 128-byte row segments, 8 lanes per row.
+                // That matters most when the row's home is another GPU: NVLink carries full lines, not fragments.
+                uint4 o[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    if (q * 8 < valid) {
-                        uint4 o;
-                        if (p.out_dtype == W8A8_DT_BF16) {
-                            o = make_uint4(pack2<W8A8_DT_BF16>(v[q * 8], v[q * 8 + 1]),
-                                           pack2<W8A8_DT_BF16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                           pack2<W8A8_DT_BF16>(v[q * 8 + 4], v[q * 8 + 5]),
-                                           pack2<W8A8_DT_BF16>(v[q * 8 + 6], v[q * 8 + 7]));
-                        } else {
-                            o = make_uint4(pack2<W8A8_DT_F16>(v[q * 8], v[q * 8 + 1]),
-                                           pack2<W8A8_DT_F16>(v[q * 8 + 2], v[q * 8 + 3]),
-                                           pack2<W8A8_DT_F16>(v[q * 8 + 4], v[q * 8 + 5]),
-                                           pack2<W8A8_DT_F16>(v[q * 8 + 6], v[q * 8 + 7]));
-                        }
-                        *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                    if (p.out_dtype == W8A8_DT_BF16) {
+                        o[q] = make_uint4(pack2<W8A8_DT_BF16>(v[q * 8], v[q * 8 + 1]),
+                                          pack2<W8A8_DT_BF16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                          pack2<W8A8_DT_BF16>(v[q * 8 + 4], v[q * 8 + 5]),
+                                          pack2<W8A8_DT_BF16>(v[q * 8 + 6], v[q * 8 + 7]));
+                    } else {
+                        o[q] = make_uint4(pack2<W8A8_DT_F16>(v[q * 8], v[q * 8 + 1]),
+                                          pack2<W8A8_DT_F16>(v[q * 8 + 2], v[q * 8 + 3]),
+                                          pack2<W8A8_DT_F16>(v[q * 8 + 4], v[q * 8 + 5]),
+                                          pack2<W8A8_DT_F16>(v[q * 8 + 6], v[q * 8 + 7]));
                     }
+                }
+                const int lane = row_in_tile & 31;
+                const int sub = (cc >> 5) & 1;  // which half of the 64-column patch
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    // row `lane`, 16-byte piece (sub*4 + q), pieces xor-swizzled by the row so that the eight
+                    // lanes of a quarter-warp hit eight different bank groups
+                    stage[lane * 8 + ((sub * 4 + q) ^ (lane & 7))] = o[q];
+                }
+                if (sub == 1) {
+                    __syncwarp();
+                    const int64_t patch_col0 = col0 - 32;  // first column of the 64-column patch
+                    const int piece = lane & 7;
+                    const int64_t pc = patch_col0 + piece * 8;
+                    const int first_row = row_in_tile & ~31;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3);  // row within the warp's 32
+                        const uint64_t rp = __shfl_sync(FULL_MASK, row_ptr, rr);
+                        const uint4 val = stage[rr * 8 + (piece ^ (rr & 7))];
+                        if (first_row + rr < tl.m_rows && !no_epilogue && pc < p.N) {
+                            *reinterpret_cast<uint4*>(rp + static_cast<uint64_t>(pc) * 2) = val;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -689,6 +718,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const int col_half = (warp - 2) >> 2;  // 0 or 1
         const int row_in_tile = quarter * 32 + lane;
         const bool no_epilogue = (p.debug & 4) != 0;
+        // this warp's 4 KB patch for turning per-thread rows into full-line stores
+        uint4* stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 512) + (warp - 2) * 256;
         const uint32_t tempty0 = (CG == 2) ? tc::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         int64_t it = 0;
         bool ok = true;
@@ -703,7 +734,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             tc::tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                     static_cast<uint32_t>(acc * BLOCK_N);
-            epilogue_tile<BLOCK_N, KIND, EPI>(p, tl, t_addr, row_in_tile, col_half, H, no_epilogue);
+            epilogue_tile<BLOCK_N, KIND, EPI>(p, tl, t_addr, row_in_tile, col_half, H, no_epilogue, stage);
             // accumulator stage drained: hand it back to the MMA issuer (one arrival per warp)
             tc::tc_fence_before_sync();
             __syncwarp();
