@@ -451,9 +451,6 @@ static int quant_matmul_impl(const int8_t* x1, const int8_t* x2, const void* sca
     p.flags = flags;
     p.out_dtype = out_dtype;
     p.bias_batch_stride = bias_batch_stride;
-    if (const char* dbg = getenv("W8A8_GEMM_DEBUG")) {
-        p.debug = atoi(dbg);
-    }
     const int cg = choose_cta_group(M, false);
     const int tile_m = 128 * cg;
     p.m_tiles_per_batch = static_cast<int32_t>((M + tile_m - 1) / tile_m);
@@ -570,9 +567,6 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.row_scale = x_scale;
         p.act = g.act;
         p.amax = g.amax;
-        if (const char* dbg = getenv("W8A8_GEMM_DEBUG")) {
-            p.debug = atoi(dbg);
-        }
         const int64_t max_total = g.max_tiles * p.n_tiles;
         const cudaError_t e = dispatch_gemm<KIND_I8, EPI_GMSQ>(cg, 256, b_mn, ta, tb, p, max_total, st);
         if (e != cudaSuccess) {

@@ -93,7 +93,6 @@ struct GemmParams {
     const uint64_t* out_row_ptrs;  // GMM: when set, row r is stored at this address instead of out + r*N
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
-    int32_t debug;    // experiments only, bit mask: 1 = no MMA, 2 = no TMA, 4 = no epilogue work
 };
 
 // fp32 exp shared with the CPU oracle: Cody-Waite reduction by ln2 in two
@@ -234,6 +233,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
             tc::tmem_ld_32x32(t_addr + 128 + c, u);
             tc::tmem_ld_wait();
             const int64_t col0 = static_cast<int64_t>(tl.nt) * 128 + c;  // column in [0, H)
+            const int lane = row_in_tile & 31;
             if (row_ok) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -253,10 +253,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
                             a[j] = __fmul_rn(canonical_silu(l), r);
                             local_max = fmaxf(local_max, fabsf(a[j]));
                         }
-                        *reinterpret_cast<float4*>(p.act + row * H + col) = make_float4(a[0], a[1], a[2], a[3]);
+                        // parked in the warp's shared-memory patch (piece q of row `lane`, xor-swizzled)
+                        stage[lane * 8 + (q ^ (lane & 7))] =
+                            make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]),
+                                       __float_as_uint(a[3]));
                     }
                 }
             }
+            // the 32 activations of each row are one 128-byte line: written by 8 lanes per row, 4 rows per
+            // instruction, instead of 16-byte pieces of 32 different rows
+            __syncwarp();
+            {
+                const int piece = lane & 7;
+                const int64_t col = col0 + piece * 4;
+                const int first_row = row_in_tile & ~31;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    if (first_row + rr < tl.m_rows && !no_epilogue && col < H) {
+                        const uint4 val = stage[rr * 8 + (piece ^ (rr & 7))];
+                        *reinterpret_cast<uint4*>(p.act + (static_cast<int64_t>(tl.a_row0) + first_row + rr) * H + col) =
+                            val;
+                    }
+                }
+            }
+            __syncwarp();
         }
         if (row_ok) {
             atomicMax(reinterpret_cast<int*>(p.amax + row), __float_as_int(local_max));
@@ -584,11 +605,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         break;
                     }
                     const uint32_t fb = full0 + 8u * stage;
-                    if (p.debug & 2) {
-                        if (leader) {
-                            tc::mbar_arrive(full_bar(stage));
-                        }
-                    } else {
+                    {
                         const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
                         const uint32_t b_dst = a_dst + GEMM_A_BYTES;
                         // Only the leader announces the bytes (its own and its partner's).  The partner's copies may
@@ -674,14 +691,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         break;
                     }
                     tc::tc_fence_after_sync();
-                    if (p.debug & 1) {
-                        if constexpr (CG == 2) {
-                            tc::mbar_arrive_cluster(tc::map_to_cta(empty_bar(stage), 0));
-                            tc::mbar_arrive_cluster(tc::map_to_cta(empty_bar(stage), 1));
-                        } else {
-                            tc::mbar_arrive(empty_bar(stage));
-                        }
-                    } else {
+                    {
                         const uint32_t a_lo = a_lo0 + stage * STAGE_STEP;
                         const uint32_t b_lo = b_lo0 + stage * STAGE_STEP;
 #pragma unroll
@@ -717,7 +727,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const int quarter = warp & 3;          // TMEM lanes [32*quarter, 32*quarter+32)
         const int col_half = (warp - 2) >> 2;  // 0 or 1
         const int row_in_tile = quarter * 32 + lane;
-        const bool no_epilogue = (p.debug & 4) != 0;
+        const bool no_epilogue = false;
         // this warp's 4 KB patch for turning per-thread rows into full-line stores
         uint4* stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 512) + (warp - 2) * 256;
         const uint32_t tempty0 = (CG == 2) ? tc::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
