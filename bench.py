@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One step is one pass of the operator over one batch of seeded synthetic input
-shaped like the configuration BASELINE.json quotes its metric on.  Workloads:
+shaped like the configuration the headline metric is quoted on.  Workloads:
 
     gmsq   grouped_matmul_swiglu_quant, E=256, 131072 rows (Zipf 1.1), K=7168, N=4096 (int8 TOPS)   [default]
     ardq   add_rms_norm_dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
@@ -137,7 +137,7 @@ class Workload:
 
 
 class ArdqWorkload(Workload):
-    """BASELINE configs[1]: x, residual bf16 [8192, 7168], gamma ~ N(1, 0.1), eps 1e-6."""
+    """Benchmark configuration 2 of 5: x, residual bf16 [8192, 7168], gamma ~ N(1, 0.1), eps 1e-6."""
     name, metric, unit, dtype, bound = "add_rms_norm_dynamic_quant", "rmsnorm_quant_hbm_gbs", "GB/s", "f32", "hbm"
     rows, n = 8192, 7168
     kernels_per_step = 1
@@ -246,7 +246,7 @@ class DqWorkload(ArdqWorkload):
 
 
 class GmsqWorkload(Workload):
-    """BASELINE configs[3]: E=256, 131072 rows with Zipf(1.1) group sizes, K=7168, N=4096."""
+    """Benchmark configuration 4 of 5: E=256, 131072 rows with Zipf(1.1) group sizes, K=7168, N=4096."""
     name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "int8",
                                         "tensor")
     E, M, K, N = 256, 131072, 7168, 4096
@@ -352,7 +352,7 @@ class GmsqWorkload(Workload):
 
 
 class QmmWorkload(Workload):
-    """BASELINE configs[2], M = 8192: dense W8A8 matmul K=7168 N=18432, bf16 output."""
+    """Benchmark configuration 3 of 5, M = 8192: dense W8A8 matmul K=7168 N=18432, bf16 output."""
     name, metric, unit, dtype, bound = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "int8", "tensor"
     M, K, N = 8192, 7168, 18432
     kernels_per_step = 1
@@ -418,7 +418,7 @@ class QmmWorkload(Workload):
 
 
 class ChainWorkload(Workload):
-    """BASELINE configs[4]: the full W8A8 MoE FFN chain, expert-parallel.  T=65536 tokens, hidden 7168, E=256,
+    """Benchmark configuration 5 of 5: the full W8A8 MoE FFN chain, expert-parallel.  T=65536 tokens, hidden 7168, E=256,
     top-8 of softmax(N(0,1) logits), inter 2048: add_rms_norm_dynamic_quant -> all-to-all dispatch (int8 rows +
     fp32 scales) -> grouped_matmul_swiglu_quant -> grouped_matmul int8 down projection -> all-to-all combine ->
     weighted sum.  Rank r owns T/N tokens and experts [r*E/N, (r+1)*E/N)."""

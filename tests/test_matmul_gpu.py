@@ -155,7 +155,7 @@ def test_quant_matmul_batched(ops, oracle):
 
 
 def test_cfg1_chain_dynamic_quant_then_quant_matmul(ops, oracle):
-    """BASELINE config 1, seed 0: the GPU chain equals the CPU chain bit for bit."""
+    """Benchmark configuration 1, seed 0: the GPU chain equals the CPU chain bit for bit."""
     O = oracle
     rng = np.random.default_rng(0)
     x = rng.standard_normal((128, 1024)).astype(F)
@@ -295,3 +295,56 @@ def test_grouped_matmul_float_path(ops, oracle, dtype, layout_nk):
     ref[130:] = xf[130:] @ wf[2] + bf[2]
     err = (out.double().cpu() - ref).abs().max().item()
     assert err <= ref.abs().max().item() * 2.0**-7, err
+
+
+def test_quant_matmul_full_size_sampled_rows(ops, oracle, cta_group):
+    """Benchmark configuration 3 at full size (M=8192, K=7168, N=18432): rows sampled across all row tiles are
+    compared bit for bit with the oracle, and the remaining rows through linearity in the per-token scale."""
+    if cta_group == "single":
+        pytest.skip("full-size case runs on the library's own kernel choice and on forced pairs")
+    O = oracle
+    g = torch.Generator(device="cuda").manual_seed(3)
+    m, k, n = 8192, 7168, 18432
+    x = torch.randint(-127, 128, (m, k), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (k, n), generator=g, device="cuda", dtype=torch.int8)
+    sc = torch.empty((n,), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+    pt = torch.empty((m,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+    out = ops.quant_matmul(x, w, sc, pertoken_scale=pt, output_dtype="bfloat16")
+    rows = torch.arange(5, m, 257, device="cuda")  # 32 rows, every 256-row tile boundary region gets hit
+    ref = O.quant_matmul(x[rows].cpu().numpy(), w.cpu().numpy(), sc.cpu().numpy(), pertoken=pt[rows].cpu().numpy(),
+                         flags=O.QM_SCALE_PERCHAN | O.QM_HAS_PT, out_dtype=O.DT_BF16)
+    assert np.array_equal(bits(out[rows]), ref)
+    # doubling every per-token scale doubles every output exactly (power-of-two scaling commutes with rounding)
+    out2 = ops.quant_matmul(x, w, sc, pertoken_scale=pt * 2, output_dtype="bfloat16")
+    assert torch.equal(out2.float(), out.float() * 2)
+
+
+def test_gmsq_full_size_sampled_rows(ops, oracle, cta_group):
+    """Benchmark configuration 4 at full size (E=256, 131072 rows, Zipf 1.1, K=7168, N=4096): every row of a few
+    experts (a large one, a one-tile one, tiny ones, the neighbours of an empty one) is compared bit for bit with
+    the oracle; all rows must use the full int8 range."""
+    if cta_group == "single":
+        pytest.skip("full-size case runs on the library's own kernel choice and on forced pairs")
+    rng = np.random.default_rng(0)
+    e, m, k, n = 256, 131072, 7168, 4096
+    gl = zipf_group_list(rng, m, e)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randint(-127, 128, (m, k), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (e, k, n), generator=g, device="cuda", dtype=torch.int8)
+    ws = torch.empty((e, n), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+    xs = torch.empty((m,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+    y, ysc = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, [int(v) for v in gl])
+    assert bool((y.to(torch.int32).abs().amax(-1) == 127).all())
+    starts = np.concatenate([[0], gl[:-1]])
+    sizes = gl - starts
+    picks = [int(np.argmax(sizes >= 1)), 40, 100, 200, 255]
+    picks += [int(i) for i in np.flatnonzero(sizes == 0)[:1]]
+    for ex in picks:
+        lo, hi = int(starts[ex]), int(gl[ex])
+        if hi == lo:
+            continue
+        hi = min(hi, lo + 300)  # a slice of the largest expert is enough
+        yo, yso = oracle.grouped_matmul_swiglu_quant(x[lo:hi].cpu().numpy(), w[ex:ex + 1].cpu().numpy(),
+                                                     ws[ex:ex + 1].cpu().numpy(), xs[lo:hi].cpu().numpy(), [hi - lo])
+        assert_same_f32(ysc[lo:hi], yso, f"y_scale of expert {ex}")
+        assert np.array_equal(y[lo:hi].cpu().numpy(), yo), f"expert {ex}"

@@ -246,7 +246,7 @@ def test_qm_order_of_operations_hand_derived(oracle):
 
 
 def test_qm_cfg1_chain_runs_on_cpu(oracle):
-    """BASELINE config 1: DynamicQuant -> QuantMatmul, seed 0, M=128 K=1024 N=1024."""
+    """Benchmark configuration 1: DynamicQuant -> QuantMatmul, seed 0, M=128 K=1024 N=1024."""
     O = oracle
     rng = np.random.default_rng(0)
     x = rng.standard_normal((128, 1024)).astype(F)

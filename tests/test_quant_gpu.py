@@ -52,7 +52,7 @@ def test_dynamic_quant_non_contiguous_and_empty(ops, oracle):
 
 
 def test_dynamic_quant_full_size_properties(ops):
-    """BASELINE config 2 shape: size-independent properties instead of a full CPU comparison."""
+    """Benchmark configuration 2 shape: size-independent properties instead of a full CPU comparison."""
     g = torch.Generator(device="cuda").manual_seed(0)
     x = torch.randn((8192, 7168), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
     y, s = ops.dynamic_quant(x)
@@ -121,7 +121,7 @@ def test_add_rms_norm_dynamic_quant_edge_rows(ops, oracle):
 
 
 def test_add_rms_norm_dynamic_quant_full_size_properties(ops, oracle):
-    """BASELINE config 2: [8192, 7168] bf16; a 64-row sample is compared with the oracle, the rest by properties."""
+    """Benchmark configuration 2: [8192, 7168] bf16; a 64-row sample is compared with the oracle, the rest by properties."""
     g = torch.Generator(device="cuda").manual_seed(0)
     x1 = torch.randn((8192, 7168), generator=g, device="cuda").to(torch.bfloat16)
     x2 = torch.randn((8192, 7168), generator=g, device="cuda").to(torch.bfloat16)
