@@ -504,7 +504,79 @@ class ChainWorkload(Workload):
         return run, m / self.TOPK, f"the two grouped matmuls of {m // self.TOPK} tokens ({m} expanded rows, {e} experts)"
 
 
-WORKLOADS = {"gmsq": GmsqWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
+class MrrWorkload(Workload):
+    """MoeReRouting at the dispatch shape of benchmark configuration 5: what 8 ranks deliver to one rank's 32 local
+    experts, 65536 int8 rows of 7168 with their fp32 scales, regrouped rank-major -> expert-major."""
+    name, metric, unit, dtype, bound = "moe_re_routing", "moe_re_routing_hbm_gbs", "GB/s", "u8", "hbm"
+    ranks, experts, rows, h = 8, 32, 65536, 7168
+    kernels_per_step = 3  # cell tables, row index, row copy
+    traffic = None
+    scaling = "weak"
+
+    def config(self, world):
+        return {"workload": "moe_re_routing: 65536 int8 rows x 7168 + scales, counts [8, 32] on the device",
+                "rows_per_gpu": self.rows, "hidden": self.h, "l2": "rows (470 MB in, 470 MB out) larger than L2",
+                "parallelism": f"replicas x{world}" if world > 1 else "single GPU"}
+
+    def _counts(self, seed):
+        rng = np.random.default_rng(seed)
+        return rng.multinomial(self.rows, np.full(self.ranks * self.experts, 1.0 / (self.ranks * self.experts))
+                               ).reshape(self.ranks, self.experts).astype(np.int64)
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        self.tok = torch.randint(-128, 128, (self.rows, self.h), generator=g, device="cuda", dtype=torch.int8)
+        self.scl = torch.rand((self.rows,), generator=g, device="cuda")
+        self.cnt = torch.from_numpy(self._counts(rank)).cuda()
+        lib = self.L.load()
+        self._out = torch.empty_like(self.tok)
+        self._oscl = torch.empty_like(self.scl)
+        self._idx = torch.empty((self.rows,), dtype=torch.int32, device="cuda")
+        self._num = torch.empty((self.experts,), dtype=torch.int64, device="cuda")
+        need = lib.w8a8_moe_re_routing_workspace_size(self.rows, self.ranks, self.experts)
+        self._ws = torch.empty((need,), dtype=torch.uint8, device="cuda")
+        self._fn = lib.w8a8_moe_re_routing
+        self._args = (self.tok.data_ptr(), self.cnt.data_ptr(), self.scl.data_ptr(), self._out.data_ptr(),
+                      self._oscl.data_ptr(), self._idx.data_ptr(), self._num.data_ptr(), self.rows, self.h, self.ranks,
+                      self.experts, 8, self._ws.data_ptr(), need)
+
+    def gpu_step(self):
+        rc = self._fn(*self._args, self.torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def bytes_per_step(self):
+        return self.rows * (2 * self.h + 4 + 4 + 4)
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def roofline_units(self):
+        return self.bytes_per_step() / 1e9
+
+    def host_inputs(self):
+        return [self.tok.cpu().pin_memory(), self.scl.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        tok = host[0].to("cuda", non_blocking=True)
+        scl = host[1].to("cuda", non_blocking=True)
+        outs = self.ops.moe_re_routing(tok, self.cnt, scl)
+        back = [o.to("cpu", non_blocking=True) for o in outs]
+        return (host[0].numel() + host[1].numel() * 4, sum(o.numel() * o.element_size() for o in back))
+
+    def cpu_sample(self, O):
+        rng = np.random.default_rng(0)
+        cnt = self._counts(0)
+        tok = rng.integers(-128, 128, (self.rows, self.h)).astype(np.int8)
+        scl = rng.random(self.rows).astype(np.float32)
+        return (lambda: O.moe_re_routing(tok, cnt, scl)), self.bytes_per_step() / 1e9, "all 65536 rows"
+
+
+WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
              "chain": ChainWorkload}
 
 

@@ -52,6 +52,8 @@ SIGNATURES = {
     "w8a8_route_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "w8a8_scatter_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "w8a8_permute_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "w8a8_moe_re_routing_workspace_size": (_sz, [_i64, _i64, _i64]),
+    "w8a8_moe_re_routing": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "w8a8_dispatch_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "w8a8_expand_row_pointers": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "w8a8_grouped_matmul_to_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32,

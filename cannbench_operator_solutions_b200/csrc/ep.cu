@@ -128,6 +128,11 @@ __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint8_t* __rest
 
 // dst[d] = src[index[d]] for whole rows (and their fp32 scales): the regroup
 // step after an all-to-all (rank-major -> expert-major) and its inverse.
+// One warp per row at a time; a lane keeps PERMUTE_UNROLL 16-byte loads in flight before it stores, which is
+// what a pure copy needs to cover the HBM latency (a CTA-wide loop with one load per thread reached 0.66 of the
+// copy bandwidth, this form is measured in the benchmark's moe_re_routing workload).
+constexpr int PERMUTE_UNROLL = 8;
+
 template <bool VEC>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint8_t* __restrict__ src,
                                                            const float* __restrict__ src_scale,
@@ -135,7 +140,10 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint8_t* __rest
                                                            const int64_t* __restrict__ index, int64_t rows,
                                                            int64_t row_bytes)
 {
-    for (int64_t d = blockIdx.x; d < rows; d += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t d = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); d < rows;
+         d += warps) {
         const int64_t s = index[d];
         if (s < 0) {
             continue;
@@ -144,15 +152,29 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint8_t* __rest
             const uint4* sp = reinterpret_cast<const uint4*>(src + s * row_bytes);
             uint4* dp = reinterpret_cast<uint4*>(dst + d * row_bytes);
             const int64_t n16 = row_bytes / 16;
-            for (int64_t c = threadIdx.x; c < n16; c += blockDim.x) {
-                __stcs(dp + c, __ldcs(sp + c));
+            for (int64_t base = 0; base < n16; base += 32 * PERMUTE_UNROLL) {
+                uint4 v[PERMUTE_UNROLL];
+#pragma unroll
+                for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+                    const int64_t c = base + u * 32 + lane;
+                    if (c < n16) {
+                        v[u] = __ldcs(sp + c);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+                    const int64_t c = base + u * 32 + lane;
+                    if (c < n16) {
+                        __stcs(dp + c, v[u]);
+                    }
+                }
             }
         } else {
-            for (int64_t c = threadIdx.x; c < row_bytes; c += blockDim.x) {
+            for (int64_t c = lane; c < row_bytes; c += 32) {
                 dst[d * row_bytes + c] = src[s * row_bytes + c];
             }
         }
-        if (threadIdx.x == 0 && src_scale != nullptr && dst_scale != nullptr) {
+        if (lane == 0 && src_scale != nullptr && dst_scale != nullptr) {
             dst_scale[d] = src_scale[s];
         }
     }
@@ -238,6 +260,139 @@ __global__ void __launch_bounds__(256) expand_row_pointers_kernel(const int64_t*
         }
     }
     out[r] = seg_ptr[lo] + static_cast<uint64_t>(r - seg_first[lo]) * static_cast<uint64_t>(row_bytes);
+}
+
+// ---------------------------------------------------------------------------
+// MoeReRouting with the count matrix in device memory
+// (operators/moererouting/csrc/ops/moe_re_routing/op_kernel/moe_re_routing_kernel.cpp:15-24)
+// ---------------------------------------------------------------------------
+// Cells are numbered in destination order, s = j * N + i (expert-major, then source rank):
+//   dst_first[s] = colStart(j) + sum_{i'<i} cnt[i'][j]      (non-decreasing in s, one extra entry = total)
+//   src_first[s] = rowStart(i) + sum_{j'<j} cnt[i][j']
+// One CTA builds both tables; the matrix is small (ranks x local experts) next to the token rows.
+// hdr[1] = 1 when a count is negative or the counts sum to more than A rows; the later kernels then do nothing.
+template <typename CntT>
+__global__ void __launch_bounds__(1024) rr_table_kernel(const CntT* __restrict__ cnt, int64_t N, int64_t E,
+                                                        int64_t A, int32_t* __restrict__ hdr,
+                                                        int64_t* __restrict__ dst_first,
+                                                        int64_t* __restrict__ src_first,
+                                                        int64_t* __restrict__ col_start,
+                                                        int64_t* __restrict__ row_start,
+                                                        CntT* __restrict__ expert_num)
+{
+    __shared__ int s_bad;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        s_bad = 0;
+    }
+    __syncthreads();
+    bool bad = false;
+    for (int64_t j = tid; j < E; j += blockDim.x) {
+        int64_t sum = 0;
+        for (int64_t i = 0; i < N; ++i) {
+            const int64_t c = static_cast<int64_t>(cnt[i * E + j]);
+            bad |= (c < 0) || (c > A);
+            sum += c;
+        }
+        col_start[j + 1] = sum;
+    }
+    for (int64_t i = tid; i < N; i += blockDim.x) {
+        int64_t sum = 0;
+        for (int64_t j = 0; j < E; ++j) {
+            const int64_t c = static_cast<int64_t>(cnt[i * E + j]);
+            sum += (c < 0 || c > A) ? 0 : c;
+        }
+        row_start[i + 1] = sum;
+    }
+    if (bad) {
+        s_bad = 1;
+    }
+    __syncthreads();
+    // The two scans are short (local experts, ranks); two threads run them side by side.
+    if (tid == 0) {
+        int64_t run = 0;
+        col_start[0] = 0;
+        int64_t next = col_start[1];
+        for (int64_t j = 0; j < E; ++j) {
+            const int64_t c = next;
+            if (j + 1 < E) {
+                next = col_start[j + 2];  // issued before the dependent store of this step
+            }
+            run += c;
+            if (run > A) {
+                s_bad = 1;
+                run = A;  // keeps later sums in range; nothing is copied once the flag is set
+            }
+            col_start[j + 1] = run;
+        }
+    }
+    if (tid == 32) {
+        int64_t run = 0;
+        row_start[0] = 0;
+        int64_t next = row_start[1];
+        for (int64_t i = 0; i < N; ++i) {
+            const int64_t c = next;
+            if (i + 1 < N) {
+                next = row_start[i + 2];
+            }
+            run += c;
+            row_start[i + 1] = run;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        dst_first[N * E] = s_bad ? 0 : col_start[E];
+        hdr[0] = 0;
+        hdr[1] = s_bad;
+    }
+    __syncthreads();
+    if (s_bad) {
+        return;
+    }
+    for (int64_t j = tid; j < E; j += blockDim.x) {
+        int64_t run = col_start[j];
+        for (int64_t i = 0; i < N; ++i) {
+            dst_first[j * N + i] = run;
+            run += static_cast<int64_t>(cnt[i * E + j]);
+        }
+        expert_num[j] = static_cast<CntT>(run - col_start[j]);
+    }
+    for (int64_t i = tid; i < N; i += blockDim.x) {
+        int64_t run = row_start[i];
+        for (int64_t j = 0; j < E; ++j) {
+            src_first[j * N + i] = run;
+            run += static_cast<int64_t>(cnt[i * E + j]);
+        }
+    }
+}
+
+// index[d] = source row of destination row d (-1 past the routed rows); out_idx[d] the same as int32.
+__global__ void __launch_bounds__(256) rr_index_kernel(const int32_t* __restrict__ hdr,
+                                                       const int64_t* __restrict__ dst_first,
+                                                       const int64_t* __restrict__ src_first, int64_t cells,
+                                                       int64_t A, int64_t* __restrict__ index,
+                                                       int32_t* __restrict__ out_idx)
+{
+    const int64_t d = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (d >= A) {
+        return;
+    }
+    if (hdr[1] != 0 || d >= dst_first[cells]) {
+        index[d] = -1;
+        return;
+    }
+    int64_t lo = 0, hi = cells;  // last cell whose first row is <= d (empty cells share a first row)
+    while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (dst_first[mid] <= d) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    const int64_t s = src_first[lo] + (d - dst_first[lo]);
+    index[d] = s;
+    out_idx[d] = static_cast<int32_t>(s);
 }
 
 // One CTA per token; each thread owns 8-element chunks of the hidden row.
@@ -378,8 +533,9 @@ extern "C" int w8a8_permute_rows(const void* src, const float* src_scale, void* 
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool vec = (row_bytes % 16 == 0) && w8a8::is_aligned(src, 16) && w8a8::is_aligned(dst, 16);
-    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
-    const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;  // 8 CTAs of 8 warps fill an SM
+    const int64_t want = (rows + 7) / 8;                             // one warp per row
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
     if (vec) {
         w8a8::permute_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                              static_cast<uint8_t*>(dst), dst_scale, index, rows,
@@ -478,4 +634,83 @@ extern "C" int w8a8_combine(const void* rows, const float* probs, const int64_t*
         }
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+// workspace: 256-byte header | dst_first[N*E+1] | src_first[N*E] | col_start[E+1] | row_start[N+1] | index[A]
+extern "C" size_t w8a8_moe_re_routing_workspace_size(int64_t A, int64_t N, int64_t E)
+{
+    if (A < 0 || N <= 0 || E <= 0) {
+        return 0;
+    }
+    const size_t cells = static_cast<size_t>(N) * static_cast<size_t>(E);
+    size_t bytes = 256;
+    bytes += w8a8::align_up((cells + 1) * sizeof(int64_t), 256);
+    bytes += w8a8::align_up(cells * sizeof(int64_t), 256);
+    bytes += w8a8::align_up(static_cast<size_t>(E + 1) * sizeof(int64_t), 256);
+    bytes += w8a8::align_up(static_cast<size_t>(N + 1) * sizeof(int64_t), 256);
+    bytes += w8a8::align_up(static_cast<size_t>(A > 0 ? A : 1) * sizeof(int64_t), 256);
+    return bytes;
+}
+
+extern "C" int w8a8_moe_re_routing(const void* tokens, const void* counts, const float* scales, void* out_tokens,
+                                   float* out_scales, int32_t* out_idx, void* expert_token_num, int64_t A,
+                                   int64_t row_bytes, int64_t N, int64_t E, int count_bytes, void* workspace,
+                                   size_t workspace_bytes, void* stream)
+{
+    if (A < 0 || row_bytes <= 0 || N <= 0 || E <= 0 || (count_bytes != 4 && count_bytes != 8)) {
+        return W8A8_ERR_INVALID;
+    }
+    if (A > INT32_MAX) {
+        return W8A8_ERR_LIMIT;  // permute_token_idx is int32
+    }
+    if (counts == nullptr || expert_token_num == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    if (A > 0 && (tokens == nullptr || out_tokens == nullptr || out_idx == nullptr)) {
+        return W8A8_ERR_INVALID;
+    }
+    if (workspace == nullptr || workspace_bytes < w8a8_moe_re_routing_workspace_size(A, N, E)) {
+        return W8A8_ERR_WORKSPACE;
+    }
+    if (!w8a8::is_aligned(workspace, 256) || !w8a8::is_aligned(counts, static_cast<size_t>(count_bytes))) {
+        return W8A8_ERR_ALIGN;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t cells = static_cast<size_t>(N) * static_cast<size_t>(E);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    int32_t* hdr = reinterpret_cast<int32_t*>(ws);
+    ws += 256;
+    int64_t* dst_first = reinterpret_cast<int64_t*>(ws);
+    ws += w8a8::align_up((cells + 1) * sizeof(int64_t), 256);
+    int64_t* src_first = reinterpret_cast<int64_t*>(ws);
+    ws += w8a8::align_up(cells * sizeof(int64_t), 256);
+    int64_t* col_start = reinterpret_cast<int64_t*>(ws);
+    ws += w8a8::align_up(static_cast<size_t>(E + 1) * sizeof(int64_t), 256);
+    int64_t* row_start = reinterpret_cast<int64_t*>(ws);
+    ws += w8a8::align_up(static_cast<size_t>(N + 1) * sizeof(int64_t), 256);
+    int64_t* index = reinterpret_cast<int64_t*>(ws);
+
+    if (count_bytes == 4) {
+        w8a8::rr_table_kernel<int32_t><<<1, 1024, 0, st>>>(static_cast<const int32_t*>(counts), N, E, A, hdr,
+                                                          dst_first, src_first, col_start, row_start,
+                                                          static_cast<int32_t*>(expert_token_num));
+    } else {
+        w8a8::rr_table_kernel<int64_t><<<1, 1024, 0, st>>>(static_cast<const int64_t*>(counts), N, E, A, hdr,
+                                                          dst_first, src_first, col_start, row_start,
+                                                          static_cast<int64_t*>(expert_token_num));
+    }
+    if (cudaGetLastError() != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    if (A == 0) {
+        return W8A8_OK;
+    }
+    const unsigned blocks = static_cast<unsigned>((A + 255) / 256);
+    w8a8::rr_index_kernel<<<blocks, 256, 0, st>>>(hdr, dst_first, src_first, static_cast<int64_t>(cells), A, index,
+                                                  out_idx);
+    if (cudaGetLastError() != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    return w8a8_permute_rows(tokens, scales, out_tokens, (scales != nullptr) ? out_scales : nullptr, index, A,
+                             row_bytes, stream);
 }

@@ -9,6 +9,7 @@
 //   quant_matmul                operators/quantmatmul/csrc/ops/quant_matmul/op_plugin/quant_matmul_plugin.cpp:46-272
 //   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:38-150
 //   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:40-190
+//   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:32-170
 // The NPU plugins enqueue their launchers with OpCommand::RunOpApi on the
 // current NPU stream; here the C-ABI call is enqueued on the current CUDA
 // stream.  The plugin only unpacks tensors: all arithmetic is in the library.
@@ -401,8 +402,70 @@ static c10::List<torch::Tensor> grouped_matmul_cuda(const torch::Tensor& x, cons
     return make_outputs(y, ends, split_item);
 }
 
+// ---------------------------------------------------------------- moe_re_routing
+using RrOut = std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>;
+
+static RrOut moe_re_routing_meta(const torch::Tensor& tokens, const torch::Tensor& counts,
+                                 const c10::optional<torch::Tensor>& scales, int64_t expert_token_num_type,
+                                 int64_t idx_type)
+{
+    (void)scales;
+    (void)expert_token_num_type;
+    (void)idx_type;
+    TORCH_CHECK(tokens.dim() == 2, "moe_re_routing: tokens must be 2D (A, H).");
+    TORCH_CHECK(counts.dim() == 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
+    const int64_t a = tokens.size(0);
+    return std::make_tuple(torch::empty({a, tokens.size(1)}, tokens.options()),
+                           torch::empty({a}, tokens.options().dtype(torch::kFloat)),
+                           torch::empty({a}, tokens.options().dtype(torch::kInt)),
+                           torch::empty({counts.size(1)}, counts.options()));
+}
+
+static RrOut moe_re_routing_cuda(const torch::Tensor& tokens, const torch::Tensor& counts,
+                                 const c10::optional<torch::Tensor>& scales, int64_t expert_token_num_type,
+                                 int64_t idx_type)
+{
+    TORCH_CHECK(idx_type == 0, "moe_re_routing: only gather index mode (idx_type == 0) is supported.");
+    const c10::cuda::OptionalCUDAGuard guard(tokens.device());
+    auto tok = tokens.contiguous();
+    auto cnt = counts.contiguous();
+    torch::Tensor scl;
+    const bool has_scales = scales.has_value() && scales->defined();
+    if (has_scales) {
+        scl = scales->contiguous();
+        TORCH_CHECK(scl.scalar_type() == torch::kFloat, "moe_re_routing: per_token_scales must be float32.");
+    }
+    auto outs = moe_re_routing_meta(tok, cnt, scales, expert_token_num_type, idx_type);
+    const int64_t a = tok.size(0), h = tok.size(1), n = cnt.size(0), e = cnt.size(1);
+    if (a <= 0 || h <= 0 || n <= 0 || e <= 0) {
+        return outs;
+    }
+    TORCH_CHECK(tok.scalar_type() == torch::kFloat16 || tok.scalar_type() == torch::kBFloat16 ||
+                    tok.scalar_type() == torch::kChar,
+                "moe_re_routing: unsupported tokens dtype.");
+    TORCH_CHECK(cnt.scalar_type() == torch::kInt || cnt.scalar_type() == torch::kLong,
+                "moe_re_routing: unsupported expert_token_num_per_rank dtype.");
+    TORCH_CHECK(cnt.is_cuda(), "moe_re_routing: expert_token_num_per_rank must be on the tokens' device.");
+    if (has_scales) {
+        TORCH_CHECK(scl.numel() == a, "moe_re_routing: per_token_scales must have A elements.");
+    }
+    const size_t ws_bytes = w8a8_moe_re_routing_workspace_size(a, n, e);
+    auto ws = torch::empty({static_cast<int64_t>(ws_bytes)}, tok.options().dtype(torch::kByte));
+    check_status(w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(),
+                                     has_scales ? static_cast<const float*>(scl.data_ptr()) : nullptr,
+                                     std::get<0>(outs).data_ptr(), static_cast<float*>(std::get<1>(outs).data_ptr()),
+                                     static_cast<int32_t*>(std::get<2>(outs).data_ptr()),
+                                     std::get<3>(outs).data_ptr(), a, h * static_cast<int64_t>(tok.element_size()), n,
+                                     e, static_cast<int>(cnt.element_size()), ws.data_ptr(), ws_bytes,
+                                     stream_of(tok)),
+                 "moe_re_routing");
+    return outs;
+}
+
 TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 {
+    m.def("moe_re_routing(Tensor tokens, Tensor expert_token_num_per_rank, Tensor? per_token_scales=None, "
+          "int expert_token_num_type=1, int idx_type=0) -> (Tensor, Tensor, Tensor, Tensor)");
     m.def("dynamic_quant(Tensor x) -> (Tensor y, Tensor scale)");
     m.def("add_rms_norm_dynamic_quant(Tensor x1, Tensor x2, Tensor gamma, float epsilon) -> "
           "(Tensor y, Tensor xOut, Tensor scaleOut)");
@@ -423,6 +486,7 @@ TORCH_LIBRARY_IMPL(cann_bench, Meta, m)
     m.impl("quant_matmul", quant_matmul_meta);
     m.impl("grouped_matmul_swiglu_quant", gmsq_meta);
     m.impl("grouped_matmul", grouped_matmul_meta);
+    m.impl("moe_re_routing", moe_re_routing_meta);
 }
 
 TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
@@ -432,6 +496,7 @@ TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
     m.impl("quant_matmul", quant_matmul_cuda);
     m.impl("grouped_matmul_swiglu_quant", gmsq_cuda);
     m.impl("grouped_matmul", grouped_matmul_cuda);
+    m.impl("moe_re_routing", moe_re_routing_cuda);
 }
 
 }  // namespace cann_bench

@@ -312,3 +312,54 @@ def grouped_matmul(x: torch.Tensor, weight: torch.Tensor, group_list: GroupList,
             s = v
         return outs
     return [y]
+
+
+def moe_re_routing(tokens: torch.Tensor, expert_token_num_per_rank: torch.Tensor,
+                   per_token_scales: Optional[torch.Tensor] = None, expert_token_num_type: int = 1,
+                   idx_type: int = 0, *, workspace: Optional[torch.Tensor] = None
+                   ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``moe_re_routing(Tensor tokens, Tensor expert_token_num_per_rank, Tensor? per_token_scales=None,
+    int expert_token_num_type=1, int idx_type=0) -> (permute_tokens, permute_per_token_scales, permute_token_idx,
+    expert_token_num)`` (operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:34-38,
+    72-161).
+
+    ``tokens`` [A, H] fp16 / bf16 / int8 in rank-major, expert-minor order (what an all-to-all delivers);
+    ``expert_token_num_per_rank`` [N, E] int32 / int64 on the device.  Rows come back expert-major.  As in the
+    reference ``expert_token_num_type`` is accepted and ignored (counts are always returned), ``idx_type`` must be
+    0, and without ``per_token_scales`` the scale output is allocated but not written.  The whole path runs on the
+    device: the count matrix is never read by the host."""
+    del expert_token_num_type
+    _check(idx_type == 0, "moe_re_routing: only gather index mode (idx_type == 0) is supported.")
+    _check(tokens.dim() == 2, "moe_re_routing: tokens must be 2D (A, H).")
+    _check(expert_token_num_per_rank.dim() == 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).")
+    _need_cuda(tokens, expert_token_num_per_rank, per_token_scales)
+    tok = tokens.contiguous()
+    cnt = expert_token_num_per_rank.contiguous()
+    scl = None
+    if per_token_scales is not None:
+        scl = per_token_scales.contiguous()
+        _check(scl.dtype == torch.float32, "moe_re_routing: per_token_scales must be float32.")
+    a, h = tok.shape
+    n, e = cnt.shape
+    out_tok = torch.empty_like(tok)
+    out_scl = torch.empty((a,), dtype=torch.float32, device=tok.device)
+    out_idx = torch.empty((a,), dtype=torch.int32, device=tok.device)
+    out_num = torch.empty((e,), dtype=cnt.dtype, device=tok.device)
+    if a <= 0 or h <= 0 or n <= 0 or e <= 0:
+        return out_tok, out_scl, out_idx, out_num
+    _check(tok.dtype in (torch.float16, torch.bfloat16, torch.int8), "moe_re_routing: unsupported tokens dtype.")
+    _check(cnt.dtype in (torch.int32, torch.int64), "moe_re_routing: unsupported expert_token_num_per_rank dtype.")
+    if scl is not None:
+        _check(scl.numel() == a, "moe_re_routing: per_token_scales must have A elements.")
+    lib = L.load()
+    need = lib.w8a8_moe_re_routing_workspace_size(a, n, e)
+    if workspace is None:
+        workspace = torch.empty((need,), dtype=torch.uint8, device=tok.device)
+    _check(workspace.numel() * workspace.element_size() >= need, "moe_re_routing: workspace too small")
+    with torch.cuda.device(tok.device):
+        rc = lib.w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(), _ptr(scl), out_tok.data_ptr(),
+                                     out_scl.data_ptr(), out_idx.data_ptr(), out_num.data_ptr(), a,
+                                     h * tok.element_size(), n, e, cnt.element_size(), workspace.data_ptr(),
+                                     workspace.numel() * workspace.element_size(), _stream())
+    _status(rc, "moe_re_routing")
+    return out_tok, out_scl, out_idx, out_num

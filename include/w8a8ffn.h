@@ -245,6 +245,24 @@ int w8a8_permute_rows(const void* src, const float* src_scale, void* dst, float*
                       const int64_t* index, int64_t rows, int64_t row_bytes, void* stream);
 
 /*
+ * MoeReRouting with the (N ranks x E local experts) count matrix in device memory: no host readback, the cell
+ * tables are built by one small kernel, then rows move as in w8a8_permute_rows.
+ *   srcStart(i,j) = sum_{i'<i} rowSum(i') + sum_{j'<j} cnt[i][j'];  dstStart(i,j) = sum_{j'<j} colSum(j') +
+ *   sum_{i'<i} cnt[i'][j];  out[dstStart+k] = in[srcStart+k], out_idx[dstStart+k] = srcStart+k,
+ *   expert_token_num[j] = colSum(j) in the counts' own integer type.
+ * Replaces launch_moe_rr_{h,bf,i8}_{i32,i64}
+ * (operators/moererouting/csrc/ops/moe_re_routing/op_kernel/moe_re_routing_launch.h:44-74); the token type only
+ * enters as row_bytes = H * element size, count_bytes is 4 (int32) or 8 (int64).  scales / out_scales are optional
+ * (fp32 [A]).  Rows past the routed total are left untouched.  A negative count or a total above A copies nothing
+ * and sets the workspace error word (w8a8_workspace_error() returns 1).
+ */
+size_t w8a8_moe_re_routing_workspace_size(int64_t A, int64_t N, int64_t E);
+int w8a8_moe_re_routing(const void* tokens, const void* counts, const float* scales, void* out_tokens,
+                        float* out_scales, int32_t* out_idx, void* expert_token_num, int64_t A,
+                        int64_t row_bytes, int64_t N, int64_t E, int count_bytes, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/*
  * Fused dispatch (no reference counterpart: the reference is single-device).  Instead of packing rows, running
  * an all-to-all and regrouping the result, every quantised token row is stored directly at the row it occupies in
  * the expert-major buffer of the rank that owns its expert -- a peer pointer when that rank is another GPU

@@ -82,6 +82,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_gather_rows.argtypes = [vp, vp, vp, i64, i64]
     lib.oracle_combine.restype = i32
     lib.oracle_combine.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32]
+    lib.oracle_moe_re_routing.restype = i32
+    lib.oracle_moe_re_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64]
     lib.oracle_num_threads.restype = i32
     _lib = lib
     return lib
@@ -259,3 +261,22 @@ def combine(rows_bits: np.ndarray, probs: np.ndarray, expanded_pos: np.ndarray, 
     if rc != 0:
         raise ValueError("oracle_combine rejected the arguments")
     return out
+
+
+def moe_re_routing(tokens: np.ndarray, counts: np.ndarray, scales: Optional[np.ndarray] = None):
+    """tokens [A, H] (any element type), counts [N, E] -> (permute_tokens, permute_scales, permute_token_idx,
+    expert_token_num)."""
+    tokens = np.ascontiguousarray(tokens)
+    cnt = _c(counts, np.int64)
+    a = tokens.shape[0]
+    n, e = cnt.shape
+    out = np.zeros_like(tokens)
+    out_s = np.zeros((a,), np.float32)
+    idx = np.zeros((a,), np.int32)
+    num = np.zeros((e,), np.int64)
+    sc = None if scales is None else _c(scales, np.float32)
+    rc = load().oracle_moe_re_routing(_p(tokens), _p(cnt), _p(sc), _p(out), _p(out_s), _p(idx), _p(num), a,
+                                      int(np.prod(tokens.shape[1:])) * tokens.itemsize, n, e)
+    if rc != 0:
+        raise ValueError("oracle_moe_re_routing rejected the arguments")
+    return out, out_s, idx, num

@@ -790,3 +790,64 @@ int oracle_combine(const void* rows, const float* probs, const int64_t* expanded
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* MoeReRouting                                                              */
+/* MRR/op_kernel/moe_re_routing_kernel.cpp:15-24 (semantics), same text in   */
+/* MRR/op_kernel/moe_re_routing_launch.h:15-21:                              */
+/*   srcStart(i,j) = sum_{i'<i} rowSum(i') + sum_{j'<j} cnt[i][j']           */
+/*   dstStart(i,j) = sum_{j'<j} colSum(j') + sum_{i'<i} cnt[i'][j]           */
+/*   out[dstStart+k] = in[srcStart+k], idx[dstStart+k] = srcStart+k,         */
+/*   expert_token_num[j] = colSum(j) (count mode; the plugin ignores         */
+/*   expert_token_num_type, MRR/op_plugin/moe_re_routing_plugin.cpp:75).     */
+/* ------------------------------------------------------------------------ */
+int oracle_moe_re_routing(const void* tokens, const int64_t* counts, const float* scales, void* out_tokens,
+                          float* out_scales, int32_t* out_idx, int64_t* expert_token_num, int64_t A,
+                          int64_t row_bytes, int64_t N, int64_t E)
+{
+    if (A < 0 || row_bytes <= 0 || N <= 0 || E <= 0) {
+        return -1;
+    }
+    int64_t total = 0;
+    for (int64_t i = 0; i < N * E; ++i) {
+        if (counts[i] < 0) {
+            return -1;
+        }
+        total += counts[i];
+    }
+    if (total > A) {
+        return -1;
+    }
+    int64_t col_start = 0;
+    for (int64_t j = 0; j < E; ++j) {
+        int64_t col_sum = 0;
+        int64_t row_start = 0;
+        for (int64_t i = 0; i < N; ++i) {
+            int64_t before = 0; /* sum_{j'<j} cnt[i][j'] */
+            for (int64_t jj = 0; jj < j; ++jj) {
+                before += counts[i * E + jj];
+            }
+            const int64_t src = row_start + before;
+            const int64_t dst = col_start + col_sum;
+            const int64_t c = counts[i * E + j];
+#pragma omp parallel for schedule(static) if (c * row_bytes > (1 << 16))
+            for (int64_t k = 0; k < c; ++k) {
+                memcpy((char*)out_tokens + (dst + k) * row_bytes, (const char*)tokens + (src + k) * row_bytes,
+                       (size_t)row_bytes);
+                if (scales != NULL && out_scales != NULL) {
+                    out_scales[dst + k] = scales[src + k];
+                }
+                out_idx[dst + k] = (int32_t)(src + k);
+            }
+            col_sum += c;
+            int64_t row_sum = 0;
+            for (int64_t jj = 0; jj < E; ++jj) {
+                row_sum += counts[i * E + jj];
+            }
+            row_start += row_sum;
+        }
+        expert_token_num[j] = col_sum;
+        col_start += col_sum;
+    }
+    return 0;
+}

@@ -106,6 +106,13 @@ int oracle_gather_rows(const void* src, void* dst, const int64_t* src_row, int64
 int oracle_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,
                    int64_t T, int64_t topk, int64_t H, int dtype);
 
+/* MoeReRouting: regroup a rank-major / expert-minor token buffer (what an all-to-all delivers) into expert-major
+ * order.  counts[i*E + j] = rows received from rank i for local expert j.  row_bytes is the byte length of a token
+ * row; scales / out_scales may be NULL. */
+int oracle_moe_re_routing(const void* tokens, const int64_t* counts, const float* scales, void* out_tokens,
+                          float* out_scales, int32_t* out_idx, int64_t* expert_token_num, int64_t A,
+                          int64_t row_bytes, int64_t N, int64_t E);
+
 int oracle_num_threads(void);
 
 #ifdef __cplusplus

@@ -88,6 +88,10 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_grouped_matmul(p, p, None, p, p, p, 8, 64, 32, 2, gl_bad, 0, L.DT_I8, 0, L.DT_BF16, L.W_KN,
                                    p, 1 << 30, None) == L.ERR_GROUP_LIST
     assert lib.w8a8_route_plan(p, 4, 2, 8, p, p, p, p, 16, None) == L.ERR_WORKSPACE
+    assert lib.w8a8_moe_re_routing(p, p, None, p, None, p, p, 4, 64, 2, 2, 2, p, 1 << 30, None) == L.ERR_INVALID
+    assert lib.w8a8_moe_re_routing(p, p, None, p, None, p, p, 4, 64, 2, 2, 4, p, 16, None) == L.ERR_WORKSPACE
+    assert lib.w8a8_moe_re_routing(p, p, None, p, None, p, p, 1 << 31, 64, 2, 2, 4, p, 1 << 40, None) == L.ERR_LIMIT
+    assert lib.w8a8_moe_re_routing_workspace_size(4, 2, 2) >= 256 + 5 * 8 + 4 * 8 + 3 * 8 + 3 * 8 + 4 * 8
     assert lib.w8a8_combine(p, p, p, p, 0, 2, 64, L.DT_BF16, None) == L.OK
     assert lib.w8a8_combine(p, p, p, p, 4, 2, 64, L.DT_F32, None) == L.ERR_INVALID
 
@@ -112,3 +116,7 @@ def test_operator_wrappers_validate_like_the_reference_plugins():
                                         torch.ones(1, 7), torch.ones(2), [2])
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         ops.dynamic_quant(torch.zeros(2, 8, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="idx_type == 0"):
+        ops.moe_re_routing(torch.zeros(2, 8, dtype=torch.int8), torch.zeros(1, 1, dtype=torch.int32), idx_type=1)
+    with pytest.raises(RuntimeError, match="must be 2D \\(N, E\\)"):
+        ops.moe_re_routing(torch.zeros(2, 8, dtype=torch.int8), torch.zeros(1, dtype=torch.int32))

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import bits
+from helpers import bits, seed_of
 
 pytestmark = pytest.mark.gpu
 F = np.float32
@@ -98,3 +98,64 @@ def test_single_gpu_chain_peer_transport_equals_collective_transport(ops):
     for _ in range(2):  # the second pass reuses the buffers of the first
         b, bx = chain.forward(*args)
         assert torch.equal(a, b) and torch.equal(ax, bx)
+
+
+@pytest.mark.parametrize("tok_dtype", [torch.int8, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cnt_dtype", [torch.int32, torch.int64])
+@pytest.mark.parametrize("n,e,h,spare", [(4, 6, 64, 0), (8, 32, 7168, 5), (1, 1, 24, 0), (3, 300, 10, 2)])
+def test_moe_re_routing_matches_oracle(ops, oracle, tok_dtype, cnt_dtype, n, e, h, spare):
+    rng = np.random.default_rng(seed_of(n, e, h, str(tok_dtype), str(cnt_dtype)))
+    cnt = rng.integers(0, 6, (n, e))
+    if n > 1:
+        cnt[rng.integers(0, n), :] = 0      # a rank that sent nothing
+    if e > 1:
+        cnt[:, rng.integers(0, e)] = 0      # an expert that received nothing
+    cnt[0, 0] += 1
+    a = int(cnt.sum()) + spare
+    if tok_dtype == torch.int8:
+        tok = rng.integers(-128, 128, (a, h)).astype(np.int8)
+    else:
+        tok = rng.integers(0, 1 << 16, (a, h)).astype(np.uint16)   # any bit pattern, NaNs included
+    scl = rng.standard_normal(a).astype(np.float32)
+    want_tok, want_scl, want_idx, want_num = oracle.moe_re_routing(tok, cnt, scl)
+    t_tok = torch.from_numpy(tok.view(np.int16) if tok.dtype == np.uint16 else tok).cuda()
+    if tok_dtype != torch.int8:
+        t_tok = t_tok.view(tok_dtype)
+    t_cnt = torch.from_numpy(cnt).to(cnt_dtype).cuda()
+    routed = a - spare
+    for with_scales in (True, False):
+        got_tok, got_scl, got_idx, got_num = ops.moe_re_routing(t_tok, t_cnt, torch.from_numpy(scl).cuda()
+                                                                if with_scales else None)
+        assert got_tok.dtype == tok_dtype and got_idx.dtype == torch.int32 and got_num.dtype == cnt_dtype
+        raw = got_tok.view(torch.int16) if tok_dtype != torch.int8 else got_tok
+        assert np.array_equal(raw.cpu().numpy().view(tok.dtype)[:routed], want_tok[:routed])
+        assert np.array_equal(got_idx.cpu().numpy()[:routed], want_idx[:routed])
+        assert np.array_equal(got_num.cpu().numpy(), want_num)
+        if with_scales:
+            assert np.array_equal(got_scl.cpu().numpy()[:routed].view(np.uint32), want_scl[:routed].view(np.uint32))
+
+
+def test_moe_re_routing_flags_bad_counts_and_empty_inputs(ops):
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    tok = torch.full((8, 32), 7, dtype=torch.int8, device="cuda")
+    out = torch.zeros_like(tok)
+    idx = torch.full((8,), -5, dtype=torch.int32, device="cuda")
+    num = torch.zeros((2,), dtype=torch.int32, device="cuda")
+    ws = torch.empty((lib.w8a8_moe_re_routing_workspace_size(8, 2, 2),), dtype=torch.uint8, device="cuda")
+    for bad in ([[5, 4], [0, 0]], [[1, -1], [2, 2]]):       # more rows than A; a negative count
+        cnt = torch.tensor(bad, dtype=torch.int32, device="cuda")
+        rc = lib.w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(), None, out.data_ptr(), None, idx.data_ptr(),
+                                     num.data_ptr(), 8, 32, 2, 2, 4, ws.data_ptr(), ws.numel(), None)
+        assert rc == L.OK
+        assert lib.w8a8_workspace_error(ws.data_ptr(), None) == 1
+        assert not out.any() and (idx == -5).all()
+    cnt = torch.tensor([[1, 2], [3, 2]], dtype=torch.int32, device="cuda")
+    rc = lib.w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(), None, out.data_ptr(), None, idx.data_ptr(),
+                                 num.data_ptr(), 8, 32, 2, 2, 4, ws.data_ptr(), ws.numel(), None)
+    assert rc == L.OK and lib.w8a8_workspace_error(ws.data_ptr(), None) == 0
+    assert (out == 7).all() and num.tolist() == [4, 4]
+    # empty token buffer: outputs come back with the reference's shapes and nothing is launched
+    e_tok, e_scl, e_idx, e_num = ops.moe_re_routing(tok[:0], torch.zeros((2, 3), dtype=torch.int64, device="cuda"))
+    assert e_tok.shape == (0, 32) and e_scl.shape == (0,) and e_idx.shape == (0,) and e_num.shape == (3,)

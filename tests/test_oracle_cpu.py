@@ -375,3 +375,32 @@ def test_combine_hand_derived(oracle):
     assert oracle.bf16_bits_to_f32(out).tolist() == [[2.25, 4.5]]
     out = oracle.combine(rows, probs, np.array([[1, -1]], np.int64), oracle.DT_BF16)
     assert oracle.bf16_bits_to_f32(out).tolist() == [[2.0, 4.0]]
+
+
+def test_moe_re_routing_hand_derived_and_against_regroup_index(oracle):
+    """Rank 0 sends 2 rows to expert 0 and 1 to expert 2; rank 1 sends 1 row to expert 0 and 3 to expert 1.
+    Source order is rank-major (rows 0-2 from rank 0, 3-6 from rank 1); the expert-major order is therefore
+    e0: [0, 1, 3], e1: [4, 5, 6], e2: [2]."""
+    cnt = np.array([[2, 0, 1], [1, 3, 0]])
+    tok = np.arange(7 * 4, dtype=np.int8).reshape(7, 4)
+    scl = np.arange(7, dtype=F) + 0.5
+    out, out_s, idx, num = oracle.moe_re_routing(tok, cnt, scl)
+    assert idx.tolist() == [0, 1, 3, 4, 5, 6, 2]
+    assert num.tolist() == [3, 3, 1]
+    assert np.array_equal(out, tok[idx]) and np.array_equal(out_s, scl[idx])
+    # the host-side index the expert-parallel chain uses is the same permutation
+    from cannbench_operator_solutions_b200.ep import regroup_index
+
+    rng = np.random.default_rng(12)
+    cnt = rng.integers(0, 5, (4, 6))
+    cnt[1, :] = 0
+    cnt[:, 2] = 0
+    a = int(cnt.sum())
+    tok = rng.integers(-128, 128, (a + 3, 16)).astype(np.int8)  # three rows past the routed total
+    out, _, idx, num = oracle.moe_re_routing(tok, cnt)
+    src_of_dst, cumsum = regroup_index(cnt)
+    assert np.array_equal(idx[:a], src_of_dst) and np.array_equal(np.cumsum(num), cumsum)
+    assert np.array_equal(out[:a], tok[idx[:a]]) and not out[a:].any()
+    assert np.array_equal(num, cnt.sum(axis=0))
+    with pytest.raises(ValueError):
+        oracle.moe_re_routing(tok[:2], cnt)

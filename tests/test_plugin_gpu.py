@@ -56,3 +56,19 @@ def test_plugin_errors_are_torch_checks(cb):
                           torch.zeros((2, 32, 16), dtype=torch.bfloat16, device="cuda"), [3, 7])
     y, s = cb.dynamic_quant(torch.empty((0, 64), dtype=torch.bfloat16, device="cuda"))
     assert y.shape == (0, 64)
+
+
+def test_plugin_moe_re_routing_matches_ctypes_operator(cb, ops):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    cnt = torch.randint(0, 9, (4, 16), generator=g, device="cuda", dtype=torch.int64)
+    a = int(cnt.sum())
+    tok = torch.randint(-128, 128, (a, 256), generator=g, device="cuda", dtype=torch.int8)
+    scl = torch.rand((a,), generator=g, device="cuda")
+    got = cb.moe_re_routing(tok, cnt, scl)
+    want = ops.moe_re_routing(tok, cnt, scl)
+    for x, y in zip(got, want):
+        assert torch.equal(x, y)
+    got = cb.moe_re_routing(tok, cnt.to(torch.int32), None, 1, 0)
+    assert torch.equal(got[0], want[0]) and got[3].dtype == torch.int32
+    with pytest.raises(RuntimeError, match="idx_type == 0"):
+        cb.moe_re_routing(tok, cnt, None, 1, 1)
