@@ -576,7 +576,77 @@ class MrrWorkload(Workload):
         return (lambda: O.moe_re_routing(tok, cnt, scl)), self.bytes_per_step() / 1e9, "all 65536 rows"
 
 
-WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
+class MfrWorkload(Workload):
+    """MoeFinalizeRouting at the combine shape of benchmark configuration 5 on one of 8 ranks: 8192 tokens, top-8,
+    bf16 rows of 7168 gathered from a 65536-row expert-major buffer, fp32 routing weights, one residual (skip1)."""
+    name, metric, unit, dtype, bound = "moe_finalize_routing", "moe_finalize_routing_hbm_gbs", "GB/s", "f32", "hbm"
+    tokens, topk, h = 8192, 8, 7168
+    kernels_per_step = 1
+    traffic = None
+    scaling = "weak"
+
+    def config(self, world):
+        return {"workload": "moe_finalize_routing: 8192 tokens x top-8 bf16 rows of 7168, fp32 scales, skip1",
+                "rows_per_gpu": self.tokens, "hidden": self.h,
+                "l2": "gathered rows (940 MB) larger than L2", "parallelism": f"replicas x{world}" if world > 1 else
+                "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        n = self.tokens * self.topk
+        self.rows = torch.randn((n, self.h), generator=g, device="cuda").to(torch.bfloat16)
+        self.skip = torch.randn((self.tokens, self.h), generator=g, device="cuda").to(torch.bfloat16)
+        self.scales = torch.rand((self.tokens, self.topk), generator=g, device="cuda")
+        self.esdr = torch.randperm(n, generator=g, device="cuda").to(torch.int32)
+        self._out = torch.empty((self.tokens, self.h), dtype=torch.bfloat16, device="cuda")
+        L = self.L
+        self._fn = L.load().w8a8_moe_finalize_routing
+        self._args = (self.rows.data_ptr(), self.esdr.data_ptr(), self.skip.data_ptr(), None, None,
+                      self.scales.data_ptr(), None, self._out.data_ptr(), self.tokens, self.h, self.topk, 0, n, 2,
+                      L.DT_BF16, L.DT_F32)
+
+    def gpu_step(self):
+        rc = self._fn(*self._args, self.torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def bytes_per_step(self):
+        return self.tokens * ((self.topk + 2) * self.h * 2 + self.topk * 8)
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def roofline_units(self):
+        return self.bytes_per_step() / 1e9
+
+    def host_inputs(self):
+        return [self.rows.cpu().pin_memory(), self.skip.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        rows = host[0].to("cuda", non_blocking=True)
+        skip = host[1].to("cuda", non_blocking=True)
+        out = self.ops.moe_finalize_routing(rows, self.esdr, skip, scales=self.scales, drop_pad_mode=2)
+        back = out.to("cpu", non_blocking=True)
+        return ((host[0].numel() + host[1].numel()) * 2, back.numel() * 2)
+
+    def cpu_sample(self, O):
+        tokens = 1024
+        rng = np.random.default_rng(0)
+        n = tokens * self.topk
+        rows = O.f32_to_bf16_bits(rng.standard_normal((n, self.h)).astype(np.float32))
+        skip = O.f32_to_bf16_bits(rng.standard_normal((tokens, self.h)).astype(np.float32))
+        scales = rng.random((tokens, self.topk)).astype(np.float32)
+        esdr = rng.permutation(n).astype(np.int32)
+        units = tokens * ((self.topk + 2) * self.h * 2 + self.topk * 8) / 1e9
+        return ((lambda: O.moe_finalize_routing(rows, esdr, O.DT_BF16, skip1=skip, scales=scales, drop_pad_mode=2)),
+                units, f"{tokens} of 8192 tokens")
+
+
+WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "mfr": MfrWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
              "chain": ChainWorkload}
 
 

@@ -395,41 +395,202 @@ __global__ void __launch_bounds__(256) rr_index_kernel(const int32_t* __restrict
     out_idx[d] = static_cast<int32_t>(s);
 }
 
-// One CTA per token; each thread owns 8-element chunks of the hidden row.
-template <int DT, bool VEC>
-__global__ void __launch_bounds__(256) combine_kernel(const uint16_t* __restrict__ rows,
-                                                      const float* __restrict__ probs,
-                                                      const int64_t* __restrict__ pos, uint16_t* __restrict__ out,
-                                                      int64_t T, int topk, int64_t H)
+// ---------------------------------------------------------------------------
+// MoeFinalizeRouting
+// (operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_kernel/moe_finalize_routing_kernel.cpp:15-25)
+// ---------------------------------------------------------------------------
+// A 16-byte chunk of a row: 8 elements of a 16-bit type or 4 floats.  Chunks are kept in registers in their raw
+// form (a uint4) while loads are in flight and unpacked to fp32 only when they are consumed.
+template <int DT>
+struct RowChunk {
+    static constexpr int EL = (DT == W8A8_DT_F32) ? 4 : 8;
+
+    template <bool VEC>
+    static __device__ __forceinline__ uint4 load_raw(const void* base, int64_t row, int c, int64_t H)
+    {
+        if constexpr (DT == W8A8_DT_F32) {
+            const float* r = static_cast<const float*>(base) + row * H;
+            if constexpr (VEC) {
+                return __ldcs(reinterpret_cast<const uint4*>(r) + c);
+            } else {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t e = static_cast<int64_t>(c) * 4 + j;
+                    w[j] = (e < H) ? __float_as_uint(r[e]) : 0u;
+                }
+                return make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+            return load_chunk16<VEC>(static_cast<const uint16_t*>(base) + row * H, c, H);
+        }
+    }
+
+    static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[EL])
+    {
+        if constexpr (DT == W8A8_DT_F32) {
+            f[0] = __uint_as_float(v.x), f[1] = __uint_as_float(v.y);
+            f[2] = __uint_as_float(v.z), f[3] = __uint_as_float(v.w);
+        } else {
+            unpack2<DT>(v.x, f[0], f[1]);
+            unpack2<DT>(v.y, f[2], f[3]);
+            unpack2<DT>(v.z, f[4], f[5]);
+            unpack2<DT>(v.w, f[6], f[7]);
+        }
+    }
+
+    template <bool VEC>
+    static __device__ __forceinline__ void load(const void* base, int64_t row, int c, int64_t H, float (&f)[EL])
+    {
+        unpack(load_raw<VEC>(base, row, c, H), f);
+    }
+
+    template <bool VEC>
+    static __device__ __forceinline__ void store(void* base, int64_t row, int c, int64_t H, const float (&f)[EL])
+    {
+        if constexpr (DT == W8A8_DT_F32) {
+            float* r = static_cast<float*>(base) + row * H;
+            if constexpr (VEC) {
+                __stcs(reinterpret_cast<float4*>(r) + c, make_float4(f[0], f[1], f[2], f[3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t e = static_cast<int64_t>(c) * 4 + j;
+                    if (e < H) {
+                        r[e] = f[j];
+                    }
+                }
+            }
+        } else {
+            const uint4 o = make_uint4(pack2<DT>(f[0], f[1]), pack2<DT>(f[2], f[3]), pack2<DT>(f[4], f[5]),
+                                       pack2<DT>(f[6], f[7]));
+            store_chunk16<VEC>(static_cast<uint16_t*>(base) + row * H, c, H, o);
+        }
+    }
+};
+
+__device__ __forceinline__ float load_scalar_as_f32(const void* p, int64_t i, int dt)
 {
-    const int nchunks = static_cast<int>((H + 7) / 8);
-    for (int64_t i = blockIdx.x; i < T; i += gridDim.x) {
-        for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                acc[j] = 0.0f;
-            }
-            for (int k = 0; k < topk; ++k) {
-                const int64_t p = pos[i * topk + k];
-                if (p < 0) {
-                    continue;
+    if (dt == W8A8_DT_F32) {
+        return static_cast<const float*>(p)[i];
+    }
+    const uint32_t b = static_cast<const uint16_t*>(p)[i];
+    return (dt == W8A8_DT_BF16) ? bits16_to_float<W8A8_DT_BF16>(b) : bits16_to_float<W8A8_DT_F16>(b);
+}
+
+// One CTA per output row.  The K (position, scale, expert) triples of the row are staged in shared memory once;
+// every thread then owns 16-byte chunks of the hidden dimension and, for MFR_BATCH values of k at a time, issues
+// all its row (and bias) loads before it touches the accumulator, so up to MFR_BATCH gathers are in flight per
+// thread.  Arithmetic order per element: acc = fp32(skip1); acc += fp32(skip2); for ascending k:
+// term = fp32(row) [+ fp32(bias)]; term *= scale; acc += term (no fused multiply-add); RNE store.
+constexpr int MFR_BATCH = 8;
+constexpr int MFR_MAX_STAGED_K = 128;
+
+template <int DT, bool VEC, bool HAS_BIAS, typename IdxT>
+__global__ void __launch_bounds__(256) mfr_kernel(const void* __restrict__ rows, const IdxT* __restrict__ esdr,
+                                                  const void* __restrict__ skip1, const void* __restrict__ skip2,
+                                                  const void* __restrict__ bias, const void* __restrict__ scales,
+                                                  const int32_t* __restrict__ expert, void* __restrict__ out,
+                                                  int64_t R, int64_t H, int K, int64_t E, int64_t num_dst,
+                                                  int col_mode, int scale_dt)
+{
+    using C = RowChunk<DT>;
+    constexpr int EL = C::EL;
+    __shared__ int64_t s_pos[MFR_MAX_STAGED_K];
+    __shared__ int64_t s_eid[MFR_MAX_STAGED_K];
+    __shared__ float s_w[MFR_MAX_STAGED_K];
+    const int nchunks = static_cast<int>((H + EL - 1) / EL);
+    for (int64_t i = blockIdx.x; i < R; i += gridDim.x) {
+        for (int k0 = 0; k0 < K; k0 += MFR_MAX_STAGED_K) {
+            const int kn = min(K - k0, MFR_MAX_STAGED_K);
+            __syncthreads();
+            if (static_cast<int>(threadIdx.x) < kn) {
+                const int k = k0 + threadIdx.x;
+                int64_t p = esdr[col_mode ? (static_cast<int64_t>(k) * R + i) : (i * K + k)];
+                if (p < 0 || p >= num_dst) {
+                    p = -1;
                 }
-                const float w = probs[i * topk + k];
-                const uint4 v = load_chunk16<VEC>(rows + p * H, c, H);
-                float f[8];
-                unpack2<DT>(v.x, f[0], f[1]);
-                unpack2<DT>(v.y, f[2], f[3]);
-                unpack2<DT>(v.z, f[4], f[5]);
-                unpack2<DT>(v.w, f[6], f[7]);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    acc[j] = __fadd_rn(acc[j], __fmul_rn(w, f[j]));
+                int64_t eid = -1;
+                if constexpr (HAS_BIAS) {
+                    eid = expert[i * K + k];
+                    if (eid < 0 || eid >= E) {
+                        eid = -1;
+                    }
                 }
+                s_pos[threadIdx.x] = p;
+                s_eid[threadIdx.x] = eid;
+                s_w[threadIdx.x] = (scales != nullptr) ? load_scalar_as_f32(scales, i * K + k, scale_dt) : 1.0f;
             }
-            const uint4 o = make_uint4(pack2<DT>(acc[0], acc[1]), pack2<DT>(acc[2], acc[3]),
-                                       pack2<DT>(acc[4], acc[5]), pack2<DT>(acc[6], acc[7]));
-            store_chunk16<VEC>(out + i * H, c, H, o);
+            __syncthreads();
+            for (int c = threadIdx.x; c < nchunks; c += blockDim.x) {
+                float acc[EL];
+                if (k0 == 0) {
+                    if (skip1 != nullptr) {
+                        C::template load<VEC>(skip1, i, c, H, acc);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < EL; ++j) {
+                            acc[j] = 0.0f;
+                        }
+                    }
+                    if (skip2 != nullptr) {
+                        float t[EL];
+                        C::template load<VEC>(skip2, i, c, H, t);
+#pragma unroll
+                        for (int j = 0; j < EL; ++j) {
+                            acc[j] = __fadd_rn(acc[j], t[j]);
+                        }
+                    }
+                } else {
+                    // more than MFR_MAX_STAGED_K terms: the partial sum so far is in `out` as fp32 only when the
+                    // output type is fp32; other types take the single-pass route below (K is limited by the host)
+                    C::template load<VEC>(out, i, c, H, acc);
+                }
+                for (int kb = 0; kb < kn; kb += MFR_BATCH) {
+                    uint4 v[MFR_BATCH];
+                    uint4 b[HAS_BIAS ? MFR_BATCH : 1];
+#pragma unroll
+                    for (int u = 0; u < MFR_BATCH; ++u) {
+                        const int k = kb + u;
+                        if (k < kn && s_pos[k] >= 0) {
+                            v[u] = C::template load_raw<VEC>(rows, s_pos[k], c, H);
+                            if constexpr (HAS_BIAS) {
+                                if (s_eid[k] >= 0) {
+                                    b[u] = C::template load_raw<VEC>(bias, s_eid[k], c, H);
+                                }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < MFR_BATCH; ++u) {
+                        const int k = kb + u;
+                        if (k < kn && s_pos[k] >= 0) {
+                            const bool add_bias = HAS_BIAS && s_eid[k] >= 0;
+                            const float w = s_w[k];
+                            float vf[EL];
+                            float bf[EL];
+                            C::unpack(v[u], vf);
+                            if constexpr (HAS_BIAS) {
+                                if (add_bias) {
+                                    C::unpack(b[u], bf);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < EL; ++j) {
+                                float term = vf[j];
+                                if (add_bias) {
+                                    term = __fadd_rn(term, bf[j]);
+                                }
+                                if (scales != nullptr) {
+                                    term = __fmul_rn(term, w);
+                                }
+                                acc[j] = __fadd_rn(acc[j], term);
+                            }
+                        }
+                    }
+                }
+                C::template store<VEC>(out, i, c, H, acc);
+            }
         }
     }
 }
@@ -617,22 +778,17 @@ extern "C" int w8a8_combine(const void* rows, const float* probs, const int64_t*
     const bool vec = (H % 8 == 0) && w8a8::is_aligned(rows, 16) && w8a8::is_aligned(out, 16);
     const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
     const unsigned grid = static_cast<unsigned>(T < cap ? T : cap);
-    const uint16_t* r = static_cast<const uint16_t*>(rows);
-    uint16_t* o = static_cast<uint16_t*>(out);
-    const int tk = static_cast<int>(topk);
-    if (dtype == W8A8_DT_BF16) {
-        if (vec) {
-            w8a8::combine_kernel<W8A8_DT_BF16, true><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
-        } else {
-            w8a8::combine_kernel<W8A8_DT_BF16, false><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
-        }
-    } else {
-        if (vec) {
-            w8a8::combine_kernel<W8A8_DT_F16, true><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
-        } else {
-            w8a8::combine_kernel<W8A8_DT_F16, false><<<grid, 256, 0, st>>>(r, probs, expanded_pos, o, T, tk, H);
-        }
+    // The scales-only, row-arranged case of the finalize kernel with 64-bit positions (no upper bound on them).
+    if (topk > w8a8::MFR_MAX_STAGED_K) {
+        return W8A8_ERR_LIMIT;
     }
+    auto kern = (dtype == W8A8_DT_BF16)
+                    ? (vec ? w8a8::mfr_kernel<W8A8_DT_BF16, true, false, int64_t>
+                           : w8a8::mfr_kernel<W8A8_DT_BF16, false, false, int64_t>)
+                    : (vec ? w8a8::mfr_kernel<W8A8_DT_F16, true, false, int64_t>
+                           : w8a8::mfr_kernel<W8A8_DT_F16, false, false, int64_t>);
+    kern<<<grid, 256, 0, st>>>(rows, expanded_pos, nullptr, nullptr, nullptr, probs, nullptr, out, T, H,
+                               static_cast<int>(topk), 0, INT64_MAX, 0, W8A8_DT_F32);
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -713,4 +869,69 @@ extern "C" int w8a8_moe_re_routing(const void* tokens, const void* counts, const
     }
     return w8a8_permute_rows(tokens, scales, out_tokens, (scales != nullptr) ? out_scales : nullptr, index, A,
                              row_bytes, stream);
+}
+
+template <int DT>
+static int launch_mfr(const void* rows, const int32_t* esdr, const void* skip1, const void* skip2, const void* bias,
+                      const void* scales, const int32_t* expert, void* out, int64_t R, int64_t H, int64_t K, int64_t E,
+                      int64_t num_dst, int col_mode, int scale_dt, bool vec, cudaStream_t st)
+{
+    const int64_t cap = static_cast<int64_t>(w8a8::sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(R < cap ? R : cap);
+    const bool has_bias = (bias != nullptr) && (expert != nullptr);
+    auto kern = vec ? (has_bias ? w8a8::mfr_kernel<DT, true, true, int32_t> : w8a8::mfr_kernel<DT, true, false, int32_t>)
+                    : (has_bias ? w8a8::mfr_kernel<DT, false, true, int32_t>
+                                : w8a8::mfr_kernel<DT, false, false, int32_t>);
+    kern<<<grid, 256, 0, st>>>(rows, esdr, skip1, skip2, bias, scales, expert, out, R, H, static_cast<int>(K), E,
+                               num_dst, col_mode, scale_dt);
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int w8a8_moe_finalize_routing(const void* rows, const int32_t* src_to_dst_row, const void* skip1,
+                                         const void* skip2, const void* bias, const void* scales,
+                                         const int32_t* expert_for_source_row, void* out, int64_t num_rows, int64_t H,
+                                         int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode, int dtype,
+                                         int scale_dtype, void* stream)
+{
+    if (dtype != W8A8_DT_F16 && dtype != W8A8_DT_BF16 && dtype != W8A8_DT_F32) {
+        return W8A8_ERR_INVALID;
+    }
+    if (scales != nullptr && scale_dtype != W8A8_DT_F16 && scale_dtype != W8A8_DT_BF16 &&
+        scale_dtype != W8A8_DT_F32) {
+        return W8A8_ERR_INVALID;
+    }
+    if (num_rows < 0 || H <= 0 || K <= 0 || E < 0 || num_dst < 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (K > w8a8::MFR_MAX_STAGED_K && dtype != W8A8_DT_F32) {
+        return W8A8_ERR_LIMIT;  // a 16-bit output cannot carry the fp32 partial sum between passes
+    }
+    if (num_rows == 0) {
+        return W8A8_OK;
+    }
+    if (rows == nullptr || src_to_dst_row == nullptr || out == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    const size_t elem = (dtype == W8A8_DT_F32) ? 4 : 2;
+    const void* ptrs[5] = {rows, skip1, skip2, bias, out};
+    bool vec = (H * static_cast<int64_t>(elem)) % 16 == 0;
+    for (const void* q : ptrs) {
+        if (q != nullptr && !w8a8::is_aligned(q, elem)) {
+            return W8A8_ERR_ALIGN;
+        }
+        vec = vec && (q == nullptr || w8a8::is_aligned(q, 16));
+    }
+    const int col_mode = (drop_pad_mode <= 1) ? 1 : 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case W8A8_DT_F16:
+        return launch_mfr<W8A8_DT_F16>(rows, src_to_dst_row, skip1, skip2, bias, scales, expert_for_source_row, out,
+                                       num_rows, H, K, E, num_dst, col_mode, scale_dtype, vec, st);
+    case W8A8_DT_BF16:
+        return launch_mfr<W8A8_DT_BF16>(rows, src_to_dst_row, skip1, skip2, bias, scales, expert_for_source_row, out,
+                                        num_rows, H, K, E, num_dst, col_mode, scale_dtype, vec, st);
+    default:
+        return launch_mfr<W8A8_DT_F32>(rows, src_to_dst_row, skip1, skip2, bias, scales, expert_for_source_row, out,
+                                       num_rows, H, K, E, num_dst, col_mode, scale_dtype, vec, st);
+    }
 }

@@ -10,6 +10,7 @@
 //   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:38-150
 //   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:40-190
 //   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:32-170
+//   moe_finalize_routing        operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:31-237
 // The NPU plugins enqueue their launchers with OpCommand::RunOpApi on the
 // current NPU stream; here the C-ABI call is enqueued on the current CUDA
 // stream.  The plugin only unpacks tensors: all arithmetic is in the library.
@@ -462,8 +463,107 @@ static RrOut moe_re_routing_cuda(const torch::Tensor& tokens, const torch::Tenso
     return outs;
 }
 
+// ---------------------------------------------------------- moe_finalize_routing
+static bool present(const c10::optional<torch::Tensor>& t)
+{
+    return t.has_value() && t->defined();
+}
+
+static void mfr_shape(const torch::Tensor& epr, const torch::Tensor& esdr, const c10::optional<torch::Tensor>& scales,
+                      int64_t& num_rows, int64_t& K, int64_t& H)
+{
+    TORCH_CHECK(epr.dim() >= 2, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
+    TORCH_CHECK(esdr.scalar_type() == torch::kInt, "moe_finalize_routing: expanded_src_to_dst_row must be int32.");
+    H = epr.size(-1);
+    K = 1;
+    if (present(scales)) {
+        TORCH_CHECK(scales->dim() == 2, "moe_finalize_routing: scales must be 2-D (NUM_ROWS, K).");
+        K = scales->size(1);
+    }
+    TORCH_CHECK(K > 0, "moe_finalize_routing: K must be positive.");
+    TORCH_CHECK(esdr.numel() % K == 0, "moe_finalize_routing: expanded_src_to_dst_row length must be K*NUM_ROWS.");
+    num_rows = esdr.numel() / K;
+}
+
+static torch::Tensor mfr_meta(const torch::Tensor& epr, const torch::Tensor& esdr, c10::optional<torch::Tensor> skip1,
+                              c10::optional<torch::Tensor> skip2, c10::optional<torch::Tensor> bias,
+                              c10::optional<torch::Tensor> scales, c10::optional<torch::Tensor> expert,
+                              int64_t drop_pad_mode)
+{
+    (void)skip1;
+    (void)skip2;
+    (void)bias;
+    (void)expert;
+    (void)drop_pad_mode;
+    int64_t num_rows = 0, K = 1, H = 0;
+    mfr_shape(epr, esdr, scales, num_rows, K, H);
+    return torch::empty({num_rows, H}, epr.options());
+}
+
+static torch::Tensor mfr_cuda(const torch::Tensor& rows, const torch::Tensor& src_to_dst,
+                              c10::optional<torch::Tensor> skip1, c10::optional<torch::Tensor> skip2,
+                              c10::optional<torch::Tensor> bias, c10::optional<torch::Tensor> scales,
+                              c10::optional<torch::Tensor> expert, int64_t drop_pad_mode)
+{
+    const auto t = rows.scalar_type();
+    TORCH_CHECK(t == torch::kFloat16 || t == torch::kFloat32 || t == torch::kBFloat16,
+                "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.");
+    const c10::cuda::OptionalCUDAGuard guard(rows.device());
+    auto epr = rows.contiguous();
+    auto esdr = src_to_dst.contiguous();
+    int64_t num_rows = 0, K = 1, H = 0;
+    mfr_shape(epr, esdr, scales, num_rows, K, H);
+    auto out = torch::empty({num_rows, H}, epr.options());
+    if (num_rows <= 0 || H <= 0) {
+        return out;
+    }
+    const bool has_scales = present(scales);
+    const bool has_expert = present(expert);
+    const bool has_bias = present(bias) && has_expert;
+    if (has_bias) {
+        TORCH_CHECK(bias->size(1) == H, "moe_finalize_routing: bias head dim must equal H.");
+        TORCH_CHECK(bias->scalar_type() == t, "moe_finalize_routing: bias must have the rows' dtype.");
+        TORCH_CHECK(expert->scalar_type() == torch::kInt, "moe_finalize_routing: expert_for_source_row must be int32.");
+    }
+    TORCH_CHECK(!present(skip1) || skip1->scalar_type() == t, "moe_finalize_routing: skip1 must have the rows' dtype.");
+    TORCH_CHECK(!present(skip2) || skip2->scalar_type() == t, "moe_finalize_routing: skip2 must have the rows' dtype.");
+    torch::Tensor s1, s2, bs, sc, ex;
+    if (present(skip1)) {
+        s1 = skip1->contiguous();
+    }
+    if (present(skip2)) {
+        s2 = skip2->contiguous();
+    }
+    if (has_bias) {
+        bs = bias->contiguous();
+        ex = expert->contiguous();
+    }
+    int sdt = dtype_code(epr);
+    if (has_scales) {
+        sc = scales->contiguous();
+        const auto st = sc.scalar_type();
+        TORCH_CHECK(st == torch::kFloat16 || st == torch::kFloat32 || st == torch::kBFloat16,
+                    "moe_finalize_routing: unsupported dtype combination for expanded_permuted_rows / scales.");
+        sdt = dtype_code(sc);
+    }
+    const int64_t mode = drop_pad_mode < 0 ? 0 : (drop_pad_mode > 3 ? 3 : drop_pad_mode);
+    check_status(w8a8_moe_finalize_routing(epr.data_ptr(), static_cast<const int32_t*>(esdr.data_ptr()),
+                                           s1.defined() ? s1.data_ptr() : nullptr,
+                                           s2.defined() ? s2.data_ptr() : nullptr,
+                                           has_bias ? bs.data_ptr() : nullptr, has_scales ? sc.data_ptr() : nullptr,
+                                           has_bias ? static_cast<const int32_t*>(ex.data_ptr()) : nullptr,
+                                           out.data_ptr(), num_rows, H, K, has_bias ? bs.size(0) : 0,
+                                           epr.numel() / H, static_cast<int>(mode), dtype_code(epr), sdt,
+                                           stream_of(epr)),
+                 "moe_finalize_routing");
+    return out;
+}
+
 TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 {
+    m.def("moe_finalize_routing(Tensor expanded_permuted_rows, Tensor expanded_src_to_dst_row, "
+          "Tensor? skip1=None, Tensor? skip2=None, Tensor? bias=None, Tensor? scales=None, "
+          "Tensor? expert_for_source_row=None, int drop_pad_mode=0) -> Tensor out");
     m.def("moe_re_routing(Tensor tokens, Tensor expert_token_num_per_rank, Tensor? per_token_scales=None, "
           "int expert_token_num_type=1, int idx_type=0) -> (Tensor, Tensor, Tensor, Tensor)");
     m.def("dynamic_quant(Tensor x) -> (Tensor y, Tensor scale)");
@@ -487,6 +587,7 @@ TORCH_LIBRARY_IMPL(cann_bench, Meta, m)
     m.impl("grouped_matmul_swiglu_quant", gmsq_meta);
     m.impl("grouped_matmul", grouped_matmul_meta);
     m.impl("moe_re_routing", moe_re_routing_meta);
+    m.impl("moe_finalize_routing", mfr_meta);
 }
 
 TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
@@ -497,6 +598,7 @@ TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
     m.impl("grouped_matmul_swiglu_quant", gmsq_cuda);
     m.impl("grouped_matmul", grouped_matmul_cuda);
     m.impl("moe_re_routing", moe_re_routing_cuda);
+    m.impl("moe_finalize_routing", mfr_cuda);
 }
 
 }  // namespace cann_bench

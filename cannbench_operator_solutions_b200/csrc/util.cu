@@ -43,7 +43,7 @@ extern "C" const char* w8a8_status_string(int status)
     case W8A8_ERR_UNSUPPORTED:
         return "configuration not supported by this build";
     case W8A8_ERR_LIMIT:
-        return "problem exceeds the fixed capacity of this entry point (see W8A8_STATIC_SCRATCH_BYTES)";
+        return "problem exceeds a fixed capacity limit of this entry point (see its declaration in w8a8ffn.h)";
     default:
         return "unknown status";
     }

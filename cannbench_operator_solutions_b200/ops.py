@@ -363,3 +363,63 @@ def moe_re_routing(tokens: torch.Tensor, expert_token_num_per_rank: torch.Tensor
                                      workspace.numel() * workspace.element_size(), _stream())
     _status(rc, "moe_re_routing")
     return out_tok, out_scl, out_idx, out_num
+
+
+def moe_finalize_routing(expanded_permuted_rows: torch.Tensor, expanded_src_to_dst_row: torch.Tensor,
+                         skip1: Optional[torch.Tensor] = None, skip2: Optional[torch.Tensor] = None,
+                         bias: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None,
+                         expert_for_source_row: Optional[torch.Tensor] = None, drop_pad_mode: int = 0) -> torch.Tensor:
+    """``moe_finalize_routing(Tensor expanded_permuted_rows, Tensor expanded_src_to_dst_row, Tensor? skip1=None,
+    Tensor? skip2=None, Tensor? bias=None, Tensor? scales=None, Tensor? expert_for_source_row=None,
+    int drop_pad_mode=0) -> Tensor out``
+    (operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:31-36,
+    40-58 for the shape rules, 96-215 for the checks).
+
+    ``out[i] = skip1[i] + skip2[i] + sum_k scales[i, k] * (rows[p(i, k)] + bias[expert[i, k]])``; K is
+    ``scales.size(1)`` (1 without scales), ``num_rows = expanded_src_to_dst_row.numel() / K``; ``drop_pad_mode`` is
+    clamped to 0..3 (0/1: index arranged [K, num_rows], 2/3: [num_rows, K]); bias is only applied together with
+    ``expert_for_source_row``."""
+    epr = expanded_permuted_rows
+    _check(epr.dtype in (torch.float16, torch.float32, torch.bfloat16),
+           "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.")
+    _check(epr.dim() >= 2, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.")
+    _check(expanded_src_to_dst_row.dtype == torch.int32,
+           "moe_finalize_routing: expanded_src_to_dst_row must be int32.")
+    h = epr.size(-1)
+    nk = expanded_src_to_dst_row.numel()
+    k = 1
+    if scales is not None:
+        _check(scales.dim() == 2, "moe_finalize_routing: scales must be 2-D (NUM_ROWS, K).")
+        k = scales.size(1)
+    _check(k > 0, "moe_finalize_routing: K must be positive.")
+    _check(nk % k == 0, "moe_finalize_routing: expanded_src_to_dst_row length must be K*NUM_ROWS.")
+    num_rows = nk // k
+    _need_cuda(epr, expanded_src_to_dst_row, skip1, skip2, bias, scales, expert_for_source_row)
+    out = torch.empty((num_rows, h), dtype=epr.dtype, device=epr.device)
+    if num_rows <= 0 or h <= 0:
+        return out
+    eprc = epr.contiguous()
+    esdr = expanded_src_to_dst_row.contiguous()
+    has_bias = bias is not None and expert_for_source_row is not None
+    if has_bias:
+        _check(bias.size(1) == h, "moe_finalize_routing: bias head dim must equal H.")
+    for name, t in (("skip1", skip1), ("skip2", skip2), ("bias", bias if has_bias else None)):
+        _check(t is None or t.dtype == epr.dtype, f"moe_finalize_routing: {name} must have the rows' dtype.")
+    if scales is not None:
+        _check(scales.dtype in (torch.float16, torch.float32, torch.bfloat16),
+               "moe_finalize_routing: unsupported dtype combination for expanded_permuted_rows / scales.")
+    if expert_for_source_row is not None:
+        _check(expert_for_source_row.dtype == torch.int32, "moe_finalize_routing: expert_for_source_row must be int32.")
+    mode = min(max(int(drop_pad_mode), 0), 3)
+    s1 = skip1.contiguous() if skip1 is not None else None
+    s2 = skip2.contiguous() if skip2 is not None else None
+    bs = bias.contiguous() if has_bias else None
+    sc = scales.contiguous() if scales is not None else None
+    ex = expert_for_source_row.contiguous() if expert_for_source_row is not None else None
+    with torch.cuda.device(epr.device):
+        rc = L.load().w8a8_moe_finalize_routing(eprc.data_ptr(), esdr.data_ptr(), _ptr(s1), _ptr(s2), _ptr(bs), _ptr(sc),
+                                                _ptr(ex) if has_bias else None, out.data_ptr(), num_rows, h, k,
+                                                bs.size(0) if has_bias else 0, eprc.numel() // h, mode, _dt(eprc),
+                                                _dt(sc) if sc is not None else _dt(eprc), _stream())
+    _status(rc, "moe_finalize_routing")
+    return out

@@ -298,6 +298,23 @@ int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const void* bias, 
 int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,
                  int64_t T, int64_t topk, int64_t H, int dtype, void* stream);
 
+/*
+ * MoeFinalizeRouting: out[i, :] = skip1[i, :] + skip2[i, :] + sum_k scales[i, k] * (rows[p(i, k), :] +
+ * bias[expert_for_source_row[i, k], :]) with p(i, k) = src_to_dst_row[k * num_rows + i] for drop_pad_mode 0 / 1 and
+ * src_to_dst_row[i * K + k] for 2 / 3.  fp32 throughout, ascending k, each term formed as (row + bias) * scale and
+ * then added (no fused multiply-add), round-to-nearest-even store.  p outside [0, num_dst) drops the term, an
+ * expert id outside [0, E) drops only its bias.  skip1, skip2, bias (needs expert_for_source_row) and scales are
+ * optional; without scales K is 1.  rows / skips / bias / out share `dtype` (F16, BF16 or F32), scales have
+ * `scale_dtype`.  Replaces the nine launch_mfr_<rows type>_<scale type> launchers
+ * (operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_kernel/moe_finalize_routing_launch.h; formula in
+ * moe_finalize_routing_kernel.cpp:15-25).  K above 128 is accepted for F32 rows only (W8A8_ERR_LIMIT otherwise).
+ */
+int w8a8_moe_finalize_routing(const void* rows, const int32_t* src_to_dst_row, const void* skip1,
+                              const void* skip2, const void* bias, const void* scales,
+                              const int32_t* expert_for_source_row, void* out, int64_t num_rows, int64_t H,
+                              int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode, int dtype,
+                              int scale_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

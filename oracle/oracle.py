@@ -84,6 +84,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_combine.argtypes = [vp, vp, vp, vp, i64, i64, i64, i32]
     lib.oracle_moe_re_routing.restype = i32
     lib.oracle_moe_re_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64]
+    lib.oracle_moe_finalize_routing.restype = i32
+    lib.oracle_moe_finalize_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
     lib.oracle_num_threads.restype = i32
     _lib = lib
     return lib
@@ -280,3 +282,31 @@ def moe_re_routing(tokens: np.ndarray, counts: np.ndarray, scales: Optional[np.n
     if rc != 0:
         raise ValueError("oracle_moe_re_routing rejected the arguments")
     return out, out_s, idx, num
+
+
+def moe_finalize_routing(rows, esdr, dtype: int, *, skip1=None, skip2=None, bias=None, scales=None,
+                         scale_dtype: int = DT_F32, expert=None, drop_pad_mode: int = 0):
+    """rows [num_dst, H] as uint16 bit patterns (F16 / BF16) or float32 (F32); esdr int32 [K * R]; scales [R, K] in
+    scale_dtype's representation.  Returns out [R, H] in rows' representation."""
+    np_t = np.float32 if dtype == DT_F32 else np.uint16
+    rows = _c(rows, np_t)
+    esdr = _c(esdr, np.int32)
+    h = rows.shape[-1]
+    num_dst = rows.size // h
+    k = 1
+    sc = None
+    if scales is not None:
+        sc = _c(scales, np.float32 if scale_dtype == DT_F32 else np.uint16)
+        k = sc.shape[1]
+    r = esdr.size // k
+    s1 = None if skip1 is None else _c(skip1, np_t)
+    s2 = None if skip2 is None else _c(skip2, np_t)
+    bs = None if bias is None else _c(bias, np_t)
+    ex = None if expert is None else _c(expert, np.int32)
+    e = 0 if bs is None else bs.shape[0]
+    out = np.empty((r, h), np_t)
+    rc = load().oracle_moe_finalize_routing(_p(rows), _p(esdr), _p(s1), _p(s2), _p(bs), _p(sc), _p(ex), _p(out), r, h,
+                                            k, e, num_dst, drop_pad_mode, dtype, scale_dtype)
+    if rc != 0:
+        raise ValueError("oracle_moe_finalize_routing rejected the arguments")
+    return out

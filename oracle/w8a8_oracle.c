@@ -851,3 +851,59 @@ int oracle_moe_re_routing(const void* tokens, const int64_t* counts, const float
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* MoeFinalizeRouting                                                        */
+/* MFR/op_kernel/moe_finalize_routing_kernel.cpp:15-25 (formula), :133-181   */
+/* (one term: fp32(row) [+ fp32(bias[eid])], then * fp32(scale), then added   */
+/* to the accumulator), :231-245 (accumulator starts as fp32(skip1) and       */
+/* fp32(skip2) is added to it), :432-437 (round-to-nearest-even store).       */
+/*   p(i,k) = esdr[k*R + i] (drop_pad_mode 0/1) or esdr[i*K + k] (2/3);       */
+/*   p outside [0, num_dst) drops the whole term; eid outside [0, E) drops    */
+/*   only the bias; scales / expert are indexed [i*K + k] in every mode.      */
+/* ------------------------------------------------------------------------ */
+int oracle_moe_finalize_routing(const void* rows, const int32_t* esdr, const void* skip1, const void* skip2,
+                                const void* bias, const void* scales, const int32_t* expert, void* out,
+                                int64_t R, int64_t H, int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode,
+                                int dtype, int scale_dtype)
+{
+    if (dtype != W8A8_DT_F16 && dtype != W8A8_DT_BF16 && dtype != W8A8_DT_F32) {
+        return -1;
+    }
+    if (scales != NULL && scale_dtype != W8A8_DT_F16 && scale_dtype != W8A8_DT_BF16 && scale_dtype != W8A8_DT_F32) {
+        return -1;
+    }
+    if (R < 0 || H <= 0 || K <= 0 || num_dst < 0) {
+        return -1;
+    }
+    const int col_mode = (drop_pad_mode <= 1);
+    const int has_bias = (bias != NULL && expert != NULL);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < R; ++i) {
+        for (int64_t c = 0; c < H; ++c) {
+            float acc = (skip1 != NULL) ? load_as_f32(skip1, i * H + c, dtype) : 0.0f;
+            if (skip2 != NULL) {
+                acc = acc + load_as_f32(skip2, i * H + c, dtype);
+            }
+            for (int64_t k = 0; k < K; ++k) {
+                const int64_t p = esdr[col_mode ? (k * R + i) : (i * K + k)];
+                if (p < 0 || p >= num_dst) {
+                    continue;
+                }
+                float term = load_as_f32(rows, p * H + c, dtype);
+                if (has_bias) {
+                    const int64_t eid = expert[i * K + k];
+                    if (eid >= 0 && eid < E) {
+                        term = term + load_as_f32(bias, eid * H + c, dtype);
+                    }
+                }
+                if (scales != NULL) {
+                    term = term * load_as_f32(scales, i * K + k, scale_dtype);
+                }
+                acc = acc + term;
+            }
+            store_from_f32(out, i * H + c, dtype, acc);
+        }
+    }
+    return 0;
+}

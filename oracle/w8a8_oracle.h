@@ -113,6 +113,13 @@ int oracle_moe_re_routing(const void* tokens, const int64_t* counts, const float
                           float* out_scales, int32_t* out_idx, int64_t* expert_token_num, int64_t A,
                           int64_t row_bytes, int64_t N, int64_t E);
 
+/* MoeFinalizeRouting: out[i] = skip1[i] + skip2[i] + sum_k scales[i,k] * (rows[p(i,k)] + bias[expert[i,k]]),
+ * fp32, ascending k, RNE store.  Every optional operand may be NULL (bias needs expert). */
+int oracle_moe_finalize_routing(const void* rows, const int32_t* esdr, const void* skip1, const void* skip2,
+                                const void* bias, const void* scales, const int32_t* expert, void* out,
+                                int64_t R, int64_t H, int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode,
+                                int dtype, int scale_dtype);
+
 int oracle_num_threads(void);
 
 #ifdef __cplusplus

@@ -92,6 +92,16 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_moe_re_routing(p, p, None, p, None, p, p, 4, 64, 2, 2, 4, p, 16, None) == L.ERR_WORKSPACE
     assert lib.w8a8_moe_re_routing(p, p, None, p, None, p, p, 1 << 31, 64, 2, 2, 4, p, 1 << 40, None) == L.ERR_LIMIT
     assert lib.w8a8_moe_re_routing_workspace_size(4, 2, 2) >= 256 + 5 * 8 + 4 * 8 + 3 * 8 + 3 * 8 + 4 * 8
+    assert lib.w8a8_moe_finalize_routing(p, p, None, None, None, None, None, p, 0, 64, 1, 0, 8, 0, L.DT_BF16,
+                                         L.DT_F32, None) == L.OK
+    assert lib.w8a8_moe_finalize_routing(p, p, None, None, None, None, None, p, 4, 64, 1, 0, 8, 0, L.DT_I8,
+                                         L.DT_F32, None) == L.ERR_INVALID
+    assert lib.w8a8_moe_finalize_routing(p, p, None, None, None, p, None, p, 4, 64, 2, 0, 8, 0, L.DT_BF16,
+                                         L.DT_I8, None) == L.ERR_INVALID
+    assert lib.w8a8_moe_finalize_routing(p, p, None, None, None, p, None, p, 4, 64, 129, 0, 8, 0, L.DT_BF16,
+                                         L.DT_F32, None) == L.ERR_LIMIT
+    assert lib.w8a8_moe_finalize_routing(p + 1, p, None, None, None, None, None, p, 4, 64, 1, 0, 8, 0, L.DT_BF16,
+                                         L.DT_F32, None) == L.ERR_ALIGN
     assert lib.w8a8_combine(p, p, p, p, 0, 2, 64, L.DT_BF16, None) == L.OK
     assert lib.w8a8_combine(p, p, p, p, 4, 2, 64, L.DT_F32, None) == L.ERR_INVALID
 
@@ -120,3 +130,9 @@ def test_operator_wrappers_validate_like_the_reference_plugins():
         ops.moe_re_routing(torch.zeros(2, 8, dtype=torch.int8), torch.zeros(1, 1, dtype=torch.int32), idx_type=1)
     with pytest.raises(RuntimeError, match="must be 2D \\(N, E\\)"):
         ops.moe_re_routing(torch.zeros(2, 8, dtype=torch.int8), torch.zeros(1, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="must be int32"):
+        ops.moe_finalize_routing(torch.zeros(4, 8), torch.zeros(4, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="float16 / float32 / bfloat16"):
+        ops.moe_finalize_routing(torch.zeros(4, 8, dtype=torch.int8), torch.zeros(4, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="K\\*NUM_ROWS"):
+        ops.moe_finalize_routing(torch.zeros(4, 8), torch.zeros(5, dtype=torch.int32), scales=torch.zeros(2, 2))

@@ -159,3 +159,84 @@ def test_moe_re_routing_flags_bad_counts_and_empty_inputs(ops):
     # empty token buffer: outputs come back with the reference's shapes and nothing is launched
     e_tok, e_scl, e_idx, e_num = ops.moe_re_routing(tok[:0], torch.zeros((2, 3), dtype=torch.int64, device="cuda"))
     assert e_tok.shape == (0, 32) and e_scl.shape == (0,) and e_idx.shape == (0,) and e_num.shape == (3,)
+
+
+_T = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}
+
+
+def _to_oracle(t: torch.Tensor):
+    return t.cpu().numpy() if t.dtype == torch.float32 else bits(t)
+
+
+def _code(oracle, dt):
+    return {torch.float16: oracle.DT_F16, torch.bfloat16: oracle.DT_BF16, torch.float32: oracle.DT_F32}[dt]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("scale_dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("mode", [0, 2])
+@pytest.mark.parametrize("r,k,h,e", [(33, 8, 7168, 16), (7, 3, 100, 4), (5, 1, 8, 2), (64, 20, 256, 300)])
+def test_moe_finalize_routing_matches_oracle(ops, oracle, dtype, scale_dtype, mode, r, k, h, e):
+    g = torch.Generator(device="cuda").manual_seed(seed_of(_T[dtype], _T[scale_dtype], mode, r, k, h, e))
+    num_dst = r * k + 3
+    rows = torch.randn((num_dst, h), generator=g, device="cuda").to(dtype)
+    skip1 = torch.randn((r, h), generator=g, device="cuda").to(dtype)
+    skip2 = torch.randn((r, h), generator=g, device="cuda").to(dtype)
+    bias = torch.randn((e, h), generator=g, device="cuda").to(dtype)
+    scales = torch.rand((r, k), generator=g, device="cuda").to(scale_dtype)
+    esdr = torch.randint(-2, num_dst + 2, (r * k,), generator=g, device="cuda", dtype=torch.int32)  # some dropped
+    expert = torch.randint(-1, e + 1, (r, k), generator=g, device="cuda", dtype=torch.int32)          # some no-bias
+    variants = [dict(skip1=skip1, skip2=skip2, bias=bias, scales=scales, expert_for_source_row=expert),
+                dict(scales=scales),
+                dict(skip2=skip2, scales=scales, bias=bias),          # bias without expert ids: ignored
+                dict(skip1=skip1, bias=bias, expert_for_source_row=expert[:, :1].contiguous()) if k == 1 else
+                dict(skip1=skip1, scales=scales, expert_for_source_row=expert)]
+    for kw in variants:
+        got = ops.moe_finalize_routing(rows, esdr, drop_pad_mode=mode, **kw)
+        okw = {}
+        for name, t in kw.items():
+            if name == "scales":
+                okw["scales"], okw["scale_dtype"] = _to_oracle(t), _code(oracle, t.dtype)
+            elif name == "expert_for_source_row":
+                okw["expert"] = t.cpu().numpy()
+            else:
+                okw[name] = _to_oracle(t)
+        if "scales" not in kw:
+            n = esdr.numel()
+            want = oracle.moe_finalize_routing(_to_oracle(rows), esdr.cpu().numpy(), _code(oracle, dtype),
+                                               drop_pad_mode=mode, **okw)
+            assert got.shape == (n, h)
+        else:
+            want = oracle.moe_finalize_routing(_to_oracle(rows), esdr.cpu().numpy(), _code(oracle, dtype),
+                                               drop_pad_mode=mode, **okw)
+        if dtype == torch.float32:
+            from helpers import assert_same_f32
+            assert_same_f32(got, want, f"mfr {sorted(kw)}")
+        else:
+            from helpers import assert_same_16
+            assert_same_16(bits(got), want, _code(oracle, dtype), f"mfr {sorted(kw)}")
+
+
+def test_moe_finalize_routing_many_terms_and_combine_equivalence(ops, oracle, backend):
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    g = torch.Generator(device="cuda").manual_seed(77)
+    # K above the staged batch: accepted for fp32 rows, rejected (clear status) for 16-bit rows
+    r, k, h = 4, 200, 64
+    rows = torch.randn((r * k, h), generator=g, device="cuda")
+    scales = torch.rand((r, k), generator=g, device="cuda")
+    esdr = torch.randperm(r * k, generator=g, device="cuda").to(torch.int32)
+    got = ops.moe_finalize_routing(rows, esdr, scales=scales, drop_pad_mode=3)
+    want = oracle.moe_finalize_routing(rows.cpu().numpy(), esdr.cpu().numpy(), oracle.DT_F32,
+                                       scales=scales.cpu().numpy(), drop_pad_mode=3)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    with pytest.raises(RuntimeError, match="limit"):
+        ops.moe_finalize_routing(rows.to(torch.bfloat16), esdr, scales=scales, drop_pad_mode=3)
+    # the chain's combine step is the scales-only, row-arranged case
+    t, topk, h = 40, 8, 512
+    rows16 = torch.randn((t * topk, h), generator=g, device="cuda").to(torch.bfloat16)
+    probs = torch.rand((t, topk), generator=g, device="cuda")
+    pos = torch.randperm(t * topk, generator=g, device="cuda").view(t, topk)
+    a = backend.combine(rows16, probs, pos.to(torch.int64))
+    b = ops.moe_finalize_routing(rows16, pos.to(torch.int32).reshape(-1), scales=probs, drop_pad_mode=2)
+    assert torch.equal(a, b)

@@ -404,3 +404,48 @@ def test_moe_re_routing_hand_derived_and_against_regroup_index(oracle):
     assert np.array_equal(num, cnt.sum(axis=0))
     with pytest.raises(ValueError):
         oracle.moe_re_routing(tok[:2], cnt)
+
+
+def test_moe_finalize_routing_hand_derived(oracle):
+    """Two output rows, K = 2, H = 2, fp32 so that every step is exact.
+    rows = [[1, 2], [10, 20], [100, 200]], bias = [[0.5, 0.5], [-1, -1]], scales = [[2, 3], [4, 5]],
+    expert = [[0, 1], [1, 7]] (7 is out of range: its bias is dropped), skip1 = 1000, skip2 = 0.25.
+    Column arrangement (mode 0): esdr = [p(0,0), p(1,0), p(0,1), p(1,1)] = [2, 0, 1, -1].
+      out[0] = 1000.25 + 2*(rows[2] + bias[0]) + 3*(rows[1] + bias[1]) = 1000.25 + [201, 401] + [27, 57]
+      out[1] = 1000.25 + 4*(rows[0] + bias[1]) + (term dropped)       = 1000.25 + [0, 4]"""
+    rows = np.array([[1, 2], [10, 20], [100, 200]], F)
+    bias = np.array([[0.5, 0.5], [-1, -1]], F)
+    scales = np.array([[2, 3], [4, 5]], F)
+    expert = np.array([[0, 1], [1, 7]], np.int32)
+    skip1 = np.full((2, 2), 1000.0, F)
+    skip2 = np.full((2, 2), 0.25, F)
+    out = oracle.moe_finalize_routing(rows, np.array([2, 0, 1, -1], np.int32), oracle.DT_F32, skip1=skip1, skip2=skip2,
+                                      bias=bias, scales=scales, expert=expert, drop_pad_mode=0)
+    assert out.tolist() == [[1228.25, 1458.25], [1000.25, 1004.25]]
+    # row arrangement (mode 2) of the same mapping
+    out2 = oracle.moe_finalize_routing(rows, np.array([2, 1, 0, -1], np.int32), oracle.DT_F32, skip1=skip1,
+                                       skip2=skip2, bias=bias, scales=scales, expert=expert, drop_pad_mode=2)
+    assert np.array_equal(out, out2)
+    # bias without expert ids is ignored; no scales means K = 1 and unit weights
+    out3 = oracle.moe_finalize_routing(rows, np.array([1, 5], np.int32), oracle.DT_F32, bias=bias)
+    assert out3.tolist() == [[10.0, 20.0], [0.0, 0.0]]
+    # the expert-parallel combine is the scales-only, row-arranged special case
+    rng = np.random.default_rng(3)
+    r16 = oracle.f32_to_bf16_bits(rng.standard_normal((12, 16)).astype(F))
+    probs = rng.random((5, 3)).astype(F)
+    pos = rng.integers(-1, 12, (5, 3))
+    a = oracle.combine(r16, probs, pos.astype(np.int64), oracle.DT_BF16)
+    b = oracle.moe_finalize_routing(r16, pos.astype(np.int32).reshape(-1), oracle.DT_BF16, scales=probs,
+                                    drop_pad_mode=2)
+    assert np.array_equal(a, b)
+
+
+def test_moe_finalize_routing_rounds_each_step_in_fp32(oracle):
+    """(row + bias) is rounded to fp32 before the multiplication, and the product before the addition:
+    row = 1, bias = 2^-24 -> 1 (the half-ulp tie rounds to even); scale 3 -> 3; a fused or reordered evaluation,
+    scale*row + scale*bias, would give 3 + 3*2^-24, which rounds to the next fp32 above 3."""
+    rows = np.array([[1.0]], F)
+    bias = np.array([[2.0**-24]], F)
+    out = oracle.moe_finalize_routing(rows, np.array([0], np.int32), oracle.DT_F32, bias=bias,
+                                      scales=np.array([[3.0]], F), expert=np.array([[0]], np.int32))
+    assert out[0, 0] == np.float32(3.0)

@@ -72,3 +72,24 @@ def test_plugin_moe_re_routing_matches_ctypes_operator(cb, ops):
     assert torch.equal(got[0], want[0]) and got[3].dtype == torch.int32
     with pytest.raises(RuntimeError, match="idx_type == 0"):
         cb.moe_re_routing(tok, cnt, None, 1, 1)
+
+
+def test_plugin_moe_finalize_routing_matches_ctypes_operator(cb, ops):
+    g = torch.Generator(device="cuda").manual_seed(9)
+    r, k, h, e = 50, 4, 1024, 8
+    rows = torch.randn((r * k, h), generator=g, device="cuda").to(torch.bfloat16)
+    skip = torch.randn((r, h), generator=g, device="cuda").to(torch.bfloat16)
+    bias = torch.randn((e, h), generator=g, device="cuda").to(torch.bfloat16)
+    scales = torch.rand((r, k), generator=g, device="cuda").to(torch.bfloat16)
+    esdr = torch.randperm(r * k, generator=g, device="cuda").to(torch.int32)
+    expert = torch.randint(0, e, (r, k), generator=g, device="cuda", dtype=torch.int32)
+    got = cb.moe_finalize_routing(rows, esdr, skip, None, bias, scales, expert, 0)
+    want = ops.moe_finalize_routing(rows, esdr, skip, None, bias, scales, expert, 0)
+    assert torch.equal(got, want)
+    assert torch.equal(cb.moe_finalize_routing(rows, esdr[:r]), ops.moe_finalize_routing(rows, esdr[:r]))
+    assert torch.equal(cb.moe_finalize_routing(rows, esdr, scales=scales, drop_pad_mode=9),     # clamped to 3
+                       ops.moe_finalize_routing(rows, esdr, scales=scales, drop_pad_mode=3))
+    with pytest.raises(RuntimeError, match="must be int32"):
+        cb.moe_finalize_routing(rows, esdr.to(torch.int64))
+    with pytest.raises(RuntimeError, match="K\\*NUM_ROWS"):
+        cb.moe_finalize_routing(rows, esdr[:7], scales=scales)
