@@ -119,6 +119,38 @@ def zipf_counts(rng, rows, experts, s=1.1):
     return rng.multinomial(rows, p).astype(np.int64)
 
 
+def place_experts(counts, world, mode):
+    """Expert-parallel shard of a grouped workload: returns (members, loads, replicas) with members[r] a list of
+    (expert, rows) for rank r.  Two placements:
+      "lpt":       E / world whole experts per rank, largest first onto the least loaded rank with a free slot.  With
+                   Zipf(1.1) sizes the most popular expert alone holds 21 % of the rows, which bounds the balance.
+      "replicate": balance 128-row tiles, not experts: experts go largest first to the rank with the most capacity
+                   left and an expert that does not fit is split at a tile boundary, its weights replicated on the
+                   ranks that share it (redundant hot experts, as expert-parallel serving systems place them).
+    Every rank then runs the same operator on its own rows and experts."""
+    loads, members = [0] * world, [[] for _ in range(world)]
+    order = np.argsort(-counts, kind="stable")
+    if mode == "lpt" or world == 1:
+        slots = -(-len(counts) // world)
+        for e in order:
+            r = min((q for q in range(world) if len(members[q]) < slots), key=lambda q: loads[q])
+            loads[r] += int(counts[e])
+            members[r].append((int(e), int(counts[e])))
+        return members, loads, 0
+    tiles = -(-counts // 128)
+    cap = [-(-int(tiles.sum()) // world)] * world
+    for e in order:
+        left = int(counts[e])
+        while left > 0:
+            r = max(range(world), key=lambda q: cap[q])
+            take = min(left, max(cap[r], 1) * 128)
+            members[r].append((int(e), take))
+            loads[r] += take
+            cap[r] -= -(-take // 128)
+            left -= take
+    return members, loads, sum(len(m) for m in members) - int((counts > 0).sum())
+
+
 class Workload:
     name = ""
     metric = ""
@@ -260,8 +292,12 @@ class GmsqWorkload(Workload):
     def config(self, world):
         return {"workload": f"configs[3]: grouped_matmul_swiglu_quant E={self.E} rows={self.M} (Zipf 1.1) "
                             f"K={self.K} N={self.N}, weights [E,K,N] int8",
-                "experts_per_gpu": self.E // world, "l2": "weights (7.5 GB) and activations larger than L2",
+                "experts_on_rank0": getattr(self, "e", self.E), "l2": "weights (7.5 GB) and activations larger than L2",
                 "parallelism": f"ep{world}" if world > 1 else "single GPU",
+                "placement": ("whole experts, largest first" if getattr(self, "placement", "replicate") == "lpt"
+                              or world == 1 else
+                              f"tile-balanced, hot experts split across ranks ({getattr(self, 'replicas', 0)} extra "
+                              "weight replicas)"),
                 "max_over_mean_rows_per_gpu": round(getattr(self, "placement_imbalance", 1.0), 3)}
 
     def gpu_setup(self, torch, rank, world):
@@ -269,22 +305,15 @@ class GmsqWorkload(Workload):
         self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
         rng = np.random.default_rng(0)
         counts = zipf_counts(rng, self.M, self.E)
-        # expert-parallel shard: E / N experts per rank, placed greedily (largest expert first, onto the least
-        # loaded rank that still has a free slot) so that the ranks' row counts are as even as the Zipf skew
-        # allows.  The most popular expert alone holds 21 % of the rows, which bounds the balance at N = 8.
-        slots = self.E // world
-        loads, members = [0] * world, [[] for _ in range(world)]
-        for e in np.argsort(-counts, kind="stable"):
-            r = min((q for q in range(world) if len(members[q]) < slots), key=lambda q: loads[q])
-            loads[r] += int(counts[e])
-            members[r].append(int(e))
-        mine = np.array(sorted(members[rank]), dtype=np.int64)
+        members, loads, self.replicas = place_experts(counts, world, getattr(self, "placement", "replicate"))
+        members[rank].sort()
         self.placement_imbalance = max(loads) / (sum(loads) / world)
-        self.counts = counts[mine]
+        self.counts = np.array([c for _, c in members[rank]], dtype=np.int64)
         self.gl = [int(v) for v in np.cumsum(self.counts)]
         self.m = int(self.counts.sum())
-        self.e = len(mine)
+        self.e = len(members[rank])
         self.total_rows = int(counts.sum())
+        self.traffic = type(self).traffic * self.m / self.total_rows  # DRAM traffic grows with the rows of the shard
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
         self.x = torch.randint(-127, 128, (self.m, self.K), generator=g, device="cuda", dtype=torch.int8)
         self.w = torch.randint(-127, 128, (self.e, self.K, self.N), generator=g, device="cuda", dtype=torch.int8)
@@ -707,6 +736,9 @@ def main():
     ap.add_argument("--layout", choices=["kn", "nk"], default="kn", help="weight layout of the matmul workloads")
     ap.add_argument("--transport", choices=["p2p", "nccl"], default="p2p",
                     help="chain workload: fused peer-memory stores or NCCL all-to-all for dispatch / combine")
+    ap.add_argument("--placement", choices=["replicate", "lpt"], default="replicate",
+                    help="grouped workload on several GPUs: split hot experts across ranks (weights replicated) or "
+                         "keep experts whole")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                     help="time the K steps as one CUDA-graph replay (auto: the bandwidth-bound workloads)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -720,6 +752,7 @@ def main():
         wl.M = args.qmm_m
     wl.layout_nk = (args.layout == "nk")
     wl.transport = args.transport
+    wl.placement = args.placement
     if args.impl == "reference":
         run_reference(args, wl)
         return
