@@ -675,7 +675,66 @@ class MfrWorkload(Workload):
                 units, f"{tokens} of 8192 tokens")
 
 
-WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "mfr": MfrWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
+class GateWorkload(Workload):
+    """MoeGatingTopKSoftmax at the router shape of benchmark configuration 5: 65536 tokens x 256 experts bf16, k = 8."""
+    name, metric, unit, dtype, bound = ("moe_gating_top_k_softmax", "moe_gating_top_k_softmax_hbm_gbs", "GB/s", "f32",
+                                        "hbm")
+    rows, inner, k = 65536, 256, 8
+    kernels_per_step = 1
+    traffic = None
+    scaling = "weak"
+
+    def config(self, world):
+        return {"workload": "moe_gating_top_k_softmax: 65536 rows x 256 experts bf16, k=8",
+                "rows_per_gpu": self.rows, "l2": "33.5 MB of logits: smaller than L2, flushed by the sustained-load "
+                                                 "loop's other buffers only; the kernel is bound by exp arithmetic",
+                "parallelism": f"rows x{world}" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        self.x = torch.randn((self.rows, self.inner), generator=g, device="cuda").to(torch.bfloat16)
+        self._y = torch.empty((self.rows, self.k), dtype=torch.bfloat16, device="cuda")
+        self._ei = torch.empty((self.rows, self.k), dtype=torch.int32, device="cuda")
+        self._ri = torch.empty((self.rows, self.k), dtype=torch.int32, device="cuda")
+        self._fn = self.L.load().w8a8_moe_gating_top_k_softmax
+        self._args = (self.x.data_ptr(), None, self._y.data_ptr(), self._ei.data_ptr(), self._ri.data_ptr(), self.rows,
+                      self.inner, self.k, self.L.DT_BF16)
+
+    def gpu_step(self):
+        rc = self._fn(*self._args, self.torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def bytes_per_step(self):
+        return self.rows * (self.inner * 2 + self.k * 10)
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def roofline_units(self):
+        return self.bytes_per_step() / 1e9
+
+    def host_inputs(self):
+        return [self.x.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        outs = self.ops.moe_gating_top_k_softmax(x, None, self.k)
+        back = [o.to("cpu", non_blocking=True) for o in outs]
+        return (host[0].numel() * 2, sum(o.numel() * o.element_size() for o in back))
+
+    def cpu_sample(self, O):
+        rng = np.random.default_rng(0)
+        x = O.f32_to_bf16_bits(rng.standard_normal((self.rows, self.inner)).astype(np.float32))
+        return (lambda: O.moe_gating_top_k_softmax(x, O.DT_BF16, self.k)), self.bytes_per_step() / 1e9, \
+            "all 65536 rows"
+
+
+WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "mfr": MfrWorkload, "gate": GateWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
              "chain": ChainWorkload}
 
 

@@ -60,6 +60,7 @@ SIGNATURES = {
                                            _i32, _i32, _vp, _sz, _vp]),
     "w8a8_moe_finalize_routing": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
                                          _i32, _i32, _vp]),
+    "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
 }
 

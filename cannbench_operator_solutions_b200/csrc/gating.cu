@@ -1,0 +1,191 @@
+// MoeGatingTopKSoftmax for sm_100a: per-row softmax over the experts, the k largest probabilities with their
+// expert indices, and the flattened row index j * rows + r.
+//
+// Arithmetic follows operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_kernel/
+// moe_gating_kernel.cpp of the reference catalog: everything in fp32 (:28), row maximum (:305-312), x - max
+// (:327), exp (:329), row sum (:333-339), descending sort of the exponentials with their indices (:344-368),
+// division of the selected values by the row sum (:390), round-to-nearest-even cast to the input type (:392);
+// a finished row reports `inner` as every expert index and keeps y and row_idx (:21, :285-300).
+//
+// Two choices the reference leaves to its hardware are fixed here and shared bit for bit with the CPU oracle:
+// exp is the canonical fp32 sequence of common.cuh, and the row sum is taken in a 32-lane order (lane t adds
+// elements t, t+32, ... in ascending order, then a butterfly over lane distances 16, 8, 4, 2, 1).  Equal
+// exponentials are ordered by ascending expert index.
+//
+// Mapping: one warp per row, the row held in registers (lane t owns elements t + 32 v); the k selections are
+// k rounds of a warp arg-max (two `redux.sync` each).  The operator moves rows * inner input elements and
+// 10 k bytes of output per row; at router sizes (inner <= 1024) it is bound by the exp arithmetic, not by HBM.
+#include "common.cuh"
+
+namespace w8a8 {
+
+template <int DT>
+__device__ __forceinline__ float gating_load(const void* x, int64_t i)
+{
+    if constexpr (DT == W8A8_DT_F32) {
+        return static_cast<const float*>(x)[i];
+    } else {
+        return bits16_to_float<DT>(static_cast<const uint16_t*>(x)[i]);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void gating_store(void* y, int64_t i, float v)
+{
+    if constexpr (DT == W8A8_DT_F32) {
+        static_cast<float*>(y)[i] = v;
+    } else {
+        static_cast<uint16_t*>(y)[i] = float_to_bits16<DT>(v);
+    }
+}
+
+constexpr int GATING_WARPS = 4;
+
+template <int DT, int VPT>
+__global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* __restrict__ x,
+                                                                   const uint8_t* __restrict__ finished,
+                                                                   void* __restrict__ y,
+                                                                   int32_t* __restrict__ expert_idx,
+                                                                   int32_t* __restrict__ row_idx, int64_t rows,
+                                                                   int inner, int k)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * GATING_WARPS;
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * GATING_WARPS + (threadIdx.x >> 5); r < rows; r += warps) {
+        float v[VPT];
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = lane + 32 * i;
+            v[i] = (c < inner) ? gating_load<DT>(x, r * inner + c) : -INFINITY;
+            m = fmaxf(m, v[i]);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            m = fmaxf(m, __shfl_xor_sync(FULL_MASK, m, off));
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = lane + 32 * i;
+            if (c < inner) {
+                v[i] = canonical_expf(__fsub_rn(v[i], m));
+                s = __fadd_rn(s, v[i]);
+            } else {
+                v[i] = -1.0f;  // below every exponential: never selected
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            s = __fadd_rn(s, __shfl_xor_sync(FULL_MASK, s, off));
+        }
+        const bool fin = (finished != nullptr) && (finished[r] != 0);
+        for (int j = 0; j < k; ++j) {
+            // this lane's best remaining element: largest value, then smallest index (ascending i is ascending index)
+            float best = -1.0f;
+            int best_i = 0;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                if (v[i] > best) {
+                    best = v[i];
+                    best_i = i;
+                }
+            }
+            // exponentials are >= 0 (or NaN, which compares as below): their bit patterns order like unsigned integers
+            const uint32_t key = (best >= 0.0f) ? __float_as_uint(best) + 1u : 0u;
+            const uint32_t top = __reduce_max_sync(FULL_MASK, key);
+            const uint32_t idx = (key == top) ? static_cast<uint32_t>(lane + 32 * best_i) : 0xffffffffu;
+            const uint32_t win = __reduce_min_sync(FULL_MASK, idx);
+            if (static_cast<uint32_t>(lane + 32 * best_i) == win && key == top) {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    if (i == best_i) {
+                        v[i] = -1.0f;
+                    }
+                }
+            }
+            if (lane == 0) {
+                const float e = (top != 0u) ? __uint_as_float(top - 1u) : NAN;
+                const int64_t o = r * k + j;
+                gating_store<DT>(y, o, __fdiv_rn(e, s));
+                expert_idx[o] = fin ? inner : static_cast<int32_t>(win);
+                row_idx[o] = static_cast<int32_t>(static_cast<int64_t>(j) * rows + r);
+            }
+        }
+    }
+}
+
+template <int DT, int VPT>
+static cudaError_t launch_gating(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                 int32_t* row_idx, int64_t rows, int inner, int k, cudaStream_t st)
+{
+    const int64_t want = (rows + GATING_WARPS - 1) / GATING_WARPS;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+    gating_kernel<DT, VPT><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k);
+    return cudaGetLastError();
+}
+
+template <int DT>
+static cudaError_t dispatch_gating(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                   int32_t* row_idx, int64_t rows, int inner, int k, cudaStream_t st)
+{
+    if (inner <= 32) {
+        return launch_gating<DT, 1>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+    }
+    if (inner <= 64) {
+        return launch_gating<DT, 2>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+    }
+    if (inner <= 128) {
+        return launch_gating<DT, 4>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+    }
+    if (inner <= 256) {
+        return launch_gating<DT, 8>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+    }
+    if (inner <= 512) {
+        return launch_gating<DT, 16>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+    }
+    return launch_gating<DT, 32>(x, finished, y, expert_idx, row_idx, rows, inner, k, st);
+}
+
+}  // namespace w8a8
+
+extern "C" int w8a8_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                             int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype,
+                                             void* stream)
+{
+    if (dtype != W8A8_DT_F16 && dtype != W8A8_DT_BF16 && dtype != W8A8_DT_F32) {
+        return W8A8_ERR_INVALID;
+    }
+    if (rows < 0 || inner <= 0 || k <= 0 || k > inner) {
+        return W8A8_ERR_INVALID;
+    }
+    if (inner > W8A8_GATING_MAX_EXPERTS || rows * k > INT32_MAX) {
+        return W8A8_ERR_LIMIT;
+    }
+    if (rows == 0) {
+        return W8A8_OK;
+    }
+    if (x == nullptr || y == nullptr || expert_idx == nullptr || row_idx == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    const size_t elem = (dtype == W8A8_DT_F32) ? 4 : 2;
+    if (!w8a8::is_aligned(x, elem) || !w8a8::is_aligned(y, elem)) {
+        return W8A8_ERR_ALIGN;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int in = static_cast<int>(inner), kk = static_cast<int>(k);
+    cudaError_t e;
+    switch (dtype) {
+    case W8A8_DT_F16:
+        e = w8a8::dispatch_gating<W8A8_DT_F16>(x, finished, y, expert_idx, row_idx, rows, in, kk, st);
+        break;
+    case W8A8_DT_BF16:
+        e = w8a8::dispatch_gating<W8A8_DT_BF16>(x, finished, y, expert_idx, row_idx, rows, in, kk, st);
+        break;
+    default:
+        e = w8a8::dispatch_gating<W8A8_DT_F32>(x, finished, y, expert_idx, row_idx, rows, in, kk, st);
+        break;
+    }
+    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}

@@ -95,45 +95,6 @@ struct GemmParams {
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
 };
 
-// fp32 exp shared with the CPU oracle: Cody-Waite reduction by ln2 in two
-// pieces, degree-5 polynomial (the classic single-precision coefficients
-// published with the Cephes library), two-step power-of-two scaling.  Built
-// from IEEE mul / add / fma only, so host and device agree bit for bit.
-__device__ __forceinline__ float canonical_expf(float x)
-{
-    if (x != x) {
-        return x;
-    }
-    x = (x > 89.0f) ? 89.0f : x;
-    x = (x < -104.0f) ? -104.0f : x;
-    const float n = rintf(__fmul_rn(x, 1.44269504088896341f));
-    float r = fmaf(n, -0.693359375f, x);
-    r = fmaf(n, 2.12194440e-4f, r);
-    float p = 1.9875691500e-4f;
-    p = fmaf(p, r, 1.3981999507e-3f);
-    p = fmaf(p, r, 8.3334519073e-3f);
-    p = fmaf(p, r, 4.1665795894e-2f);
-    p = fmaf(p, r, 1.6666665459e-1f);
-    p = fmaf(p, r, 5.0000001201e-1f);
-    const float r2 = __fmul_rn(r, r);
-    float e = fmaf(p, r2, r);
-    e = __fadd_rn(e, 1.0f);
-    const int ni = static_cast<int>(n);
-    const int n1 = ni >> 1;
-    const int n2 = ni - n1;
-    const float s1 = __int_as_float((n1 + 127) << 23);
-    const float s2 = __int_as_float((n2 + 127) << 23);
-    return __fmul_rn(__fmul_rn(e, s1), s2);
-}
-
-// silu(l) = l / (1 + exp(-l)), the operation sequence of the reference
-// (gmsq_vec_kernel.cpp:213-217).
-__device__ __forceinline__ float canonical_silu(float l)
-{
-    const float e = __fadd_rn(canonical_expf(-l), 1.0f);
-    return __fdiv_rn(l, e);
-}
-
 __device__ __forceinline__ float vec_elem_as_float(const void* p, int64_t i, int kind)
 {
     switch (kind) {

@@ -10,6 +10,7 @@
 //   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:38-150
 //   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:40-190
 //   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:32-170
+//   moe_gating_top_k_softmax    operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_plugin/moe_gating_plugin.cpp:28-120
 //   moe_finalize_routing        operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:31-237
 // The NPU plugins enqueue their launchers with OpCommand::RunOpApi on the
 // current NPU stream; here the C-ABI call is enqueued on the current CUDA
@@ -559,8 +560,55 @@ static torch::Tensor mfr_cuda(const torch::Tensor& rows, const torch::Tensor& sr
     return out;
 }
 
+// ------------------------------------------------------ moe_gating_top_k_softmax
+using GateOut = std::tuple<torch::Tensor, torch::Tensor, torch::Tensor>;
+
+static GateOut gating_meta(const torch::Tensor& x, const c10::optional<torch::Tensor>& finished, int64_t k)
+{
+    TORCH_CHECK(x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kFloat16 ||
+                    x.scalar_type() == torch::kBFloat16,
+                "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.");
+    TORCH_CHECK(x.dim() >= 2, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.");
+    const int64_t inner = x.size(-1);
+    TORCH_CHECK(inner > 0, "cann_bench.moe_gating_top_k_softmax requires a non-empty last dimension.");
+    TORCH_CHECK(k > 0 && k <= inner, "cann_bench.moe_gating_top_k_softmax requires 0 < k <= x.size(-1).");
+    if (present(finished)) {
+        TORCH_CHECK(finished->scalar_type() == torch::kBool,
+                    "cann_bench.moe_gating_top_k_softmax requires a bool 'finished' tensor.");
+    }
+    std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end() - 1);
+    shape.push_back(k);
+    return std::make_tuple(torch::empty(shape, x.options()), torch::empty(shape, x.options().dtype(torch::kInt)),
+                           torch::empty(shape, x.options().dtype(torch::kInt)));
+}
+
+static GateOut gating_cuda(const torch::Tensor& x, const c10::optional<torch::Tensor>& finished, int64_t k)
+{
+    const c10::cuda::OptionalCUDAGuard guard(x.device());
+    auto xc = x.contiguous();
+    auto outs = gating_meta(xc, finished, k);
+    const int64_t inner = xc.size(-1);
+    const int64_t rows = xc.numel() / inner;
+    TORCH_CHECK(rows > 0, "cann_bench.moe_gating_top_k_softmax requires at least one row.");
+    torch::Tensor fin;
+    if (present(finished)) {
+        fin = finished->contiguous();
+        TORCH_CHECK(fin.numel() == rows, "cann_bench.moe_gating_top_k_softmax: finished must have numel == rows.");
+    }
+    check_status(w8a8_moe_gating_top_k_softmax(xc.data_ptr(),
+                                               fin.defined() ? static_cast<const uint8_t*>(fin.data_ptr()) : nullptr,
+                                               std::get<0>(outs).data_ptr(),
+                                               static_cast<int32_t*>(std::get<1>(outs).data_ptr()),
+                                               static_cast<int32_t*>(std::get<2>(outs).data_ptr()), rows, inner, k,
+                                               dtype_code(xc), stream_of(xc)),
+                 "moe_gating_top_k_softmax");
+    return outs;
+}
+
 TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 {
+    m.def("moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> "
+          "(Tensor y, Tensor expert_idx, Tensor row_idx)");
     m.def("moe_finalize_routing(Tensor expanded_permuted_rows, Tensor expanded_src_to_dst_row, "
           "Tensor? skip1=None, Tensor? skip2=None, Tensor? bias=None, Tensor? scales=None, "
           "Tensor? expert_for_source_row=None, int drop_pad_mode=0) -> Tensor out");
@@ -588,6 +636,7 @@ TORCH_LIBRARY_IMPL(cann_bench, Meta, m)
     m.impl("grouped_matmul", grouped_matmul_meta);
     m.impl("moe_re_routing", moe_re_routing_meta);
     m.impl("moe_finalize_routing", mfr_meta);
+    m.impl("moe_gating_top_k_softmax", gating_meta);
 }
 
 TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
@@ -599,6 +648,7 @@ TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
     m.impl("grouped_matmul", grouped_matmul_cuda);
     m.impl("moe_re_routing", moe_re_routing_cuda);
     m.impl("moe_finalize_routing", mfr_cuda);
+    m.impl("moe_gating_top_k_softmax", gating_cuda);
 }
 
 }  // namespace cann_bench

@@ -423,3 +423,38 @@ def moe_finalize_routing(expanded_permuted_rows: torch.Tensor, expanded_src_to_d
                                                 _dt(sc) if sc is not None else _dt(eprc), _stream())
     _status(rc, "moe_finalize_routing")
     return out
+
+
+def moe_gating_top_k_softmax(x: torch.Tensor, finished: Optional[torch.Tensor] = None, k: int = 1
+                             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> (Tensor y, Tensor expert_idx,
+    Tensor row_idx)`` (operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_plugin/
+    moe_gating_plugin.cpp:28-53 for the schema and shape rules, 60-88 for the checks).
+
+    Softmax over the last dimension in fp32, the ``k`` largest probabilities per row in ``x``'s dtype, their
+    expert columns (int32; ``x.size(-1)`` for rows whose ``finished`` flag is set) and ``row_idx = j * rows + r``."""
+    _check(x.dtype in (torch.float32, torch.float16, torch.bfloat16),
+           "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.")
+    _check(x.dim() >= 2, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.")
+    inner = x.size(-1)
+    _check(inner > 0, "cann_bench.moe_gating_top_k_softmax requires a non-empty last dimension.")
+    _check(0 < k <= inner, "cann_bench.moe_gating_top_k_softmax requires 0 < k <= x.size(-1).")
+    if finished is not None:
+        _check(finished.dtype == torch.bool, "cann_bench.moe_gating_top_k_softmax requires a bool 'finished' tensor.")
+    _need_cuda(x, finished)
+    xc = x.contiguous()
+    rows = xc.numel() // inner
+    _check(rows > 0, "cann_bench.moe_gating_top_k_softmax requires at least one row.")
+    shape = tuple(xc.shape[:-1]) + (k,)
+    y = torch.empty(shape, dtype=xc.dtype, device=xc.device)
+    ei = torch.empty(shape, dtype=torch.int32, device=xc.device)
+    ri = torch.empty(shape, dtype=torch.int32, device=xc.device)
+    fin = None
+    if finished is not None:
+        fin = finished.contiguous()
+        _check(fin.numel() == rows, "cann_bench.moe_gating_top_k_softmax: finished must have numel == rows.")
+    with torch.cuda.device(xc.device):
+        rc = L.load().w8a8_moe_gating_top_k_softmax(xc.data_ptr(), _ptr(fin), y.data_ptr(), ei.data_ptr(),
+                                                    ri.data_ptr(), rows, inner, k, _dt(xc), _stream())
+    _status(rc, "moe_gating_top_k_softmax")
+    return y, ei, ri

@@ -315,6 +315,21 @@ int w8a8_moe_finalize_routing(const void* rows, const int32_t* src_to_dst_row, c
                               int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode, int dtype,
                               int scale_dtype, void* stream);
 
+/*
+ * MoeGatingTopKSoftmax: p = softmax(x, last dim) in fp32; y[r, j] = the j-th largest p of row r (rounded to x's
+ * type), expert_idx[r, j] its column (equal values: lower column first), row_idx[r, j] = j * rows + r.  A row
+ * with finished[r] != 0 reports `inner` as every expert index; y and row_idx are unaffected.  `finished` is
+ * optional (one byte per row, torch bool).  x: F16 / BF16 / F32 [rows, inner], 0 < k <= inner <=
+ * W8A8_GATING_MAX_EXPERTS (W8A8_ERR_LIMIT beyond; the row is held in one warp's registers).
+ * Replaces launch_moe_gating_kernel_{float,half,bfloat16}
+ * (operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_kernel/moe_gating_launch.h; formula in
+ * moe_gating_kernel.cpp:14-21).
+ */
+#define W8A8_GATING_MAX_EXPERTS 1024
+int w8a8_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                  int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype,
+                                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

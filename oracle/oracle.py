@@ -86,6 +86,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_moe_re_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64]
     lib.oracle_moe_finalize_routing.restype = i32
     lib.oracle_moe_finalize_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
+    lib.oracle_moe_gating_top_k_softmax.restype = i32
+    lib.oracle_moe_gating_top_k_softmax.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32]
     lib.oracle_num_threads.restype = i32
     _lib = lib
     return lib
@@ -310,3 +312,20 @@ def moe_finalize_routing(rows, esdr, dtype: int, *, skip1=None, skip2=None, bias
     if rc != 0:
         raise ValueError("oracle_moe_finalize_routing rejected the arguments")
     return out
+
+
+def moe_gating_top_k_softmax(x, dtype: int, k: int, finished=None):
+    """x [..., inner] as uint16 bit patterns (F16 / BF16) or float32 -> (y, expert_idx, row_idx), each [..., k]."""
+    np_t = np.float32 if dtype == DT_F32 else np.uint16
+    x = _c(x, np_t)
+    inner = x.shape[-1]
+    rows = x.size // inner
+    shape = x.shape[:-1] + (k,)
+    y = np.empty(shape, np_t)
+    ei = np.empty(shape, np.int32)
+    ri = np.empty(shape, np.int32)
+    fin = None if finished is None else _c(finished, np.uint8)
+    rc = load().oracle_moe_gating_top_k_softmax(_p(x), _p(fin), _p(y), _p(ei), _p(ri), rows, inner, k, dtype)
+    if rc != 0:
+        raise ValueError("oracle_moe_gating_top_k_softmax rejected the arguments")
+    return y, ei, ri

@@ -907,3 +907,67 @@ int oracle_moe_finalize_routing(const void* rows, const int32_t* esdr, const voi
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* MoeGatingTopKSoftmax                                                      */
+/* MGT/op_kernel/moe_gating_kernel.cpp:14-21 (formula), :305-339 (max, x-max, */
+/* exp, sum), :344-368 (descending sort with indices), :390-392 (divide the   */
+/* selected values by the row sum, round to the input type).  The reference   */
+/* leaves the summation order and the exp implementation to its hardware;     */
+/* here the sum runs over 32 lanes (lane t adds elements t, t+32, ... in      */
+/* ascending order, then a butterfly over distances 16, 8, 4, 2, 1) and exp   */
+/* is oracle_expf, both shared with the CUDA kernel.  Equal values: lower     */
+/* column first.                                                              */
+/* ------------------------------------------------------------------------ */
+int oracle_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                    int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype)
+{
+    if (dtype != W8A8_DT_F16 && dtype != W8A8_DT_BF16 && dtype != W8A8_DT_F32) {
+        return -1;
+    }
+    if (rows < 0 || inner <= 0 || k <= 0 || k > inner) {
+        return -1;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float* e = (float*)malloc((size_t)inner * sizeof(float));
+        float m = -INFINITY;
+        for (int64_t c = 0; c < inner; ++c) {
+            e[c] = load_as_f32(x, r * inner + c, dtype);
+            m = fmaxf(m, e[c]);
+        }
+        float lane[32];
+        for (int t = 0; t < 32; ++t) {
+            lane[t] = 0.0f;
+        }
+        for (int64_t c = 0; c < inner; ++c) {
+            e[c] = oracle_expf(e[c] - m);
+            lane[c & 31] = lane[c & 31] + e[c];
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            float next[32];
+            for (int t = 0; t < 32; ++t) {
+                next[t] = lane[t] + lane[t ^ off];
+            }
+            memcpy(lane, next, sizeof(lane));
+        }
+        const float sum = lane[0];
+        for (int64_t j = 0; j < k; ++j) {
+            int64_t best = -1;
+            for (int64_t c = 0; c < inner; ++c) {
+                if (e[c] >= 0.0f && (best < 0 || e[c] > e[best])) {
+                    best = c;
+                }
+            }
+            const float val = (best >= 0) ? e[best] : NAN;
+            store_from_f32(y, r * k + j, dtype, val / sum);
+            expert_idx[r * k + j] = (finished != NULL && finished[r]) ? (int32_t)inner : (int32_t)best;
+            row_idx[r * k + j] = (int32_t)(j * rows + r);
+            if (best >= 0) {
+                e[best] = -1.0f;
+            }
+        }
+        free(e);
+    }
+    return 0;
+}

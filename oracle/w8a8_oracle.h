@@ -120,6 +120,11 @@ int oracle_moe_finalize_routing(const void* rows, const int32_t* esdr, const voi
                                 int64_t R, int64_t H, int64_t K, int64_t E, int64_t num_dst, int drop_pad_mode,
                                 int dtype, int scale_dtype);
 
+/* MoeGatingTopKSoftmax: softmax over the last dimension, the k largest probabilities (lower column first among
+ * equals), their columns (inner for finished rows) and row_idx = j * rows + r. */
+int oracle_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
+                                    int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype);
+
 int oracle_num_threads(void);
 
 #ifdef __cplusplus

@@ -102,6 +102,10 @@ def test_argument_validation_needs_no_gpu(lib):
                                          L.DT_F32, None) == L.ERR_LIMIT
     assert lib.w8a8_moe_finalize_routing(p + 1, p, None, None, None, None, None, p, 4, 64, 1, 0, 8, 0, L.DT_BF16,
                                          L.DT_F32, None) == L.ERR_ALIGN
+    assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 0, 64, 2, L.DT_BF16, None) == L.OK
+    assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 64, 65, L.DT_BF16, None) == L.ERR_INVALID
+    assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 64, 2, L.DT_I8, None) == L.ERR_INVALID
+    assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 1025, 2, L.DT_F32, None) == L.ERR_LIMIT
     assert lib.w8a8_combine(p, p, p, p, 0, 2, 64, L.DT_BF16, None) == L.OK
     assert lib.w8a8_combine(p, p, p, p, 4, 2, 64, L.DT_F32, None) == L.ERR_INVALID
 
@@ -136,3 +140,7 @@ def test_operator_wrappers_validate_like_the_reference_plugins():
         ops.moe_finalize_routing(torch.zeros(4, 8, dtype=torch.int8), torch.zeros(4, dtype=torch.int32))
     with pytest.raises(RuntimeError, match="K\\*NUM_ROWS"):
         ops.moe_finalize_routing(torch.zeros(4, 8), torch.zeros(5, dtype=torch.int32), scales=torch.zeros(2, 2))
+    with pytest.raises(RuntimeError, match="0 < k <= x.size"):
+        ops.moe_gating_top_k_softmax(torch.zeros(4, 8), k=9)
+    with pytest.raises(RuntimeError, match="rank >= 2"):
+        ops.moe_gating_top_k_softmax(torch.zeros(8), k=1)

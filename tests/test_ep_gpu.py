@@ -240,3 +240,38 @@ def test_moe_finalize_routing_many_terms_and_combine_equivalence(ops, oracle, ba
     a = backend.combine(rows16, probs, pos.to(torch.int64))
     b = ops.moe_finalize_routing(rows16, pos.to(torch.int32).reshape(-1), scales=probs, drop_pad_mode=2)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,inner,k", [(37, 8, 2), (1000, 256, 8), (5, 32, 32), (64, 60, 1), (33, 1000, 6),
+                                          (9, 1024, 16), (3, 3, 3)])
+def test_moe_gating_top_k_softmax_matches_oracle(ops, oracle, dtype, rows, inner, k):
+    g = torch.Generator(device="cuda").manual_seed(seed_of(_T[dtype], rows, inner, k))
+    x = (torch.randn((rows, inner), generator=g, device="cuda") * 2).to(dtype)
+    x[0] = torch.round(x[0])                      # coarse values: many exact ties in the first row
+    if rows > 2:
+        x[1] = 0.0                                # every probability equal
+    fin = torch.rand((rows,), generator=g, device="cuda") < 0.3
+    for finished in (None, fin):
+        y, ei, ri = ops.moe_gating_top_k_softmax(x, finished, k)
+        wy, wei, wri = oracle.moe_gating_top_k_softmax(_to_oracle(x), _code(oracle, dtype), k,
+                                                       finished=None if finished is None else fin.cpu().numpy())
+        assert y.shape == (rows, k) and ei.dtype == torch.int32 and ri.dtype == torch.int32
+        assert np.array_equal(ei.cpu().numpy(), wei)
+        assert np.array_equal(ri.cpu().numpy(), wri)
+        if dtype == torch.float32:
+            from helpers import assert_same_f32
+            assert_same_f32(y, wy, "gating y")
+        else:
+            from helpers import assert_same_16
+            assert_same_16(bits(y), wy, _code(oracle, dtype), "gating y")
+
+
+def test_moe_gating_top_k_softmax_shapes_and_limits(ops):
+    x = torch.randn((2, 3, 5, 16), device="cuda")
+    y, ei, ri = ops.moe_gating_top_k_softmax(x, k=4)
+    assert y.shape == (2, 3, 5, 4) and ri.view(-1, 4)[7].tolist() == [7, 37, 67, 97]
+    ref = torch.softmax(x, -1).topk(4, -1)
+    assert torch.equal(ei.long(), ref.indices) and torch.allclose(y, ref.values, rtol=1e-5, atol=1e-7)
+    with pytest.raises(RuntimeError, match="limit"):
+        ops.moe_gating_top_k_softmax(torch.zeros((2, 2048), device="cuda"), k=2)

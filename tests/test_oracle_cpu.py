@@ -449,3 +449,33 @@ def test_moe_finalize_routing_rounds_each_step_in_fp32(oracle):
     out = oracle.moe_finalize_routing(rows, np.array([0], np.int32), oracle.DT_F32, bias=bias,
                                       scales=np.array([[3.0]], F), expert=np.array([[0]], np.int32))
     assert out[0, 0] == np.float32(3.0)
+
+
+def test_moe_gating_top_k_softmax_hand_derived_and_against_fp64(oracle):
+    # equal logits: every probability is exactly 1/4; ties go to the lower column; row_idx = j * rows + r
+    x = np.zeros((3, 4), F)
+    y, ei, ri = oracle.moe_gating_top_k_softmax(x, oracle.DT_F32, 2, finished=np.array([0, 1, 0], np.uint8))
+    assert y.tolist() == [[0.25, 0.25]] * 3
+    assert ei.tolist() == [[0, 1], [4, 4], [0, 1]]          # the finished row reports inner = 4
+    assert ri.tolist() == [[0, 3], [1, 4], [2, 5]]
+    # separated logits against an fp64 softmax: same columns, probabilities within 4 fp32 ulp
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((64, 256)).astype(F) * 3
+    y, ei, _ = oracle.moe_gating_top_k_softmax(x, oracle.DT_F32, 8)
+    p = np.exp(x.astype(np.float64) - x.max(1, keepdims=True).astype(np.float64))
+    p /= p.sum(1, keepdims=True)
+    order = np.argsort(-p, axis=1, kind="stable")[:, :8]
+    assert np.array_equal(ei, order)
+    want = np.take_along_axis(p, order, 1)
+    assert np.abs(y - want).max() <= 4 * np.spacing(want.astype(F)).max()
+    # 16-bit inputs: probabilities are rounded to the input type
+    xb = oracle.f32_to_bf16_bits(x)
+    yb, eib, _ = oracle.moe_gating_top_k_softmax(xb, oracle.DT_BF16, 4)
+    xf = oracle.bf16_bits_to_f32(xb).astype(np.float64)
+    pb = np.exp(xf - xf.max(1, keepdims=True))
+    pb /= pb.sum(1, keepdims=True)
+    got = oracle.bf16_bits_to_f32(yb)
+    want = np.take_along_axis(pb, eib.astype(np.int64), 1)
+    assert np.abs(got - want).max() <= 2.0**-8 * want.max()
+    with pytest.raises(ValueError):
+        oracle.moe_gating_top_k_softmax(x, oracle.DT_F32, 257)

@@ -93,3 +93,17 @@ def test_plugin_moe_finalize_routing_matches_ctypes_operator(cb, ops):
         cb.moe_finalize_routing(rows, esdr.to(torch.int64))
     with pytest.raises(RuntimeError, match="K\\*NUM_ROWS"):
         cb.moe_finalize_routing(rows, esdr[:7], scales=scales)
+
+
+def test_plugin_moe_gating_matches_ctypes_operator(cb, ops):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn((300, 256), generator=g, device="cuda").to(torch.bfloat16)
+    fin = torch.rand((300,), generator=g, device="cuda") < 0.5
+    for a, b in zip(cb.moe_gating_top_k_softmax(x, fin, 8), ops.moe_gating_top_k_softmax(x, fin, 8)):
+        assert torch.equal(a, b)
+    for a, b in zip(cb.moe_gating_top_k_softmax(x), ops.moe_gating_top_k_softmax(x)):
+        assert torch.equal(a, b)
+    with pytest.raises(RuntimeError, match="0 < k <= x.size"):
+        cb.moe_gating_top_k_softmax(x, None, 0)
+    with pytest.raises(RuntimeError, match="bool 'finished'"):
+        cb.moe_gating_top_k_softmax(x, fin.to(torch.int32), 2)
