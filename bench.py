@@ -734,7 +734,72 @@ class GateWorkload(Workload):
             "all 65536 rows"
 
 
-WORKLOADS = {"gmsq": GmsqWorkload, "mrr": MrrWorkload, "mfr": MfrWorkload, "gate": GateWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
+class DqsqWorkload(Workload):
+    """DequantSwigluQuant on the accumulator shape of benchmark configuration 5's up projection on one of 8 ranks:
+    int32 [16384, 4096] (H = 2048) with per-channel and per-token scales."""
+    name, metric, unit, dtype, bound = "dequant_swiglu_quant", "dequant_swiglu_quant_hbm_gbs", "GB/s", "f32", "hbm"
+    rows, h = 16384, 2048
+    kernels_per_step = 1
+    traffic = None
+    scaling = "weak"
+
+    def config(self, world):
+        return {"workload": "dequant_swiglu_quant: int32 [16384, 4096] -> int8 [16384, 2048], activate_left",
+                "rows_per_gpu": self.rows, "l2": "input (268 MB) larger than L2",
+                "parallelism": f"rows x{world}" if world > 1 else "single GPU"}
+
+    def gpu_setup(self, torch, rank, world):
+        import cannbench_operator_solutions_b200 as pkg
+        self.torch, self.ops, self.L = torch, pkg.ops, pkg._lib
+        g = torch.Generator(device="cuda").manual_seed(rank)
+        self.x = torch.randint(-300000, 300000, (self.rows, 2 * self.h), generator=g, device="cuda",
+                               dtype=torch.int32)
+        self.ws = torch.empty((2 * self.h,), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+        self.as_ = torch.empty((self.rows,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+        self._y = torch.empty((self.rows, self.h), dtype=torch.int8, device="cuda")
+        self._s = torch.empty((self.rows,), dtype=torch.float32, device="cuda")
+        self._fn = self.L.load().w8a8_dequant_swiglu_quant
+        self._args = (self.x.data_ptr(), self.ws.data_ptr(), self.as_.data_ptr(), None, self._y.data_ptr(),
+                      self._s.data_ptr(), self.rows, self.h, self.L.DT_I32, 1, 0)
+
+    def gpu_step(self):
+        rc = self._fn(*self._args, self.torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
+    def kernel_step(self):
+        return self.gpu_step()
+
+    def bytes_per_step(self):
+        return self.rows * (9 * self.h + 8) + 8 * self.h
+
+    def units_per_step(self):
+        return self.bytes_per_step() / 1e9
+
+    def roofline_units(self):
+        return self.bytes_per_step() / 1e9
+
+    def host_inputs(self):
+        return [self.x.cpu().pin_memory(), self.as_.cpu().pin_memory()]
+
+    def e2e_step(self, host):
+        x = host[0].to("cuda", non_blocking=True)
+        a_s = host[1].to("cuda", non_blocking=True)
+        outs = self.ops.dequant_swiglu_quant(x, self.ws, a_s, None, True)
+        back = [o.to("cpu", non_blocking=True) for o in outs]
+        return (host[0].numel() * 4 + host[1].numel() * 4, sum(o.numel() * o.element_size() for o in back))
+
+    def cpu_sample(self, O):
+        rows = 4096
+        rng = np.random.default_rng(0)
+        x = rng.integers(-300000, 300000, (rows, 2 * self.h)).astype(np.int32)
+        ws = rng.uniform(1e-3, 1e-2, 2 * self.h).astype(np.float32)
+        a_s = rng.uniform(1e-3, 5e-2, rows).astype(np.float32)
+        return ((lambda: O.dequant_swiglu_quant(x, O.DT_I32, weight_scale=ws, activation_scale=a_s,
+                                                activate_left=True)),
+                (rows * (9 * self.h + 8) + 8 * self.h) / 1e9, f"{rows} of 16384 rows")
+
+
+WORKLOADS = {"dqsq": DqsqWorkload, "gmsq": GmsqWorkload, "mrr": MrrWorkload, "mfr": MfrWorkload, "gate": GateWorkload, "ardq": ArdqWorkload, "dq": DqWorkload, "qmm": QmmWorkload,
              "chain": ChainWorkload}
 
 

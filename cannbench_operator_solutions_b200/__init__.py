@@ -8,13 +8,13 @@ in-tree nvcc build.  Loading the torch plugin (``load_torch_plugin``)
 additionally registers the operators as ``torch.ops.cann_bench.*``.
 """
 from . import _lib, ops  # noqa: F401
-from .ops import (add_rms_norm_dynamic_quant, dynamic_quant, grouped_matmul,  # noqa: F401
+from .ops import (add_rms_norm_dynamic_quant, dequant_swiglu_quant, dynamic_quant, grouped_matmul,  # noqa: F401
                   grouped_matmul_swiglu_quant, moe_finalize_routing, moe_gating_top_k_softmax,
                   moe_re_routing, quant_matmul)
 
 __all__ = [
     "dynamic_quant", "add_rms_norm_dynamic_quant", "quant_matmul", "grouped_matmul_swiglu_quant", "grouped_matmul",
-    "moe_re_routing", "moe_finalize_routing", "moe_gating_top_k_softmax", "load_torch_plugin",
+    "moe_re_routing", "moe_finalize_routing", "moe_gating_top_k_softmax", "dequant_swiglu_quant", "load_torch_plugin",
 ]
 
 

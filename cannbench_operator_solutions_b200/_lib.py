@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libw8a8ffn.so")
 OK = 0
 ERR_INVALID, ERR_ALIGN, ERR_GROUP_LIST, ERR_WORKSPACE, ERR_CUDA, ERR_UNSUPPORTED, ERR_LIMIT = -1, -2, -3, -4, -5, -6, -7
 STATIC_SCRATCH_BYTES = (8 << 20) + (64 << 10)
-DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
+DT_F16, DT_BF16, DT_F32, DT_I8, DT_I32 = 0, 1, 2, 3, 4
 F_ROUND_DIRECT = 1
 F_STAGE_MATMUL, F_STAGE_REQUANT = 2, 4
 W_KN, W_NK = 0, 1
@@ -61,6 +61,7 @@ SIGNATURES = {
     "w8a8_moe_finalize_routing": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
                                          _i32, _i32, _vp]),
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
 }
 

@@ -10,6 +10,7 @@
 //   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:38-150
 //   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:40-190
 //   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:32-170
+//   dequant_swiglu_quant        operators/dequantswigluquant/csrc/ops/dequant_swiglu_quant/op_plugin/dqsq_plugin.cpp:31-160
 //   moe_gating_top_k_softmax    operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_plugin/moe_gating_plugin.cpp:28-120
 //   moe_finalize_routing        operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:31-237
 // The NPU plugins enqueue their launchers with OpCommand::RunOpApi on the
@@ -605,8 +606,77 @@ static GateOut gating_cuda(const torch::Tensor& x, const c10::optional<torch::Te
     return outs;
 }
 
+// ---------------------------------------------------------- dequant_swiglu_quant
+static std::tuple<torch::Tensor, torch::Tensor> dqsq_meta(const torch::Tensor& x,
+                                                          const c10::optional<torch::Tensor>& weight_scale,
+                                                          const c10::optional<torch::Tensor>& activation_scale,
+                                                          const c10::optional<torch::Tensor>& quant_scale,
+                                                          bool activate_left)
+{
+    (void)weight_scale;
+    (void)activation_scale;
+    (void)quant_scale;
+    (void)activate_left;
+    TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
+    TORCH_CHECK(x.size(1) % 2 == 0, "dequant_swiglu_quant requires an even last dimension.");
+    return std::make_tuple(torch::empty({x.size(0), x.size(1) / 2}, x.options().dtype(torch::kChar)),
+                           torch::empty({x.size(0)}, x.options().dtype(torch::kFloat)));
+}
+
+static std::tuple<torch::Tensor, torch::Tensor> dqsq_cuda(const torch::Tensor& x,
+                                                          const c10::optional<torch::Tensor>& weight_scale,
+                                                          const c10::optional<torch::Tensor>& activation_scale,
+                                                          const c10::optional<torch::Tensor>& quant_scale,
+                                                          bool activate_left)
+{
+    const c10::cuda::OptionalCUDAGuard guard(x.device());
+    TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
+    TORCH_CHECK(x.is_contiguous(), "dequant_swiglu_quant requires a contiguous input.");
+    auto outs = dqsq_meta(x, weight_scale, activation_scale, quant_scale, activate_left);
+    const int64_t M = x.size(0), N2 = x.size(1);
+    if (M <= 0 || N2 <= 0) {
+        return outs;
+    }
+    const int64_t H = N2 / 2;
+    const auto xt = x.scalar_type();
+    const bool is_i32 = (xt == torch::kInt);
+    if (is_i32) {
+        TORCH_CHECK(present(weight_scale), "weight_scale is required when x is int32.");
+        TORCH_CHECK(present(activation_scale), "activation_scale is required when x is int32.");
+        TORCH_CHECK(weight_scale->scalar_type() == torch::kFloat, "weight_scale must be float32.");
+        TORCH_CHECK(activation_scale->scalar_type() == torch::kFloat, "activation_scale must be float32.");
+        TORCH_CHECK(weight_scale->is_contiguous() && activation_scale->is_contiguous(),
+                    "weight_scale / activation_scale must be contiguous.");
+        TORCH_CHECK(weight_scale->numel() == N2, "weight_scale must have 2H elements.");
+        TORCH_CHECK(activation_scale->numel() == M, "activation_scale must have TokensNum elements.");
+    } else {
+        TORCH_CHECK(xt == torch::kFloat16 || xt == torch::kBFloat16,
+                    "dequant_swiglu_quant supports int32 / float16 / bfloat16 inputs.");
+        TORCH_CHECK(!present(weight_scale), "weight_scale must be None for float16 / bfloat16 inputs.");
+        TORCH_CHECK(!present(activation_scale), "activation_scale must be None for float16 / bfloat16 inputs.");
+    }
+    const bool has_q = present(quant_scale);
+    if (has_q) {
+        TORCH_CHECK(quant_scale->scalar_type() == torch::kFloat, "quant_scale must be float32.");
+        TORCH_CHECK(quant_scale->is_contiguous(), "quant_scale must be contiguous.");
+        TORCH_CHECK(quant_scale->numel() == H, "quant_scale must have H elements.");
+    }
+    const int code = is_i32 ? W8A8_DT_I32 : dtype_code(x);
+    check_status(w8a8_dequant_swiglu_quant(x.data_ptr(),
+                                           is_i32 ? static_cast<const float*>(weight_scale->data_ptr()) : nullptr,
+                                           is_i32 ? static_cast<const float*>(activation_scale->data_ptr()) : nullptr,
+                                           has_q ? static_cast<const float*>(quant_scale->data_ptr()) : nullptr,
+                                           static_cast<int8_t*>(std::get<0>(outs).data_ptr()),
+                                           static_cast<float*>(std::get<1>(outs).data_ptr()), M, H, code,
+                                           activate_left ? 1 : 0, 0, stream_of(x)),
+                 "dequant_swiglu_quant");
+    return outs;
+}
+
 TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 {
+    m.def("dequant_swiglu_quant(Tensor x, Tensor? weight_scale=None, Tensor? activation_scale=None, "
+          "Tensor? quant_scale=None, bool activate_left=False) -> (Tensor y, Tensor scale)");
     m.def("moe_gating_top_k_softmax(Tensor x, Tensor? finished=None, int k=1) -> "
           "(Tensor y, Tensor expert_idx, Tensor row_idx)");
     m.def("moe_finalize_routing(Tensor expanded_permuted_rows, Tensor expanded_src_to_dst_row, "
@@ -637,6 +707,7 @@ TORCH_LIBRARY_IMPL(cann_bench, Meta, m)
     m.impl("moe_re_routing", moe_re_routing_meta);
     m.impl("moe_finalize_routing", mfr_meta);
     m.impl("moe_gating_top_k_softmax", gating_meta);
+    m.impl("dequant_swiglu_quant", dqsq_meta);
 }
 
 TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
@@ -649,6 +720,7 @@ TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
     m.impl("moe_re_routing", moe_re_routing_cuda);
     m.impl("moe_finalize_routing", mfr_cuda);
     m.impl("moe_gating_top_k_softmax", gating_cuda);
+    m.impl("dequant_swiglu_quant", dqsq_cuda);
 }
 
 }  // namespace cann_bench

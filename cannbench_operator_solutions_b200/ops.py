@@ -40,6 +40,8 @@ def _dt(t: torch.Tensor) -> int:
         return L.DT_F32
     if t.dtype == torch.int8:
         return L.DT_I8
+    if t.dtype == torch.int32:
+        return L.DT_I32
     raise RuntimeError(f"unsupported dtype {t.dtype}")
 
 
@@ -458,3 +460,51 @@ def moe_gating_top_k_softmax(x: torch.Tensor, finished: Optional[torch.Tensor] =
                                                     ri.data_ptr(), rows, inner, k, _dt(xc), _stream())
     _status(rc, "moe_gating_top_k_softmax")
     return y, ei, ri
+
+
+def dequant_swiglu_quant(x: torch.Tensor, weight_scale: Optional[torch.Tensor] = None,
+                         activation_scale: Optional[torch.Tensor] = None, quant_scale: Optional[torch.Tensor] = None,
+                         activate_left: bool = False, *, round_direct: bool = False
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``dequant_swiglu_quant(Tensor x, Tensor? weight_scale=None, Tensor? activation_scale=None,
+    Tensor? quant_scale=None, bool activate_left=False) -> (Tensor y, Tensor scale)``
+    (operators/dequantswigluquant/csrc/ops/dequant_swiglu_quant/op_plugin/dqsq_plugin.cpp:31-56 for the schema and
+    shapes, 62-111 for the checks).
+
+    ``x`` [TokensNum, 2H] int32 (then both scales are required) or float16 / bfloat16 (then both must be None);
+    returns int8 ``y`` [TokensNum, H] and float32 ``scale`` [TokensNum]."""
+    _check(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].")
+    m, n2 = x.shape
+    _check(n2 % 2 == 0, "dequant_swiglu_quant requires an even last dimension.")
+    h = n2 // 2
+    _need_cuda(x, weight_scale, activation_scale, quant_scale)
+    _check(x.is_contiguous(), "dequant_swiglu_quant requires a contiguous input.")
+    y = torch.empty((m, h), dtype=torch.int8, device=x.device)
+    scale = torch.empty((m,), dtype=torch.float32, device=x.device)
+    if m <= 0 or n2 <= 0:
+        return y, scale
+    if x.dtype == torch.int32:
+        _check(weight_scale is not None, "weight_scale is required when x is int32.")
+        _check(activation_scale is not None, "activation_scale is required when x is int32.")
+        _check(weight_scale.dtype == torch.float32, "weight_scale must be float32.")
+        _check(activation_scale.dtype == torch.float32, "activation_scale must be float32.")
+        _check(weight_scale.is_contiguous() and activation_scale.is_contiguous(),
+               "weight_scale / activation_scale must be contiguous.")
+        _check(weight_scale.numel() == n2, "weight_scale must have 2H elements.")
+        _check(activation_scale.numel() == m, "activation_scale must have TokensNum elements.")
+    else:
+        _check(x.dtype in (torch.float16, torch.bfloat16),
+               "dequant_swiglu_quant supports int32 / float16 / bfloat16 inputs.")
+        _check(weight_scale is None, "weight_scale must be None for float16 / bfloat16 inputs.")
+        _check(activation_scale is None, "activation_scale must be None for float16 / bfloat16 inputs.")
+    if quant_scale is not None:
+        _check(quant_scale.dtype == torch.float32, "quant_scale must be float32.")
+        _check(quant_scale.is_contiguous(), "quant_scale must be contiguous.")
+        _check(quant_scale.numel() == h, "quant_scale must have H elements.")
+    with torch.cuda.device(x.device):
+        rc = L.load().w8a8_dequant_swiglu_quant(x.data_ptr(), _ptr(weight_scale), _ptr(activation_scale),
+                                                _ptr(quant_scale), y.data_ptr(), scale.data_ptr(), m, h, _dt(x),
+                                                1 if activate_left else 0, L.F_ROUND_DIRECT if round_direct else 0,
+                                                _stream())
+    _status(rc, "dequant_swiglu_quant")
+    return y, scale

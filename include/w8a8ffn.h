@@ -19,7 +19,7 @@
  *   - Return value: W8A8_OK or a negative W8A8_ERR_* code.  Nothing throws.
  *     A call with zero rows is a successful no-op, as in the reference
  *     plugins.
- *   - dtype codes: W8A8_DT_F16 / W8A8_DT_BF16 / W8A8_DT_F32 / W8A8_DT_I8.
+ *   - dtype codes: W8A8_DT_F16 / W8A8_DT_BF16 / W8A8_DT_F32 / W8A8_DT_I8 / W8A8_DT_I32.
  *   - Row-major, densely packed tensors.  Rows that are 16-byte aligned
  *     take the vectorised kernels; anything else takes a slower generic path
  *     with identical results.
@@ -47,6 +47,7 @@ extern "C" {
 #define W8A8_DT_BF16 1
 #define W8A8_DT_F32 2
 #define W8A8_DT_I8 3
+#define W8A8_DT_I32 4
 
 /* `flags` of the quantising operators */
 #define W8A8_F_ROUND_DIRECT 1 /* fp32 -> int8 in one rounding instead of the
@@ -329,6 +330,22 @@ int w8a8_moe_finalize_routing(const void* rows, const int32_t* src_to_dst_row, c
 int w8a8_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
                                   int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype,
                                   void* stream);
+
+/*
+ * DequantSwigluQuant: x [M, 2H] int32 (a matmul accumulator; needs weight_scale fp32 [2H] and activation_scale
+ * fp32 [M]) or F16 / BF16 (both scales must be NULL); A = x[:, :H], B = x[:, H:] after dequantisation
+ * d = (float(x) * weight_scale) * activation_scale[row].  activate_left == 0: out = silu(B) * A, otherwise
+ * out = silu(A) * B, evaluated as (A * B) / (1 + exp(-gate)); the optional quant_scale fp32 [H] multiplies the
+ * half that is not the gate input; s = max(max|out| / 127, 1e-12); y = narrow(clamp(out / s, -128, 127)) int8
+ * [M, H], scale fp32 [M]; rows whose padded half is longer than 1984 elements use out * (1 / s), as the
+ * reference's long-row layout does.  flags: W8A8_F_ROUND_DIRECT.
+ * Replaces launch_dqsq_{int32,half,bfloat16}
+ * (operators/dequantswigluquant/csrc/ops/dequant_swiglu_quant/op_kernel/dqsq_launch.h; formula in
+ * dqsq_kernel.cpp:14-28).
+ */
+int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const float* activation_scale,
+                              const float* quant_scale, int8_t* y, float* scale, int64_t M, int64_t H,
+                              int x_dtype, int activate_left, int flags, void* stream);
 
 #ifdef __cplusplus
 }

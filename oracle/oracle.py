@@ -19,7 +19,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_ref", "libw8a8_oracle.so")
 
-DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
+DT_F16, DT_BF16, DT_F32, DT_I8, DT_I32 = 0, 1, 2, 3, 4
 ROUND_AS_WRITTEN, ROUND_DIRECT = 0, 1
 SUM_CANONICAL, SUM_FP64 = 0, 1
 EXP_CANONICAL, EXP_LIBM = 0, 1
@@ -88,6 +88,8 @@ def load() -> ctypes.CDLL:
     lib.oracle_moe_finalize_routing.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, i32, i32]
     lib.oracle_moe_gating_top_k_softmax.restype = i32
     lib.oracle_moe_gating_top_k_softmax.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32]
+    lib.oracle_dequant_swiglu_quant.restype = i32
+    lib.oracle_dequant_swiglu_quant.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp]
     lib.oracle_num_threads.restype = i32
     _lib = lib
     return lib
@@ -329,3 +331,22 @@ def moe_gating_top_k_softmax(x, dtype: int, k: int, finished=None):
     if rc != 0:
         raise ValueError("oracle_moe_gating_top_k_softmax rejected the arguments")
     return y, ei, ri
+
+
+def dequant_swiglu_quant(x, x_dtype: int, *, weight_scale=None, activation_scale=None, quant_scale=None,
+                         activate_left: bool = False, round_mode: int = ROUND_AS_WRITTEN, want_out: bool = False):
+    """x [M, 2H]: int32 (DT_I32) or uint16 bit patterns (DT_F16 / DT_BF16) -> (y int8 [M, H], scale fp32 [M])."""
+    x = _c(x, np.int32 if x_dtype == DT_I32 else np.uint16)
+    m, n2 = x.shape
+    h = n2 // 2
+    y = np.empty((m, h), np.int8)
+    sc = np.empty((m,), np.float32)
+    out = np.empty((m, h), np.float32) if want_out else None
+    ws = None if weight_scale is None else _c(weight_scale, np.float32)
+    a_s = None if activation_scale is None else _c(activation_scale, np.float32)
+    qs = None if quant_scale is None else _c(quant_scale, np.float32)
+    rc = load().oracle_dequant_swiglu_quant(_p(x), _p(ws), _p(a_s), _p(qs), _p(y), _p(sc), m, h, x_dtype,
+                                            1 if activate_left else 0, round_mode, _p(out))
+    if rc != 0:
+        raise ValueError("oracle_dequant_swiglu_quant rejected the arguments")
+    return (y, sc, out) if want_out else (y, sc)

@@ -971,3 +971,81 @@ int oracle_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------ */
+/* DequantSwigluQuant                                                        */
+/* DQSQ/op_kernel/dqsq_kernel.cpp, in the order its vector instructions run: */
+/* weight_scale (:335-347), quant_scale on the half that is not the gate     */
+/* input (:349-363), activation_scale on both halves (:386-410), the gate    */
+/* out = (a*b) / (1 + exp(gate * -1)) (:415-428), row maximum with           */
+/* not-greater-than-zero read as 0 (:489-495), s = max(m*(1/127), 1e-12)     */
+/* (:496-499), out / s in the batched short-row layout (:482) and            */
+/* out * (1/s) otherwise (:500-504): here the division is used when the      */
+/* half-row padded to 32 bytes of the input type is at most 1984 elements    */
+/* (:97), the reciprocal for longer rows; clamp to [-128, 127] (:509-510),   */
+/* fp32 -> fp16 -> int8 (:516-524).  A NaN activation quantises to 0.        */
+/* ------------------------------------------------------------------------ */
+int oracle_dequant_swiglu_quant(const void* x, const float* weight_scale, const float* activation_scale,
+                                const float* quant_scale, int8_t* y, float* scale, int64_t M, int64_t H,
+                                int x_dtype, int activate_left, int round_mode, float* out_f32)
+{
+    const int is_i32 = (x_dtype == W8A8_DT_I32);
+    if (!is_i32 && x_dtype != W8A8_DT_F16 && x_dtype != W8A8_DT_BF16) {
+        return -1;
+    }
+    if (M < 0 || H <= 0 || is_i32 != (weight_scale != NULL) || is_i32 != (activation_scale != NULL)) {
+        return -1;
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < M; ++r) {
+        float* out = (float*)malloc((size_t)H * sizeof(float));
+        float m = 0.0f;
+        for (int64_t j = 0; j < H; ++j) {
+            float a, b;
+            if (is_i32) {
+                a = (float)((const int32_t*)x)[r * 2 * H + j] * weight_scale[j];
+                b = (float)((const int32_t*)x)[r * 2 * H + H + j] * weight_scale[H + j];
+            } else {
+                a = load_as_f32(x, r * 2 * H + j, x_dtype);
+                b = load_as_f32(x, r * 2 * H + H + j, x_dtype);
+            }
+            if (quant_scale != NULL) {
+                if (activate_left) {
+                    b = b * quant_scale[j];
+                } else {
+                    a = a * quant_scale[j];
+                }
+            }
+            if (is_i32) {
+                a = a * activation_scale[r];
+                b = b * activation_scale[r];
+            }
+            const float gate = activate_left ? a : b;
+            const float den = oracle_expf(gate * -1.0f) + 1.0f;
+            out[j] = (a * b) / den;
+            m = fmaxf(m, fabsf(out[j]));
+            if (out_f32 != NULL) {
+                out_f32[r * H + j] = out[j];
+            }
+        }
+        float s = m * (1.0f / 127.0f);
+        if (s < 1e-12f) {
+            s = 1e-12f;
+        }
+        scale[r] = s;
+        const int64_t pad = is_i32 ? 8 : 16;
+        const int divide = ((H + pad - 1) / pad * pad <= 1984);
+        const float inv = 1.0f / s;
+        for (int64_t j = 0; j < H; ++j) {
+            float q = divide ? out[j] / s : out[j] * inv;
+            if (q != q) {
+                y[r * H + j] = 0;
+                continue;
+            }
+            q = fmaxf(fminf(q, 127.0f), -128.0f);
+            y[r * H + j] = oracle_narrow_i8(q, round_mode);
+        }
+        free(out);
+    }
+    return 0;
+}

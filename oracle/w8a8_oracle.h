@@ -33,6 +33,7 @@ extern "C" {
 #define W8A8_DT_BF16 1
 #define W8A8_DT_F32 2
 #define W8A8_DT_I8 3
+#define W8A8_DT_I32 4
 
 #define W8A8_ROUND_AS_WRITTEN 0
 #define W8A8_ROUND_DIRECT 1
@@ -124,6 +125,12 @@ int oracle_moe_finalize_routing(const void* rows, const int32_t* esdr, const voi
  * equals), their columns (inner for finished rows) and row_idx = j * rows + r. */
 int oracle_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* y, int32_t* expert_idx,
                                     int32_t* row_idx, int64_t rows, int64_t inner, int64_t k, int dtype);
+
+/* DequantSwigluQuant: x [M, 2H] int32 (with weight_scale [2H], activation_scale [M]) or F16 / BF16;
+ * out_f32 (optional) receives the fp32 activations before quantisation. */
+int oracle_dequant_swiglu_quant(const void* x, const float* weight_scale, const float* activation_scale,
+                                const float* quant_scale, int8_t* y, float* scale, int64_t M, int64_t H,
+                                int x_dtype, int activate_left, int round_mode, float* out_f32);
 
 int oracle_num_threads(void);
 

@@ -106,6 +106,10 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 64, 65, L.DT_BF16, None) == L.ERR_INVALID
     assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 64, 2, L.DT_I8, None) == L.ERR_INVALID
     assert lib.w8a8_moe_gating_top_k_softmax(p, None, p, p, p, 4, 1025, 2, L.DT_F32, None) == L.ERR_LIMIT
+    assert lib.w8a8_dequant_swiglu_quant(p, p, p, None, p, p, 0, 64, L.DT_I32, 0, 0, None) == L.OK
+    assert lib.w8a8_dequant_swiglu_quant(p, None, p, None, p, p, 4, 64, L.DT_I32, 0, 0, None) == L.ERR_INVALID
+    assert lib.w8a8_dequant_swiglu_quant(p, p, None, None, p, p, 4, 64, L.DT_BF16, 0, 0, None) == L.ERR_INVALID
+    assert lib.w8a8_dequant_swiglu_quant(p, None, None, None, p, p, 4, 64, L.DT_F32, 0, 0, None) == L.ERR_INVALID
     assert lib.w8a8_combine(p, p, p, p, 0, 2, 64, L.DT_BF16, None) == L.OK
     assert lib.w8a8_combine(p, p, p, p, 4, 2, 64, L.DT_F32, None) == L.ERR_INVALID
 
@@ -144,3 +148,7 @@ def test_operator_wrappers_validate_like_the_reference_plugins():
         ops.moe_gating_top_k_softmax(torch.zeros(4, 8), k=9)
     with pytest.raises(RuntimeError, match="rank >= 2"):
         ops.moe_gating_top_k_softmax(torch.zeros(8), k=1)
+    with pytest.raises(RuntimeError, match="even last dimension"):
+        ops.dequant_swiglu_quant(torch.zeros(2, 7, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="2D input"):
+        ops.dequant_swiglu_quant(torch.zeros(8, dtype=torch.bfloat16))

@@ -479,3 +479,35 @@ def test_moe_gating_top_k_softmax_hand_derived_and_against_fp64(oracle):
     assert np.abs(got - want).max() <= 2.0**-8 * want.max()
     with pytest.raises(ValueError):
         oracle.moe_gating_top_k_softmax(x, oracle.DT_F32, 257)
+
+
+def test_dequant_swiglu_quant_hand_derived(oracle):
+    """One row, H = 2, int32 input.  x = [4, -8 | 0, 0] with unit weight scales and activation scale 0.5:
+    a = [2, -4], b = [0, 0].  activate_left = 0 gates on b: out = (a*b)/(1+exp(0)) = [0, -0] -> scale clamps to
+    1e-12, y = 0.  activate_left = 1 gates on a with b = [1, 1] (x = [4, -8 | 2, 2]):
+    out = a*b/(1+exp(-a)) = [2/(1+e^-2), -4/(1+e^4)]."""
+    x = np.array([[4, -8, 0, 0]], np.int32)
+    ws = np.ones(4, F)
+    a_s = np.array([0.5], F)
+    y, s = oracle.dequant_swiglu_quant(x, oracle.DT_I32, weight_scale=ws, activation_scale=a_s)
+    assert y.tolist() == [[0, 0]] and s[0] == np.float32(1e-12)
+    x = np.array([[4, -8, 2, 2]], np.int32)
+    y, s, out = oracle.dequant_swiglu_quant(x, oracle.DT_I32, weight_scale=ws, activation_scale=a_s,
+                                            activate_left=True, want_out=True)
+    want = np.array([2.0 / (1.0 + np.exp(-2.0)), -4.0 / (1.0 + np.exp(4.0))])
+    assert np.abs(out[0] - want).max() < 1e-6
+    assert abs(s[0] - want[0] / 127.0) < 1e-8 and y[0, 0] == 127 and y[0, 1] == round(want[1] / (want[0] / 127.0))
+    # quant_scale multiplies the half that is not the gate input: gating on a, it scales b
+    y2, s2, out2 = oracle.dequant_swiglu_quant(x, oracle.DT_I32, weight_scale=ws, activation_scale=a_s,
+                                               quant_scale=np.array([2.0, 0.5], F), activate_left=True,
+                                               want_out=True)
+    assert np.allclose(out2[0], want * np.array([2.0, 0.5]), rtol=1e-6)
+    # 16-bit input takes no scales; activate_left = 0 gates on the right half
+    xb = oracle.f32_to_bf16_bits(np.array([[3.0, 1.0, 2.0, -1.0]], F))
+    _, _, out3 = oracle.dequant_swiglu_quant(xb, oracle.DT_BF16, want_out=True)
+    want3 = np.array([3.0 * 2.0 / (1.0 + np.exp(-2.0)), 1.0 * -1.0 / (1.0 + np.exp(1.0))])
+    assert np.abs(out3[0] - want3).max() < 1e-6
+    with pytest.raises(ValueError):
+        oracle.dequant_swiglu_quant(xb, oracle.DT_BF16, weight_scale=ws)
+    with pytest.raises(ValueError):
+        oracle.dequant_swiglu_quant(x, oracle.DT_I32, weight_scale=ws)

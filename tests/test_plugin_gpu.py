@@ -107,3 +107,20 @@ def test_plugin_moe_gating_matches_ctypes_operator(cb, ops):
         cb.moe_gating_top_k_softmax(x, None, 0)
     with pytest.raises(RuntimeError, match="bool 'finished'"):
         cb.moe_gating_top_k_softmax(x, fin.to(torch.int32), 2)
+
+
+def test_plugin_dequant_swiglu_quant_matches_ctypes_operator(cb, ops):
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.randint(-100000, 100000, (50, 512), generator=g, device="cuda", dtype=torch.int32)
+    ws = torch.rand((512,), generator=g, device="cuda") * 1e-2
+    a_s = torch.rand((50,), generator=g, device="cuda") * 1e-2
+    qs = torch.rand((256,), generator=g, device="cuda") + 0.5
+    for a, b in zip(cb.dequant_swiglu_quant(x, ws, a_s, qs, True), ops.dequant_swiglu_quant(x, ws, a_s, qs, True)):
+        assert torch.equal(a, b)
+    xb = torch.randn((20, 128), generator=g, device="cuda").to(torch.bfloat16)
+    for a, b in zip(cb.dequant_swiglu_quant(xb), ops.dequant_swiglu_quant(xb)):
+        assert torch.equal(a, b)
+    with pytest.raises(RuntimeError, match="weight_scale is required"):
+        cb.dequant_swiglu_quant(x)
+    with pytest.raises(RuntimeError, match="must be None for float16"):
+        cb.dequant_swiglu_quant(xb, ws[:128])

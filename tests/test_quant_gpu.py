@@ -137,3 +137,56 @@ def test_add_rms_norm_dynamic_quant_full_size_properties(ops, oracle):
     yo, xoo, sco = oracle.add_rms_norm_dynamic_quant(bits(x1[idx]), bits(x2[idx]), bits(gamma), 1e-6, oracle.DT_BF16)
     assert np.array_equal(y[idx].cpu().numpy(), yo)
     assert_same_f32(sc[idx], sco, "scaleOut sample")
+
+
+@pytest.mark.parametrize("xdtype", [torch.int32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,h", [(64, 2048), (7, 24), (3, 4096), (5, 20480), (130, 256), (2, 7), (9, 9000)])
+@pytest.mark.parametrize("left", [False, True])
+def test_dequant_swiglu_quant_matches_oracle(ops, oracle, xdtype, m, h, left):
+    from helpers import assert_same_f32, bits, seed_of
+    g = torch.Generator(device="cuda").manual_seed(seed_of("dqsq", str(xdtype), m, h, left))
+    if xdtype == torch.int32:
+        x = torch.randint(-200000, 200000, (m, 2 * h), generator=g, device="cuda", dtype=torch.int32)
+        ws = torch.empty((2 * h,), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+        a_s = torch.empty((m,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+        x[0, :] = 0                                          # an all-zero row: scale clamps to 1e-12
+        kw = dict(weight_scale=ws, activation_scale=a_s)
+        okw = dict(weight_scale=ws.cpu().numpy(), activation_scale=a_s.cpu().numpy())
+        ox = x.cpu().numpy()
+        code = oracle.DT_I32
+    else:
+        x = (torch.randn((m, 2 * h), generator=g, device="cuda") * 3).to(xdtype)
+        if m > 1:
+            x[1, 3] = float("nan")                           # a NaN activation quantises to 0
+        kw, okw, ox = {}, {}, bits(x)
+        code = oracle.DT_BF16 if xdtype == torch.bfloat16 else oracle.DT_F16
+    qs = torch.empty((h,), device="cuda").uniform_(0.5, 2.0, generator=g)
+    for quant_scale in (None, qs):
+        y, sc = ops.dequant_swiglu_quant(x, quant_scale=quant_scale, activate_left=left, **kw)
+        wy, wsc = oracle.dequant_swiglu_quant(ox, code, quant_scale=None if quant_scale is None else qs.cpu().numpy(),
+                                              activate_left=left, **okw)
+        assert y.shape == (m, h) and y.dtype == torch.int8 and sc.shape == (m,)
+        assert_same_f32(sc, wsc, "dqsq scale")
+        assert np.array_equal(y.cpu().numpy(), wy)
+    y, _ = ops.dequant_swiglu_quant(x, activate_left=left, round_direct=True, **kw)
+    wy, _ = oracle.dequant_swiglu_quant(ox, code, activate_left=left, round_mode=oracle.ROUND_DIRECT, **okw)
+    assert np.array_equal(y.cpu().numpy(), wy)
+
+
+def test_dequant_swiglu_quant_is_the_unfused_form_of_the_grouped_epilogue(ops, oracle):
+    """int32 accumulators -> dequant_swiglu_quant(activate_left=True) against grouped_matmul_swiglu_quant on the
+    same operands: the fused operator gates on the left half too; its dequantisation multiplies by the token scale
+    first and its quantisation multiplies by 127/amax, so the int8 results may differ by one step on a few elements
+    and the scales by an ulp."""
+    g = torch.Generator(device="cuda").manual_seed(99)
+    m, k, n = 256, 512, 1024
+    x = torch.randint(-127, 128, (m, k), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (1, k, n), generator=g, device="cuda", dtype=torch.int8)
+    ws = torch.empty((1, n), device="cuda").uniform_(1e-3, 1e-2, generator=g)
+    xs = torch.empty((m,), device="cuda").uniform_(1e-3, 5e-2, generator=g)
+    y_fused, s_fused = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, [m])
+    acc = (x.double() @ w[0].double()).to(torch.int32)
+    y, s = ops.dequant_swiglu_quant(acc, ws.view(-1), xs, None, True)
+    assert torch.allclose(s, s_fused, rtol=1e-5)
+    diff = (y.int() - y_fused.int()).abs()
+    assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 2e-2
