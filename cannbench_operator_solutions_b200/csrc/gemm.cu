@@ -149,19 +149,24 @@ static cudaError_t dispatch_gemm(int cta_group, int block_n, bool b_mn, const CU
 }
 
 // Kernel shape: CTA pairs for dense problems with enough rows to fill 256-row tiles.  The environment variable
-// W8A8_GEMM_CTA_GROUP (1 or 2) overrides the choice; the tests use it to run every case on both shapes.
+// W8A8_GEMM_CTA_GROUP (1, 2, or 3 = pairs plus singles for grouped problems) overrides the choice; the tests use it
+// to run every case on every shape.
+constexpr int GEMM_SHAPE_HYBRID = 3;
+
 static int choose_cta_group(int64_t rows, bool grouped)
 {
     if (const char* env = getenv("W8A8_GEMM_CTA_GROUP")) {
         const int v = atoi(env);
-        if (v == 1 || v == 2) {
+        if (v == 1 || v == 2 || (v == GEMM_SHAPE_HYBRID && grouped)) {
             return v;
         }
     }
-    // Grouped problems keep 128-row tiles: with skewed group sizes the rows a 256-row tile pads at the end of
-    // every group cost more than pairing gains (measured on the 256-expert Zipf configuration).
+    // Grouped problems with enough rows run in two launches: CTA pairs on every group's 256-row blocks (the last
+    // one partial when it holds more than 128 rows) and single CTAs on leftovers of at most 128 rows.  Pairs on everything would pad the end of every group to 256 rows,
+    // which with skewed group sizes costs more than pairing gains (measured on the 256-expert Zipf configuration:
+    // 4.94 ms against 4.66 ms with 128-row tiles only).
     if (grouped) {
-        return 1;
+        return rows >= 2048 ? GEMM_SHAPE_HYBRID : 1;
     }
     return rows >= 256 ? 2 : 1;
 }
@@ -177,10 +182,21 @@ struct GroupEndsByValue {
     int32_t ends[PLAN_MAX_BY_VALUE];
 };
 
+// mode PLAN_ALL: every row of a group, in tiles of tile_m (the last one partial).
+// mode PLAN_WHOLE: the whole tile_m-row tiles of a group, plus its last partial tile when that holds more than
+//                  tile_m / 2 rows (as a pair tile it pads no more rows than two single tiles would).
+// mode PLAN_LEFTOVER: what a group leaves over after its (2 * tile_m)-row blocks when that is at most tile_m rows:
+//                  one tile of tile_m.
+// PLAN_WHOLE at 256 rows and PLAN_LEFTOVER at 128 rows together cover every row exactly once.
+constexpr int PLAN_ALL = 0;
+constexpr int PLAN_WHOLE = 1;
+constexpr int PLAN_LEFTOVER = 2;
+
 __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restrict__ dev_list,
                                                           const GroupEndsByValue by_value, int use_by_value,
                                                           int64_t E, int64_t M, GroupedHeader* header,
-                                                          TileEntry* tiles, int64_t max_tiles, int tile_m)
+                                                          TileEntry* tiles, int64_t max_tiles, int tile_m, int mode,
+                                                          int32_t* shared_error)
 {
     extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
     __shared__ int32_t s_warp_sum[8];
@@ -207,7 +223,16 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
             if (e < prev || e > M || (g == E - 1 && e != M)) {
                 s_bad = 1;
             } else {
-                cnt = static_cast<int32_t>((static_cast<uint32_t>(e - prev) + tile_m - 1) / static_cast<uint32_t>(tile_m));
+                const uint32_t rows = static_cast<uint32_t>(e - prev);
+                const uint32_t tm = static_cast<uint32_t>(tile_m);
+                if (mode == PLAN_WHOLE) {
+                    cnt = static_cast<int32_t>(rows / tm) + ((rows % tm > tm / 2) ? 1 : 0);
+                } else if (mode == PLAN_LEFTOVER) {
+                    const uint32_t rest = rows % (2 * tm);
+                    cnt = (rest >= 1 && rest <= tm) ? 1 : 0;
+                } else {
+                    cnt = static_cast<int32_t>((rows + tm - 1) / tm);
+                }
             }
         }
         int32_t incl = cnt;
@@ -242,6 +267,9 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
         s_first[E] = total;
         header->num_m_tiles = bad ? 0 : total;
         header->error = bad;
+        if (bad && shared_error != nullptr) {
+            *shared_error = 1;  // the error word the caller reads lives in the first header
+        }
     }
     __syncthreads();
     if (bad) {
@@ -249,8 +277,13 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
     }
     // one warp per group at a time fills that group's tile entries
     for (int64_t g = wid; g < E; g += 8) {
-        const int64_t start = (g == 0) ? 0 : end_of(g - 1);
-        const int64_t rows = end_of(g) - start;
+        int64_t start = (g == 0) ? 0 : end_of(g - 1);
+        int64_t rows = end_of(g) - start;
+        if (mode == PLAN_LEFTOVER) {
+            const int64_t whole = rows / (2 * tile_m) * (2 * tile_m);
+            start += whole;
+            rows -= whole;
+        }
         const int32_t first = s_first[g];
         const int32_t cnt = s_first[g + 1] - first;
         for (int32_t t = lane; t < cnt; t += 32) {
@@ -329,6 +362,11 @@ struct GroupedWorkspace {
     int64_t max_tiles;
     uint32_t* amax;
     float* act;
+    // second tile table: what a group leaves over after its 256-row blocks when that is at most 128 rows (one tile
+    // per group), used when the blocks run on CTA pairs and these leftovers on single CTAs
+    GroupedHeader* tail_header;
+    TileEntry* tail_tiles;
+    int64_t tail_max_tiles;
     size_t total;
 };
 
@@ -346,14 +384,43 @@ static GroupedWorkspace carve_workspace(void* ws, int64_t M, int64_t E, int64_t 
     off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * sizeof(uint32_t), 256) : 0;
     g.act = reinterpret_cast<float*>(p + off);
     off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * act_cols * sizeof(float), 256) : 0;
+    g.tail_header = reinterpret_cast<GroupedHeader*>(p + off);
+    off += align_up_sz(sizeof(GroupedHeader), 256);
+    g.tail_max_tiles = E + 1;
+    g.tail_tiles = reinterpret_cast<TileEntry*>(p + off);
+    off += align_up_sz(static_cast<size_t>(g.tail_max_tiles) * sizeof(TileEntry), 256);
     g.total = off;
     return g;
 }
 
+// A host group list is checked before any CUDA call is made for the operator.
+static int check_host_group_list(const int64_t* group_list, int list_on_device, int64_t E, int64_t M)
+{
+    if (list_on_device) {
+        return W8A8_OK;
+    }
+    if (E > PLAN_MAX_BY_VALUE) {
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    int64_t prev = 0;
+    for (int64_t i = 0; i < E; ++i) {
+        const int64_t v = group_list[i];
+        if (v < prev || v > M) {
+            return W8A8_ERR_GROUP_LIST;
+        }
+        prev = v;
+    }
+    return (prev == M) ? W8A8_OK : W8A8_ERR_GROUP_LIST;
+}
+
 // returns W8A8_OK or an error; launches the planner on `st`
 static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E, int64_t M,
-                       const GroupedWorkspace& g, int tile_m, cudaStream_t st)
+                       const GroupedWorkspace& g, int tile_m, cudaStream_t st, int mode = PLAN_ALL)
 {
+    GroupedHeader* header = (mode == PLAN_LEFTOVER) ? g.tail_header : g.header;
+    TileEntry* tiles = (mode == PLAN_LEFTOVER) ? g.tail_tiles : g.tiles;
+    const int64_t max_tiles = (mode == PLAN_LEFTOVER) ? g.tail_max_tiles : g.max_tiles;
+    int32_t* shared_error = (mode == PLAN_LEFTOVER) ? &g.header->error : nullptr;
     GroupEndsByValue bv;
     int use_bv = 0;
     const int64_t* dev_list = group_list;
@@ -383,8 +450,48 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
     if (smem > 48 * 1024) {
         return W8A8_ERR_UNSUPPORTED;
     }
-    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, g.header, g.tiles, g.max_tiles, tile_m);
+    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, header, tiles, max_tiles, tile_m, mode,
+                                             shared_error);
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+// Runs a grouped problem whose GemmParams are filled in except for the tile table: plans the groups and launches
+// the kernel shape(s) choose_cta_group picked.
+template <int KIND, int EPI>
+static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E, int64_t M, const GroupedWorkspace& g,
+                       bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st)
+{
+    const int shape = choose_cta_group(M, true);
+    p.grouped = 1;
+    p.error = &g.header->error;
+    if (shape != GEMM_SHAPE_HYBRID) {
+        const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * shape, st);
+        if (rc != W8A8_OK) {
+            return rc;
+        }
+        p.tiles = g.tiles;
+        p.header = g.header;
+        const cudaError_t e = dispatch_gemm<KIND, EPI>(shape, 256, b_mn, ta, tb, p, g.max_tiles * p.n_tiles, st);
+        return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+    }
+    int rc = plan_groups(group_list, list_on_device, E, M, g, 256, st, PLAN_WHOLE);
+    if (rc != W8A8_OK) {
+        return rc;
+    }
+    rc = plan_groups(group_list, list_on_device, E, M, g, 128, st, PLAN_LEFTOVER);
+    if (rc != W8A8_OK) {
+        return rc;
+    }
+    p.tiles = g.tiles;
+    p.header = g.header;
+    cudaError_t e = dispatch_gemm<KIND, EPI>(2, 256, b_mn, ta, tb, p, (M / 256 + E + 1) * p.n_tiles, st);
+    if (e != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    p.tiles = g.tail_tiles;
+    p.header = g.tail_header;
+    e = dispatch_gemm<KIND, EPI>(1, 256, b_mn, ta, tb, p, g.tail_max_tiles * p.n_tiles, st);
+    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
 }  // namespace w8a8
@@ -540,10 +647,9 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GroupedWorkspace g = carve_workspace(workspace, M, E, H);
     if (run_matmul) {
-        const int cg = choose_cta_group(M, true);
-        const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * cg, st);
-        if (rc != W8A8_OK) {
-            return rc;
+        const int list_rc = check_host_group_list(group_list, list_on_device, E, M);
+        if (list_rc != W8A8_OK) {
+            return list_rc;
         }
         if (cudaMemsetAsync(g.amax, 0, static_cast<size_t>(M) * sizeof(uint32_t), st) != cudaSuccess) {
             return W8A8_ERR_CUDA;
@@ -559,18 +665,13 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.K = K;
         p.num_k_blocks = static_cast<int32_t>((K + GEMM_KBYTES - 1) / GEMM_KBYTES);
         p.n_tiles = static_cast<int32_t>((H + 127) / 128);
-        p.grouped = 1;
-        p.tiles = g.tiles;
-        p.header = g.header;
-        p.error = &g.header->error;
         p.scale = w_scale;
         p.row_scale = x_scale;
         p.act = g.act;
         p.amax = g.amax;
-        const int64_t max_total = g.max_tiles * p.n_tiles;
-        const cudaError_t e = dispatch_gemm<KIND_I8, EPI_GMSQ>(cg, 256, b_mn, ta, tb, p, max_total, st);
-        if (e != cudaSuccess) {
-            return W8A8_ERR_CUDA;
+        const int rc = run_grouped<KIND_I8, EPI_GMSQ>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
+        if (rc != W8A8_OK) {
+            return rc;
         }
     }
     if (!run_requant) {
@@ -663,10 +764,9 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GroupedWorkspace g = carve_workspace(workspace, M, E, 0);
-    const int cg = choose_cta_group(M, true);
-    const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * cg, st);
-    if (rc != W8A8_OK) {
-        return rc;
+    const int list_rc = check_host_group_list(group_list, list_on_device, E, M);
+    if (list_rc != W8A8_OK) {
+        return list_rc;
     }
     const bool b_mn = (w_layout == W8A8_W_KN);
     CUtensorMap ta, tb;
@@ -679,10 +779,6 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
     p.K = K;
     const int block_k = GEMM_KBYTES / elem;
     p.num_k_blocks = static_cast<int32_t>((K + block_k - 1) / block_k);
-    p.grouped = 1;
-    p.tiles = g.tiles;
-    p.header = g.header;
-    p.error = &g.header->error;
     p.scale = w_scale;
     p.row_scale = x_scale;
     p.bias = bias;
@@ -690,18 +786,14 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
     p.out_row_ptrs = out_row_ptrs;
     p.flags = (bias != nullptr ? 4 : 0) | (bias_dtype & 3);
     p.out_dtype = out_dtype;
-    const int block_n = 256;
-    p.n_tiles = static_cast<int32_t>((N + block_n - 1) / block_n);
-    const int64_t max_total = g.max_tiles * p.n_tiles;
-    cudaError_t e;
+    p.n_tiles = static_cast<int32_t>((N + 255) / 256);
     if (kind == KIND_I8) {
-        e = dispatch_gemm<KIND_I8, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
-    } else if (kind == KIND_F16) {
-        e = dispatch_gemm<KIND_F16, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
-    } else {
-        e = dispatch_gemm<KIND_BF16, EPI_GMM>(cg, block_n, b_mn, ta, tb, p, max_total, st);
+        return run_grouped<KIND_I8, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
     }
-    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+    if (kind == KIND_F16) {
+        return run_grouped<KIND_F16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
+    }
+    return run_grouped<KIND_BF16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
 }
 
 extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y, const float* x_scale,

@@ -17,14 +17,17 @@ pytestmark = pytest.mark.gpu
 F = np.float32
 
 
-@pytest.fixture(autouse=True, params=["auto", "single", "pair"])
+@pytest.fixture(autouse=True, params=["auto", "single", "pair", "hybrid"])
 def cta_group(request, monkeypatch):
-    """Every test runs with the library's own choice of kernel shape, with single-CTA tiles forced and with
-    CTA-pair (cta_group::2) tiles forced: all three must give identical results."""
+    """Every test runs with the library's own choice of kernel shape, with single-CTA tiles forced, with CTA-pair
+    (cta_group::2) tiles forced, and with the two-launch form of grouped problems forced (pairs on whole 256-row
+    blocks, single CTAs on the leftovers; dense problems ignore it): all must give identical results."""
     if request.param == "single":
         monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "1")
     elif request.param == "pair":
         monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "2")
+    elif request.param == "hybrid":
+        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "3")
     else:
         monkeypatch.delenv("W8A8_GEMM_CTA_GROUP", raising=False)
     return request.param
