@@ -342,10 +342,11 @@ class GmsqWorkload(Workload):
         self._call(0)
 
     def kernel_step(self):
-        """The tensor-core stage alone (plan + matmul with the fused dequant/SwiGLU/row-max epilogue)."""
+        """The tensor-core stage alone (tile planners + the two matmul launches with the fused dequant / SwiGLU /
+        row-max epilogue)."""
         self._call(self.L.F_STAGE_MATMUL)
 
-    kernels_per_step = 4  # plan, row-max clear (memset), matmul, requant
+    kernels_per_step = 5  # two tile-table planners, pair-tile matmul, single-tile matmul, requant (+ one memset)
 
     def ops_per_step(self):
         return 2.0 * self.m * self.K * self.N
