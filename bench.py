@@ -282,7 +282,9 @@ class GmsqWorkload(Workload):
     name, metric, unit, dtype, bound = ("grouped_matmul_swiglu_quant", "gmm_swiglu_quant_int8_tops", "TOPS", "int8",
                                         "tensor")
     E, M, K, N = 256, 131072, 7168, 4096
-    traffic = 10.66e9  # E=32 / 16384-row capture (1.333 GB per launch) scaled by 8 in rows and experts
+    # DRAM bytes of the matmul stage (its two launches): E=32 / 16384-row capture (1.059 GB pair tiles + 0.431 GB
+    # leftover tiles), scaled by 8 in rows and experts
+    traffic = 11.92e9
     traffic_source = "profiles/gemm_tc_kernel_gmsq_e32.md"
 
     def __init__(self, small=False):
