@@ -351,3 +351,32 @@ def test_gmsq_full_size_sampled_rows(ops, oracle, cta_group):
                                                      ws[ex:ex + 1].cpu().numpy(), xs[lo:hi].cpu().numpy(), [hi - lo])
         assert_same_f32(ysc[lo:hi], yso, f"y_scale of expert {ex}")
         assert np.array_equal(y[lo:hi].cpu().numpy(), yo), f"expert {ex}"
+
+
+@pytest.mark.parametrize("chunk", [96, 1000, 5000])
+def test_host_front_end_equals_the_whole_tensor_operator(ops, chunk, cta_group):
+    """Rows pipelined through the host-buffer front end in chunks (which start and end inside experts) give the
+    same bytes as one call on the whole tensor."""
+    from cannbench_operator_solutions_b200.host_io import GroupedSwigluQuantFromHost
+
+    if cta_group != "auto":
+        pytest.skip("kernel shape does not matter here")
+    rng = np.random.default_rng(seed_of("front", chunk))
+    e, k, n = 7, 256, 512
+    counts = np.array([300, 0, 1, 700, 129, 0, 1270])
+    m = int(counts.sum())
+    gl = np.cumsum(counts).tolist()
+    x = _i8(rng, (m, k))
+    w = _i8(rng, (e, k, n))
+    ws = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n)).astype(F)).cuda()
+    xs = torch.from_numpy(rng.uniform(1e-3, 5e-2, m).astype(F)).cuda()
+    want_y, want_s = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, gl)
+    front = GroupedSwigluQuantFromHost(w, ws, chunk_rows=chunk)
+    got_y, got_s = front(x.cpu().pin_memory(), xs.cpu().pin_memory(), gl)
+    torch.cuda.synchronize()
+    assert torch.equal(got_y, want_y.cpu()) and torch.equal(got_s, want_s.cpu())
+    got_y2, got_s2 = front(x.cpu().pin_memory(), xs.cpu().pin_memory(), gl)      # buffers are reusable
+    torch.cuda.synchronize()
+    assert torch.equal(got_y2, want_y.cpu()) and torch.equal(got_s2, want_s.cpu())
+    with pytest.raises(RuntimeError, match="cumsum"):
+        front(x.cpu(), xs.cpu(), [5, 3] + gl[2:])
