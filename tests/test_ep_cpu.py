@@ -148,3 +148,37 @@ def test_two_rank_chain_equals_single_rank():
     # conservation: every (token, k) pair arrived at exactly one expert
     total = sum(int(ret[r][2].sum()) for r in range(world))
     assert total == 48 * 2
+
+
+def test_expert_placement_covers_every_row_once_and_balances_tiles():
+    """The benchmark's shard of the grouped workload: both placements hand out every expert's rows exactly once;
+    the replicating one balances 128-row tiles across ranks and splits experts only at tile boundaries."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+
+    rng = np.random.default_rng(0)
+    counts = bench.zipf_counts(rng, 131072, 256)
+    for world in (1, 2, 4, 8):
+        for mode in ("lpt", "replicate"):
+            members, loads, replicas = bench.place_experts(counts, world, mode)
+            got = np.zeros_like(counts)
+            for rank_members in members:
+                for e, rows in rank_members:
+                    got[e] += rows
+            assert np.array_equal(got, counts) and sum(loads) == int(counts.sum())
+            if mode == "lpt":
+                assert replicas == 0 and all(len(m) == 256 // world for m in members)
+            else:
+                tiles = [sum(-(-rows // 128) for _, rows in m) for m in members]
+                assert max(tiles) - min(tiles) <= 2
+                pieces = {}
+                for rank_members in members:
+                    for e, rows in rank_members:
+                        pieces.setdefault(e, []).append(rows)
+                for e, parts in pieces.items():     # a split expert: every piece but one is whole tiles
+                    assert sum(1 for r in parts if r % 128 != 0) <= 1
+    # at 8 ranks whole experts cannot balance (one expert holds more than a rank's share); replication can
+    _, loads_lpt, _ = bench.place_experts(counts, 8, "lpt")
+    _, loads_rep, replicas = bench.place_experts(counts, 8, "replicate")
+    assert max(loads_lpt) / (sum(loads_lpt) / 8) > 1.5
+    assert max(loads_rep) / (sum(loads_rep) / 8) < 1.2 and replicas >= 1
