@@ -47,7 +47,7 @@ static CUtensorMapDataType tm_dtype(int kind)
 }
 
 // A: [rows, K] row-major.  Box = 128 bytes of K x 128 rows.
-static bool make_map_a(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int kind)
+static bool make_map_a(CUtensorMap* m, const void* base, int64_t rows, int64_t K, int kind, int box_rows = 128)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
@@ -56,7 +56,7 @@ static bool make_map_a(CUtensorMap* m, const void* base, int64_t rows, int64_t K
     const int elem = (kind == KIND_I8) ? 1 : 2;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * elem};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), 128};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     return fn(m, tm_dtype(kind), 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -543,11 +543,15 @@ static int quant_matmul_impl(const int8_t* x1, const int8_t* x2, const void* sca
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool b_mn = (x2_layout == W8A8_W_KN);
+    // With fewer than 128 rows in all, the A load only brings the rows that exist (rounded up to 8): the rest of the
+    // 128-row shared-memory tile keeps whatever it held, which only reaches accumulator rows the epilogue never stores.
+    const int a_box_rows = (batch * M < 128) ? static_cast<int>((batch * M + 7) / 8 * 8) : 128;
     CUtensorMap ta, tb;
-    if (!make_map_a(&ta, x1, batch * M, K, KIND_I8) || !make_map_b(&tb, x2, batch, N, K, KIND_I8, b_mn)) {
+    if (!make_map_a(&ta, x1, batch * M, K, KIND_I8, a_box_rows) || !make_map_b(&tb, x2, batch, N, K, KIND_I8, b_mn)) {
         return W8A8_ERR_CUDA;
     }
     GemmParams p{};
+    p.a_box_bytes = a_box_rows * GEMM_KBYTES;
     p.M = M;
     p.N = N;
     p.K = K;
@@ -665,6 +669,7 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
             return W8A8_ERR_CUDA;
         }
         GemmParams p{};
+        p.a_box_bytes = GEMM_A_BYTES;
         p.M = M;
         p.N = N;
         p.K = K;
@@ -779,6 +784,7 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
         return W8A8_ERR_CUDA;
     }
     GemmParams p{};
+    p.a_box_bytes = GEMM_A_BYTES;
     p.M = M;
     p.N = N;
     p.K = K;

@@ -91,6 +91,7 @@ struct GemmParams {
     int32_t out_dtype;
     int64_t bias_batch_stride;
     const uint64_t* out_row_ptrs;  // GMM: when set, row r is stored at this address instead of out + r*N
+    int32_t a_box_bytes;  // bytes one A load delivers: GEMM_A_BYTES, or less when the A map's box has fewer rows
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
 };
@@ -573,7 +574,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         // complete first: the barrier's phase cannot end before the leader's arrival, and a
                         // transaction count may run ahead of its announcement.
                         if (leader) {
-                            tc::mbar_arrive_expect_tx(full_bar(stage), CG * STAGE_BYTES);
+                            tc::mbar_arrive_expect_tx(full_bar(stage), CG * (static_cast<uint32_t>(p.a_box_bytes) + B_BYTES));
                         }
                         if constexpr (CG == 2) {
                             tc::tma_load_2d_pair(a_dst, &tm_a, fb, kb * BLOCK_K, tl.a_row0);
