@@ -80,6 +80,10 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
             s = __fadd_rn(s, __shfl_xor_sync(FULL_MASK, s, off));
         }
         const bool fin = (finished != nullptr) && (finished[r] != 0);
+        // Lane j keeps the j-th selection and the lanes store together after every 32 rounds: one division and one
+        // store instruction per 32 results instead of one per result.
+        uint32_t keep_top = 0u;
+        uint32_t keep_win = 0xffffffffu;
         for (int j = 0; j < k; ++j) {
             // this lane's best remaining element: largest value, then smallest index (ascending i is ascending index)
             float best = -1.0f;
@@ -104,12 +108,19 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
                     }
                 }
             }
-            if (lane == 0) {
-                const float e = (top != 0u) ? __uint_as_float(top - 1u) : NAN;
-                const int64_t o = r * k + j;
-                gating_store<DT>(y, o, __fdiv_rn(e, s));
-                expert_idx[o] = fin ? inner : static_cast<int32_t>(win);
-                row_idx[o] = static_cast<int32_t>(static_cast<int64_t>(j) * rows + r);
+            if (lane == (j & 31)) {
+                keep_top = top;
+                keep_win = win;
+            }
+            if ((j & 31) == 31 || j == k - 1) {
+                const int jj = (j & ~31) + lane;  // the round this lane holds
+                if (jj <= j) {
+                    const float e = (keep_top != 0u) ? __uint_as_float(keep_top - 1u) : NAN;
+                    const int64_t o = r * k + jj;
+                    gating_store<DT>(y, o, __fdiv_rn(e, s));
+                    expert_idx[o] = fin ? inner : static_cast<int32_t>(keep_win);
+                    row_idx[o] = static_cast<int32_t>(static_cast<int64_t>(jj) * rows + r);
+                }
             }
         }
     }
