@@ -133,3 +133,96 @@ class GroupedSwigluQuantFromHost:
             if len(returned) > 1:
                 main.wait_event(returned[-2])
         return y, y_scale
+
+
+class RowQuantFromHost:
+    """``dynamic_quant`` / ``add_rms_norm_dynamic_quant`` for 16-bit rows that live in pinned host memory.
+
+    ``fused=False``: x -> (y int8, scale).  ``fused=True``: (x1, x2) with a device-resident gamma ->
+    (y int8, x_out, scale).  Rows travel and compute ``chunk_rows`` at a time over a copy-in stream, the current
+    stream and a copy-out stream, with double-buffered device staging."""
+
+    def __init__(self, n: int, dtype: torch.dtype, device, *, fused: bool, gamma: Optional[torch.Tensor] = None,
+                 epsilon: float = 1e-6, chunk_rows: int = 1024):
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise RuntimeError("RowQuantFromHost: rows must be float16 or bfloat16")
+        if fused and (gamma is None or not gamma.is_cuda or gamma.dtype != dtype or gamma.numel() != n):
+            raise RuntimeError("RowQuantFromHost: the fused form needs a CUDA gamma of the rows' dtype and length")
+        self.n, self.dtype, self.fused, self.eps, self.chunk = n, dtype, fused, float(epsilon), int(chunk_rows)
+        self.gamma = gamma.contiguous() if fused else None
+        self.dev = torch.device(device)
+        self.code = L.DT_BF16 if dtype == torch.bfloat16 else L.DT_F16
+        self.lib = L.load()
+        with torch.cuda.device(self.dev):
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            mk = lambda dt, *shape: [torch.empty(shape, dtype=dt, device=self.dev) for _ in range(2)]
+            self.x1 = mk(dtype, self.chunk, n)
+            self.x2 = mk(dtype, self.chunk, n) if fused else None
+            self.y = mk(torch.int8, self.chunk, n)
+            self.xo = mk(dtype, self.chunk, n) if fused else None
+            self.sc = mk(torch.float32, self.chunk)
+
+    def __call__(self, x1: torch.Tensor, x2: Optional[torch.Tensor] = None, out: Optional[Sequence[torch.Tensor]] = None):
+        rows = x1.size(0)
+        if x1.is_cuda or x1.dtype != self.dtype or x1.dim() != 2 or x1.size(1) != self.n:
+            raise RuntimeError("RowQuantFromHost: x must be a host tensor [rows, N] of the configured dtype")
+        if self.fused and (x2 is None or x2.shape != x1.shape or x2.dtype != self.dtype or x2.is_cuda):
+            raise RuntimeError("RowQuantFromHost: the fused form needs a second host tensor of the same shape")
+        if out is None:
+            out = [torch.empty((rows, self.n), dtype=torch.int8).pin_memory()]
+            if self.fused:
+                out.append(torch.empty((rows, self.n), dtype=self.dtype).pin_memory())
+            out.append(torch.empty((rows,), dtype=torch.float32).pin_memory())
+        y_h, sc_h = out[0], out[-1]
+        xo_h = out[1] if self.fused else None
+        if rows == 0:
+            return tuple(out)
+        lib = self.lib
+        with torch.cuda.device(self.dev):
+            main = torch.cuda.current_stream()
+            start = torch.cuda.Event()
+            start.record(main)
+            self.s_in.wait_event(start)
+            self.s_out.wait_event(start)
+            computed: List[torch.cuda.Event] = []
+            returned: List[torch.cuda.Event] = []
+            for i, r0 in enumerate(range(0, rows, self.chunk)):
+                r1 = min(rows, r0 + self.chunk)
+                b, m = i % 2, r1 - r0
+                with torch.cuda.stream(self.s_in):
+                    if i >= 2:
+                        self.s_in.wait_event(computed[i - 2])
+                    self.x1[b][:m].copy_(x1[r0:r1], non_blocking=True)
+                    if self.fused:
+                        self.x2[b][:m].copy_(x2[r0:r1], non_blocking=True)
+                    arrived = torch.cuda.Event()
+                    arrived.record(self.s_in)
+                main.wait_event(arrived)
+                if i >= 2:
+                    main.wait_event(returned[i - 2])
+                if self.fused:
+                    rc = lib.w8a8_add_rms_norm_dynamic_quant(self.x1[b].data_ptr(), self.x2[b].data_ptr(),
+                                                             self.gamma.data_ptr(), self.y[b].data_ptr(),
+                                                             self.xo[b].data_ptr(), self.sc[b].data_ptr(), m, self.n,
+                                                             self.eps, self.code, 0, main.cuda_stream)
+                else:
+                    rc = lib.w8a8_dynamic_quant(self.x1[b].data_ptr(), self.y[b].data_ptr(), self.sc[b].data_ptr(), m,
+                                                self.n, self.code, 0, main.cuda_stream)
+                if rc != L.OK:
+                    raise RuntimeError(f"RowQuantFromHost: {L.status_string(rc)} (status {rc})")
+                done = torch.cuda.Event()
+                done.record(main)
+                computed.append(done)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(done)
+                    y_h[r0:r1].copy_(self.y[b][:m], non_blocking=True)
+                    if self.fused:
+                        xo_h[r0:r1].copy_(self.xo[b][:m], non_blocking=True)
+                    sc_h[r0:r1].copy_(self.sc[b][:m], non_blocking=True)
+                    back = torch.cuda.Event()
+                    back.record(self.s_out)
+                returned.append(back)
+            main.wait_event(returned[-1])
+            if len(returned) > 1:
+                main.wait_event(returned[-2])
+        return tuple(out)

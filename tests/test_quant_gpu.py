@@ -190,3 +190,27 @@ def test_dequant_swiglu_quant_is_the_unfused_form_of_the_grouped_epilogue(ops, o
     assert torch.allclose(s, s_fused, rtol=1e-5)
     diff = (y.int() - y_fused.int()).abs()
     assert int(diff.max()) <= 1 and float((diff > 0).float().mean()) < 2e-2
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_host_front_end_equals_the_whole_tensor_operators(ops, fused):
+    """Rows pipelined through the host-buffer front end in chunks give the same bytes as one call."""
+    from cannbench_operator_solutions_b200.host_io import RowQuantFromHost
+
+    g = torch.Generator(device="cuda").manual_seed(31)
+    rows, n = 1000, 1536
+    x1 = torch.randn((rows, n), generator=g, device="cuda").to(torch.bfloat16)
+    x2 = torch.randn((rows, n), generator=g, device="cuda").to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn((n,), generator=g, device="cuda")).to(torch.bfloat16)
+    front = RowQuantFromHost(n, torch.bfloat16, "cuda", fused=fused, gamma=gamma if fused else None, chunk_rows=96)
+    for _ in range(2):   # staging buffers are reusable
+        if fused:
+            want = ops.add_rms_norm_dynamic_quant(x1, x2, gamma, 1e-6)
+            got = front(x1.cpu().pin_memory(), x2.cpu().pin_memory())
+        else:
+            want = ops.dynamic_quant(x1)
+            got = front(x1.cpu().pin_memory())
+        torch.cuda.synchronize()
+        assert len(got) == len(want)
+        for a, b in zip(got, want):
+            assert torch.equal(a.view(torch.uint8), b.cpu().view(torch.uint8))
