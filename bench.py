@@ -476,8 +476,9 @@ class ChainWorkload(Workload):
         return {"workload": f"configs[4]: W8A8 MoE FFN chain T={self.T} hidden={self.HID} inter={self.INTER} "
                             f"E={self.E} top-{self.TOPK}", "tokens_per_gpu": self.T // world,
                 "experts_per_gpu": self.E // world, "l2": "weights (11.3 GB) and activations larger than L2",
-                "parallelism": (f"ep{world} ({getattr(self, 'transport', 'p2p')} dispatch/combine)" if world > 1
-                                else "single GPU")}
+                "parallelism": (f"ep{world} ({getattr(self, 'transport', 'p2p')} dispatch/combine"
+                                f"{', device-built tables' if getattr(self, 'device_tables', False) else ''})"
+                                if world > 1 else "single GPU")}
 
     def gpu_setup(self, torch, rank, world):
         import cannbench_operator_solutions_b200 as pkg
@@ -500,7 +501,8 @@ class ChainWorkload(Workload):
             torch.empty((e_local, 2 * self.INTER), device="cuda").uniform_(1e-3, 1e-2, generator=g),
             torch.randint(-127, 128, (e_local, self.INTER, self.HID), generator=g, device="cuda", dtype=torch.int8),
             torch.empty((e_local, self.HID), device="cuda").uniform_(1e-3, 1e-2, generator=g))
-        self.chain = MoeFfnChain(self.E, shard, transport=getattr(self, "transport", "p2p"))
+        self.chain = MoeFfnChain(self.E, shard, transport=getattr(self, "transport", "p2p"),
+                                 device_tables=getattr(self, "device_tables", False))
         self.scaling = "strong"
 
     def gpu_step(self):
@@ -876,6 +878,8 @@ def main():
     ap.add_argument("--layout", choices=["kn", "nk"], default="kn", help="weight layout of the matmul workloads")
     ap.add_argument("--transport", choices=["p2p", "nccl"], default="p2p",
                     help="chain workload: fused peer-memory stores or NCCL all-to-all for dispatch / combine")
+    ap.add_argument("--device-tables", action="store_true",
+                    help="chain workload, p2p transport: build the address tables on the device (no host readback)")
     ap.add_argument("--placement", choices=["replicate", "lpt"], default="replicate",
                     help="grouped workload on several GPUs: split hot experts across ranks (weights replicated) or "
                          "keep experts whole")
@@ -893,6 +897,7 @@ def main():
     wl.layout_nk = (args.layout == "nk")
     wl.transport = args.transport
     wl.placement = args.placement
+    wl.device_tables = args.device_tables
     if args.impl == "reference":
         run_reference(args, wl)
         return

@@ -31,6 +31,7 @@ QM_BIAS_NONE, QM_BIAS_I32, QM_BIAS_F16, QM_BIAS_BF16, QM_BIAS_F32 = 0, 1, 2, 3, 
 
 # every symbol include/w8a8ffn.h declares: (name, restype, argtypes)
 _vp, _i64, _i32, _f32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+_u64 = ctypes.c_uint64
 SIGNATURES = {
     "w8a8_version": (_i32, []),
     "w8a8_status_string": (ctypes.c_char_p, [_i32]),
@@ -55,6 +56,8 @@ SIGNATURES = {
     "w8a8_moe_re_routing_workspace_size": (_sz, [_i64, _i64, _i64]),
     "w8a8_moe_re_routing": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _sz, _vp]),
     "w8a8_dispatch_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "w8a8_ep_tables": (_i32, [_vp, _i64, _i64, _i64, _vp, _u64, _u64, _u64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp,
+                              _vp, _vp, _vp]),
     "w8a8_expand_row_pointers": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "w8a8_grouped_matmul_to_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32,
                                            _i32, _i32, _vp, _sz, _vp]),

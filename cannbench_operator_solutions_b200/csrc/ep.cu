@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) dispatch_rows_kernel(const uint8_t* __res
             const int32_t e = expert_idx[pr];
             const int64_t p = pos[pr];
             uint64_t d = 0;
-            if (p >= 0) {
+            if (p >= 0 && row_dst[e] != 0) {  // a zero destination: the table builder found the buffers too small
                 const int64_t off = p - my_base[e];
                 d = row_dst[e] + static_cast<uint64_t>(off) * static_cast<uint64_t>(row_bytes);
                 if (src_scale != nullptr) {
@@ -595,6 +595,121 @@ __global__ void __launch_bounds__(256) mfr_kernel(const void* __restrict__ rows,
     }
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel address tables, computed on the device from the all-gathered count matrix C[P, E]
+// (C[i][e] = rows rank i routes to global expert e; expert e lives on rank e / (E / P)).
+// Everything dispatch_rows, the grouped matmuls and the row-pointer expansion need, with no host readback:
+//   row_dst[e], scale_dst[e]  where this rank's first row / scale for expert e goes in the owner's buffers
+//   my_base[e]                position of this rank's first pair for expert e in its own expert-major order
+//   group_list[j]             cumulative rows of this rank's local experts (all source ranks)
+//   seg_first / seg_ptr       one segment per (local expert, source rank): first local row, and the address in
+//                             the source rank's return buffer where the segment's first output row goes
+//   status[0]                 1 when some rank would receive more rows than the buffers hold
+// One CTA; thread i < P walks rank i's counts, thread e < E a column.
+// ---------------------------------------------------------------------------
+constexpr int EP_MAX_RANKS = 64;
+constexpr int EP_MAX_CELLS = 2048;  // P * E, held in shared memory
+
+__global__ void __launch_bounds__(1024) ep_tables_kernel(const int64_t* __restrict__ counts, int P, int E, int rank,
+                                                         const uint64_t* __restrict__ peer_base, uint64_t off_x,
+                                                         uint64_t off_s, uint64_t off_back, int64_t row_bytes,
+                                                         int64_t back_row_bytes, int64_t cap_rows,
+                                                         uint64_t* __restrict__ row_dst,
+                                                         uint64_t* __restrict__ scale_dst,
+                                                         int64_t* __restrict__ my_base,
+                                                         int64_t* __restrict__ group_list,
+                                                         int64_t* __restrict__ seg_first,
+                                                         uint64_t* __restrict__ seg_ptr, int32_t* __restrict__ status)
+{
+    __shared__ int64_t s_base[EP_MAX_CELLS];  // [P][E]: rank i's exclusive prefix over experts
+    __shared__ int64_t s_col[1024];           // rows per expert over all ranks
+    __shared__ int64_t s_before[1024];        // rows of lower ranks inside each expert
+    __shared__ int64_t s_exbase[1024];        // expert's first row in its owner's buffer
+    __shared__ int s_bad;
+    const int tid = threadIdx.x;
+    const int e_local = E / P;
+    if (tid == 0) {
+        s_bad = 0;
+    }
+    __syncthreads();
+    if (tid < P) {
+        int64_t run = 0;
+        for (int e = 0; e < E; ++e) {
+            s_base[tid * E + e] = run;
+            run += counts[static_cast<int64_t>(tid) * E + e];
+        }
+    }
+    for (int e = tid; e < E; e += blockDim.x) {
+        int64_t col = 0, before = 0;
+        for (int i = 0; i < P; ++i) {
+            const int64_t c = counts[static_cast<int64_t>(i) * E + e];
+            if (i < rank) {
+                before += c;
+            }
+            col += c;
+        }
+        s_col[e] = col;
+        s_before[e] = before;
+    }
+    __syncthreads();
+    if (tid < P) {  // thread o: the experts of owner o
+        int64_t run = 0;
+        for (int j = 0; j < e_local; ++j) {
+            const int e = tid * e_local + j;
+            s_exbase[e] = run;
+            run += s_col[e];
+            if (tid == rank) {
+                group_list[j] = run;
+            }
+        }
+        if (run > cap_rows) {
+            s_bad = 1;
+        }
+    }
+    __syncthreads();
+    // Too many rows for some rank's buffers: nothing may be stored anywhere.  Every rank sees the same counts, so
+    // every rank takes this branch together: zero destinations (dispatch skips them) and empty groups.
+    const bool bad = (s_bad != 0);
+    for (int e = tid; e < E; e += blockDim.x) {
+        const int owner = e / e_local;
+        const uint64_t first = static_cast<uint64_t>(s_exbase[e] + s_before[e]);
+        row_dst[e] = bad ? 0 : peer_base[owner] + off_x + first * static_cast<uint64_t>(row_bytes);
+        scale_dst[e] = bad ? 0 : peer_base[owner] + off_s + first * 4u;
+        my_base[e] = s_base[rank * E + e];
+    }
+    if (bad) {
+        for (int j = tid; j < e_local; j += blockDim.x) {
+            group_list[j] = 0;
+        }
+        for (int sidx = tid; sidx <= e_local * P; sidx += blockDim.x) {
+            seg_first[sidx] = 0;
+            if (sidx < e_local * P) {
+                seg_ptr[sidx] = 0;
+            }
+        }
+        if (tid == 0) {
+            status[0] = 1;
+        }
+        return;
+    }
+    // segments in (local expert, source rank) order: their first rows are an exclusive prefix in that order
+    if (tid == 0) {
+        int64_t run = 0;
+        for (int j = 0; j < e_local; ++j) {
+            const int e = rank * e_local + j;
+            for (int i = 0; i < P; ++i) {
+                const int sidx = j * P + i;
+                seg_first[sidx] = run;
+                seg_ptr[sidx] = peer_base[i] + off_back +
+                                static_cast<uint64_t>(s_base[i * E + e]) * static_cast<uint64_t>(back_row_bytes);
+                run += counts[static_cast<int64_t>(i) * E + e];
+            }
+        }
+        seg_first[e_local * P] = run;
+        status[0] = s_bad;
+    }
+}
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace w8a8
@@ -934,4 +1049,28 @@ extern "C" int w8a8_moe_finalize_routing(const void* rows, const int32_t* src_to
         return launch_mfr<W8A8_DT_F32>(rows, src_to_dst_row, skip1, skip2, bias, scales, expert_for_source_row, out,
                                        num_rows, H, K, E, num_dst, col_mode, scale_dtype, vec, st);
     }
+}
+
+extern "C" int w8a8_ep_tables(const int64_t* counts, int64_t P, int64_t E, int64_t rank, const uint64_t* peer_base,
+                              uint64_t off_x, uint64_t off_s, uint64_t off_back, int64_t row_bytes,
+                              int64_t back_row_bytes, int64_t cap_rows, uint64_t* row_dst, uint64_t* scale_dst,
+                              int64_t* my_base, int64_t* group_list, int64_t* seg_first, uint64_t* seg_ptr,
+                              int32_t* status, void* stream)
+{
+    if (P <= 0 || E <= 0 || E % P != 0 || rank < 0 || rank >= P || row_bytes <= 0 || back_row_bytes <= 0 ||
+        cap_rows < 0) {
+        return W8A8_ERR_INVALID;
+    }
+    if (P > w8a8::EP_MAX_RANKS || E > 1024 || P * E > w8a8::EP_MAX_CELLS) {
+        return W8A8_ERR_LIMIT;
+    }
+    if (counts == nullptr || peer_base == nullptr || row_dst == nullptr || scale_dst == nullptr ||
+        my_base == nullptr || group_list == nullptr || seg_first == nullptr || seg_ptr == nullptr ||
+        status == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    w8a8::ep_tables_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        counts, static_cast<int>(P), static_cast<int>(E), static_cast<int>(rank), peer_base, off_x, off_s, off_back,
+        row_bytes, back_row_bytes, cap_rows, row_dst, scale_dst, my_base, group_list, seg_first, seg_ptr, status);
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
                                                           const GroupEndsByValue by_value, int use_by_value,
                                                           int64_t E, int64_t M, GroupedHeader* header,
                                                           TileEntry* tiles, int64_t max_tiles, int tile_m, int mode,
-                                                          int32_t* shared_error)
+                                                          int32_t* shared_error, int allow_prefix)
 {
     extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
     __shared__ int32_t s_warp_sum[8];
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
         if (g < E) {
             const int64_t prev = (g == 0) ? 0 : end_of(g - 1);
             const int64_t e = end_of(g);
-            if (e < prev || e > M || (g == E - 1 && e != M)) {
+            if (e < prev || e > M || (g == E - 1 && e != M && !allow_prefix)) {
                 s_bad = 1;
             } else {
                 const uint32_t rows = static_cast<uint32_t>(e - prev);
@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
         s_first[E] = total;
         header->num_m_tiles = bad ? 0 : total;
         header->error = bad;
+        header->rows_total = bad ? 0 : static_cast<int32_t>(end_of(E - 1));
         if (bad && shared_error != nullptr) {
             *shared_error = 1;  // the error word the caller reads lives in the first header
         }
@@ -317,7 +318,8 @@ __global__ void __launch_bounds__(256) gmsq_requant_kernel(const float* __restri
     const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t warps_total = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
     const int64_t n4 = H / 4;
-    for (int64_t row = warp_global; row < M; row += warps_total) {
+    const int64_t rows = min(M, static_cast<int64_t>(header->rows_total));  // a device list may end before M
+    for (int64_t row = warp_global; row < rows; row += warps_total) {
         float amax = __uint_as_float(amax_bits[row]);
         if (!(amax > 1.1754944e-38f)) {
             amax = 1.1754944e-38f;
@@ -396,6 +398,9 @@ static GroupedWorkspace carve_workspace(void* ws, int64_t M, int64_t E, int64_t 
 // A host group list is checked before any CUDA call is made for the operator.
 static int check_host_group_list(const int64_t* group_list, int list_on_device, int64_t E, int64_t M)
 {
+    if (list_on_device < 0 || list_on_device > 2) {
+        return W8A8_ERR_INVALID;
+    }
     if (list_on_device) {
         return W8A8_OK;
     }
@@ -451,7 +456,7 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
         return W8A8_ERR_UNSUPPORTED;
     }
     plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, header, tiles, max_tiles, tile_m, mode,
-                                             shared_error);
+                                             shared_error, list_on_device == 2 ? 1 : 0);
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 

@@ -66,7 +66,8 @@ struct TileEntry {
 struct GroupedHeader {
     int32_t num_m_tiles;
     int32_t error;  // 0 ok, 1 invalid group list, 2 pipeline wait ran out
-    int32_t pad[62];
+    int32_t rows_total;  // the list's last entry: rows the groups cover (may be below M for a device prefix list)
+    int32_t pad[61];
 };
 
 struct GemmParams {

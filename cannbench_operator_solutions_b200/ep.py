@@ -165,6 +165,53 @@ class CudaBackend:
         if rc != 0:
             raise RuntimeError(f"grouped_matmul_to_rows: {L.status_string(rc)}")
 
+    # -- forms that take their row count from a device list (no host readback) ---------------------------
+    def ep_tables(self, gathered, rank, peer_base, off_x, off_s, off_back, row_bytes, back_row_bytes, cap_rows, out):
+        p, e = gathered.shape
+        rc = self.lib.w8a8_ep_tables(gathered.data_ptr(), p, e, rank, peer_base.data_ptr(), off_x, off_s, off_back,
+                                     row_bytes, back_row_bytes, cap_rows, out["row_dst"].data_ptr(),
+                                     out["scale_dst"].data_ptr(), out["my_base"].data_ptr(),
+                                     out["group_list"].data_ptr(), out["seg_first"].data_ptr(),
+                                     out["seg_ptr"].data_ptr(), out["status"].data_ptr(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"ep_tables: {self.L.status_string(rc)}")
+
+    def grouped_matmul_swiglu_quant_capacity(self, x, w, w_scale, x_scale, group_list_dev, y, y_scale, workspace):
+        """x, x_scale, y, y_scale hold `capacity` rows; the device list says how many of them exist."""
+        cap, k = x.shape
+        e, _, n = w.shape
+        L = self.L
+        rc = self.lib.w8a8_grouped_matmul_swiglu_quant(x.data_ptr(), w.data_ptr(), w_scale.data_ptr(),
+                                                       x_scale.data_ptr(), y.data_ptr(), y_scale.data_ptr(), cap, k,
+                                                       n, e, group_list_dev.data_ptr(), 2, L.W_KN, 0,
+                                                       workspace.data_ptr(), workspace.numel(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"grouped_matmul_swiglu_quant: {L.status_string(rc)}")
+
+    def grouped_matmul_int8_to_rows_capacity(self, x, w, group_list_dev, x_scale, w_scale, out_row_ptrs, out_dtype,
+                                             workspace):
+        cap, k = x.shape
+        e, _, n = w.shape
+        L = self.L
+        code = L.DT_BF16 if out_dtype == torch.bfloat16 else L.DT_F16
+        rc = self.lib.w8a8_grouped_matmul_to_rows(x.data_ptr(), w.data_ptr(), None, out_row_ptrs.data_ptr(),
+                                                  x_scale.data_ptr(), w_scale.data_ptr(), cap, n, k, e,
+                                                  group_list_dev.data_ptr(), 2, L.DT_I8, L.DT_F32, code, L.W_KN,
+                                                  workspace.data_ptr(), workspace.numel(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"grouped_matmul_to_rows: {L.status_string(rc)}")
+
+    def expand_row_pointers_into(self, seg_first, seg_ptr, nseg, rows, row_bytes, out):
+        rc = self.lib.w8a8_expand_row_pointers(seg_first.data_ptr(), seg_ptr.data_ptr(), nseg, rows, row_bytes,
+                                               out.data_ptr(), self._st())
+        if rc != 0:
+            raise RuntimeError(f"expand_row_pointers: {self.L.status_string(rc)}")
+
+    def workspace_bytes(self, cap, hidden, inter):
+        lib = self.lib
+        return max(lib.w8a8_grouped_matmul_swiglu_quant_workspace_size(cap, hidden, 2 * inter, 1 << 10),
+                   lib.w8a8_grouped_matmul_workspace_size(cap, hidden, inter, 1 << 10))
+
     def combine(self, rows, probs, pos):
         t, topk = probs.shape
         out = torch.empty((t, rows.shape[1]), dtype=rows.dtype, device=rows.device)
@@ -220,12 +267,17 @@ class PeerBuffers:
 
 class MoeFfnChain:
     def __init__(self, num_experts: int, shard: ExpertShard, backend=None, group=None, transport: str = "nccl",
-                 capacity_rows: Optional[int] = None):
+                 capacity_rows: Optional[int] = None, device_tables: bool = False):
         self.group = group
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' or 'p2p'")
         self.transport = transport
         self.capacity_rows = capacity_rows
+        # p2p transport only: build the address tables on the device from the gathered counts, so that a step has
+        # no host readback at all (the row counts then exist only on the device and the grouped matmuls are
+        # launched on the buffers' capacity with a device list that says how many rows exist)
+        self.device_tables = device_tables
+        self._dev_state = None
         self.peer: Optional[PeerBuffers] = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -333,11 +385,74 @@ class MoeFfnChain:
         out = b.combine(back, probs, pos)
         return out, x_out
 
+    def _forward_p2p_device_tables(self, x, residual, gamma, eps, expert_idx, probs):
+        """The p2p step with no host readback: count all-gather -> ep_tables kernel -> dispatch -> grouped matmuls
+        on the capacity with a device group list -> combine.  `check()` reads the overflow flag when asked."""
+        b = self.backend
+        dev = x.device
+        t, topk = expert_idx.shape
+        hidden = x.shape[1]
+        elem = x.element_size()
+        inter = self.shard.w_down.shape[1]
+        if self.peer is None:
+            cap = self.capacity_rows
+            if cap is None:
+                cap = int(1.5 * t * topk) + 1024
+            self.peer = PeerBuffers(cap, hidden, t * topk, dev, self.world, self.group)
+        pb = self.peer
+        if t * topk > pb.home_rows:
+            raise RuntimeError("expert-parallel return buffer too small for this batch: raise capacity_rows")
+        cap = pb.cap_rows
+        nseg = self.e_local * self.world
+        if self._dev_state is None:
+            i64 = dict(dtype=torch.int64, device=dev)
+            self._dev_state = {
+                "peer_base": torch.tensor([int(p) for p in pb.ptrs], dtype=torch.int64, device=dev),
+                "gathered": torch.empty((self.world, self.E), **i64),
+                "row_dst": torch.empty((self.E,), **i64), "scale_dst": torch.empty((self.E,), **i64),
+                "my_base": torch.empty((self.E,), **i64), "group_list": torch.empty((self.e_local,), **i64),
+                "seg_first": torch.empty((nseg + 1,), **i64), "seg_ptr": torch.empty((nseg,), **i64),
+                "status": torch.zeros((4,), dtype=torch.int32, device=dev),
+                "h": torch.empty((cap, inter), dtype=torch.int8, device=dev),
+                "hs": torch.empty((cap,), dtype=torch.float32, device=dev),
+                "out_ptrs": torch.empty((cap,), **i64),
+                "workspace": torch.empty((b.workspace_bytes(cap, hidden, inter),), dtype=torch.uint8, device=dev),
+            }
+        st = self._dev_state
+        xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)
+        count, _cumsum, pos = b.route_plan(expert_idx, self.E)
+        if self.world > 1:
+            dist.all_gather_into_tensor(st["gathered"], count, group=self.group)
+        else:
+            st["gathered"].copy_(count.view(1, self.E))
+        b.ep_tables(st["gathered"], self.rank, st["peer_base"], pb.off_x, pb.off_s, pb.off_back, hidden,
+                    hidden * elem, cap, st)
+        self._barrier(dev)   # nobody is still reading last step's buffers
+        b.dispatch_rows(xq, xs, expert_idx, pos, st["row_dst"], st["scale_dst"], st["my_base"])
+        self._barrier(dev)   # every rank's rows have landed
+        b.grouped_matmul_swiglu_quant_capacity(pb.xe, self.shard.w_up, self.shard.s_up, pb.xs, st["group_list"],
+                                               st["h"], st["hs"], st["workspace"])
+        b.expand_row_pointers_into(st["seg_first"], st["seg_ptr"], nseg, cap, hidden * elem, st["out_ptrs"])
+        b.grouped_matmul_int8_to_rows_capacity(st["h"], self.shard.w_down, st["group_list"], st["hs"],
+                                               self.shard.s_down, st["out_ptrs"], x.dtype, st["workspace"])
+        self._barrier(dev)   # every rank's output rows have landed at home
+        back = pb.buf[pb.off_back:pb.off_back + t * topk * hidden * elem].view(x.dtype).view(t * topk, hidden)
+        out = b.combine(back, probs, pos)
+        return out, x_out
+
+    def check(self) -> None:
+        """Device-table mode: raises if a step routed more rows to a rank than its buffers hold (reads one flag from
+        the device, so call it when a synchronisation is acceptable)."""
+        if self._dev_state is not None and int(self._dev_state["status"][0].item()) != 0:
+            raise RuntimeError("expert-parallel receive buffer too small for this routing: raise capacity_rows")
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
                 expert_idx: torch.Tensor, probs: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """x, residual [T_local, hidden] fp16/bf16; expert_idx int32 [T_local, topk]; probs fp32 [T_local, topk].
         Returns (ffn_out [T_local, hidden], residual_out [T_local, hidden])."""
         if self.transport == "p2p":
+            if self.device_tables:
+                return self._forward_p2p_device_tables(x, residual, gamma, eps, expert_idx, probs)
             return self._forward_p2p(x, residual, gamma, eps, expert_idx, probs)
         b = self.backend
         t, topk = expert_idx.shape

@@ -144,7 +144,11 @@ int w8a8_matmul_i8_i32(const int8_t* x1, const int8_t* x2, int32_t* c, int64_t b
  * an int64 cumulative list of length E in host memory (validated, then passed
  * by value, E <= 1024) or in device memory (list_on_device = 1; validated on
  * the device: an invalid list leaves y untouched and sets a flag readable
- * with w8a8_workspace_error()).
+ * with w8a8_workspace_error()).  list_on_device = 2 is a device list that may
+ * end below M: M is then an upper bound (the buffers' row capacity) and rows
+ * past the list's last entry are neither read nor written, which lets a
+ * caller that only knows the row count on the device launch without a
+ * readback.
  *   x int8 [M, K]; w int8 [E, K, N] (W8A8_W_KN) or [E, N, K] (W8A8_W_NK);
  *   w_scale fp32 [E, N]; x_scale fp32 [M]; y int8 [M, N/2]; y_scale fp32 [M].
  * K a multiple of 16, N a multiple of 32.
@@ -275,6 +279,21 @@ int w8a8_moe_re_routing(const void* tokens, const void* counts, const float* sca
 int w8a8_dispatch_rows(const void* src, const float* src_scale, const int32_t* expert_idx,
                        const int64_t* expanded_pos, const uint64_t* row_dst, const uint64_t* scale_dst,
                        const int64_t* my_base, int64_t T, int64_t topk, int64_t row_bytes, void* stream);
+
+/*
+ * Address tables of the fused expert-parallel transport, computed on the device from the all-gathered count
+ * matrix counts[P, E] (rows rank i routes to global expert e; expert e lives on rank e / (E / P)), so that a step
+ * needs no host readback.  peer_base[P] are the ranks' buffer addresses as this rank sees them; off_x / off_s /
+ * off_back the byte offsets of the int8 rows, the fp32 scales and the 16-bit return rows inside each buffer.
+ * Outputs: row_dst[E], scale_dst[E], my_base[E] for w8a8_dispatch_rows; group_list[E / P] (cumulative rows of this
+ * rank's experts, a device list for the grouped matmuls with list_on_device = 2); seg_first[(E / P) * P + 1] and
+ * seg_ptr[(E / P) * P] for w8a8_expand_row_pointers; status[0] = 1 when some rank would receive more than cap_rows
+ * rows.  P <= 64, E <= 1024, P * E <= 2048 (W8A8_ERR_LIMIT beyond).  No reference counterpart.
+ */
+int w8a8_ep_tables(const int64_t* counts, int64_t P, int64_t E, int64_t rank, const uint64_t* peer_base,
+                   uint64_t off_x, uint64_t off_s, uint64_t off_back, int64_t row_bytes, int64_t back_row_bytes,
+                   int64_t cap_rows, uint64_t* row_dst, uint64_t* scale_dst, int64_t* my_base,
+                   int64_t* group_list, int64_t* seg_first, uint64_t* seg_ptr, int32_t* status, void* stream);
 
 /* out[r] = seg_ptr[s] + (r - seg_first[s]) * row_bytes for the segment s containing row r (seg_first has
  * nseg + 1 non-decreasing entries): turns a (source rank, expert) segment table into one destination address per

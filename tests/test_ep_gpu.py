@@ -98,6 +98,16 @@ def test_single_gpu_chain_peer_transport_equals_collective_transport(ops):
     for _ in range(2):  # the second pass reuses the buffers of the first
         b, bx = chain.forward(*args)
         assert torch.equal(a, b) and torch.equal(ax, bx)
+    # the same transport with the address tables built on the device (no host readback in the step)
+    chain = MoeFfnChain(experts, shard, transport="p2p", device_tables=True)
+    for _ in range(2):
+        b, bx = chain.forward(*args)
+        assert torch.equal(a, b) and torch.equal(ax, bx)
+    chain.check()
+    tight = MoeFfnChain(experts, shard, transport="p2p", device_tables=True, capacity_rows=256)   # 1200 rows routed
+    tight.forward(*args)
+    with pytest.raises(RuntimeError, match="too small"):
+        tight.check()
 
 
 @pytest.mark.parametrize("tok_dtype", [torch.int8, torch.bfloat16, torch.float16])

@@ -39,11 +39,13 @@ def _worker(rank, world, port, experts, ret):
         args = (x[st].contiguous().to(dev), res[st].contiguous().to(dev), gamma.to(dev), 1e-6,
                 idx[st].contiguous().to(dev), probs[st].contiguous().to(dev))
         out = {}
-        for transport in ("nccl", "p2p"):
-            chain = MoeFfnChain(experts, shard, transport=transport)
+        for transport in ("nccl", "p2p", "p2p-device-tables"):
+            chain = MoeFfnChain(experts, shard, transport=transport.split("-")[0],
+                                device_tables=transport.endswith("device-tables"))
             for _ in range(2):
                 o, xo = chain.forward(*args)
             torch.cuda.synchronize()
+            chain.check()
             out[transport] = (_bits(o.cpu()).copy(), _bits(xo.cpu()).copy())
         ret[rank] = out
     finally:
@@ -74,7 +76,7 @@ def test_two_gpu_chain_both_transports_equal_single_rank(ops):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, port, experts, ret), nprocs=2, join=True)
-    for transport in ("nccl", "p2p"):
+    for transport in ("nccl", "p2p", "p2p-device-tables"):
         got = np.concatenate([ret[r][transport][0] for r in range(2)], 0)
         got_x = np.concatenate([ret[r][transport][1] for r in range(2)], 0)
         assert np.array_equal(got_x, want_x), transport
