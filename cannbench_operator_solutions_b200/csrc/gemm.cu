@@ -172,7 +172,7 @@ static int choose_cta_group(int64_t rows, bool grouped)
 }
 
 // ---------------------------------------------------------------------------
-// Group planner: cumulative group list -> table of 128-row tiles.
+// Group planner: cumulative group list -> table of row tiles (128 rows for single CTAs, 256 for CTA pairs).
 // The list arrives by value (host lists, validated by the caller) or from
 // device memory (validated here; an invalid list yields zero tiles and
 // error = 1).
