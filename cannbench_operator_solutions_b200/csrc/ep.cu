@@ -621,42 +621,65 @@ __global__ void __launch_bounds__(1024) ep_tables_kernel(const int64_t* __restri
                                                          int64_t* __restrict__ seg_first,
                                                          uint64_t* __restrict__ seg_ptr, int32_t* __restrict__ status)
 {
-    __shared__ int64_t s_base[EP_MAX_CELLS];  // [P][E]: rank i's exclusive prefix over experts
-    __shared__ int64_t s_col[1024];           // rows per expert over all ranks
-    __shared__ int64_t s_before[1024];        // rows of lower ranks inside each expert
-    __shared__ int64_t s_exbase[1024];        // expert's first row in its owner's buffer
+    // The whole matrix is staged in shared memory first (one coalesced pass), so that the sequential prefix loops
+    // below run on shared memory instead of waiting for a global load per step.  Row counts fit 32 bits (a rank's
+    // buffers hold fewer than 2^31 rows; larger counts set the overflow flag).
+    __shared__ int32_t s_cnt[EP_MAX_CELLS];   // [P][E]
+    __shared__ int32_t s_base[EP_MAX_CELLS];  // [P][E]: rank i's exclusive prefix over experts
+    __shared__ int32_t s_seg[EP_MAX_CELLS];   // [E/P][P]: first local row of each (local expert, source rank) segment
+    __shared__ int32_t s_col[1024];           // rows per expert over all ranks
+    __shared__ int32_t s_before[1024];        // rows of lower ranks inside each expert
+    __shared__ int32_t s_exbase[1024];        // expert's first row in its owner's buffer
     __shared__ int s_bad;
     const int tid = threadIdx.x;
     const int e_local = E / P;
+    const int cells = P * E;
     if (tid == 0) {
         s_bad = 0;
+    }
+    __syncthreads();
+    const int64_t limit = cap_rows < 0x7fffffffLL ? cap_rows : 0x7fffffffLL;
+    for (int c = tid; c < cells; c += blockDim.x) {
+        const int64_t v = counts[c];
+        if (v < 0 || v > limit) {
+            s_bad = 1;
+        }
+        s_cnt[c] = (v < 0 || v > limit) ? 0 : static_cast<int32_t>(v);
     }
     __syncthreads();
     if (tid < P) {
         int64_t run = 0;
         for (int e = 0; e < E; ++e) {
-            s_base[tid * E + e] = run;
-            run += counts[static_cast<int64_t>(tid) * E + e];
+            s_base[tid * E + e] = static_cast<int32_t>(run);
+            run += s_cnt[tid * E + e];
+        }
+        if (run > 0x7fffffffLL) {
+            s_bad = 1;
         }
     }
     for (int e = tid; e < E; e += blockDim.x) {
         int64_t col = 0, before = 0;
         for (int i = 0; i < P; ++i) {
-            const int64_t c = counts[static_cast<int64_t>(i) * E + e];
+            const int32_t c = s_cnt[i * E + e];
             if (i < rank) {
                 before += c;
             }
             col += c;
         }
-        s_col[e] = col;
-        s_before[e] = before;
+        if (col > limit) {
+            s_bad = 1;
+            col = 0;
+            before = 0;
+        }
+        s_col[e] = static_cast<int32_t>(col);
+        s_before[e] = static_cast<int32_t>(before);
     }
     __syncthreads();
     if (tid < P) {  // thread o: the experts of owner o
         int64_t run = 0;
         for (int j = 0; j < e_local; ++j) {
             const int e = tid * e_local + j;
-            s_exbase[e] = run;
+            s_exbase[e] = static_cast<int32_t>(run < 0x7fffffffLL ? run : 0);
             run += s_col[e];
             if (tid == rank) {
                 group_list[j] = run;
@@ -666,47 +689,49 @@ __global__ void __launch_bounds__(1024) ep_tables_kernel(const int64_t* __restri
             s_bad = 1;
         }
     }
+    if (tid == 32) {  // segments in (local expert, source rank) order: exclusive prefix of their lengths
+        int64_t run = 0;
+        for (int j = 0; j < e_local; ++j) {
+            const int e = rank * e_local + j;
+            for (int i = 0; i < P; ++i) {
+                s_seg[j * P + i] = static_cast<int32_t>(run < 0x7fffffffLL ? run : 0);
+                run += s_cnt[i * E + e];
+            }
+        }
+    }
     __syncthreads();
     // Too many rows for some rank's buffers: nothing may be stored anywhere.  Every rank sees the same counts, so
     // every rank takes this branch together: zero destinations (dispatch skips them) and empty groups.
     const bool bad = (s_bad != 0);
+    const int nseg = e_local * P;
     for (int e = tid; e < E; e += blockDim.x) {
         const int owner = e / e_local;
-        const uint64_t first = static_cast<uint64_t>(s_exbase[e] + s_before[e]);
+        const uint64_t first = static_cast<uint64_t>(s_exbase[e]) + static_cast<uint64_t>(s_before[e]);
         row_dst[e] = bad ? 0 : peer_base[owner] + off_x + first * static_cast<uint64_t>(row_bytes);
         scale_dst[e] = bad ? 0 : peer_base[owner] + off_s + first * 4u;
         my_base[e] = s_base[rank * E + e];
+    }
+    for (int sidx = tid; sidx < nseg; sidx += blockDim.x) {
+        const int j = sidx / P, i = sidx - j * P;
+        const int e = rank * e_local + j;
+        seg_first[sidx] = bad ? 0 : s_seg[sidx];
+        seg_ptr[sidx] = bad ? 0
+                            : peer_base[i] + off_back +
+                                  static_cast<uint64_t>(s_base[i * E + e]) * static_cast<uint64_t>(back_row_bytes);
     }
     if (bad) {
         for (int j = tid; j < e_local; j += blockDim.x) {
             group_list[j] = 0;
         }
-        for (int sidx = tid; sidx <= e_local * P; sidx += blockDim.x) {
-            seg_first[sidx] = 0;
-            if (sidx < e_local * P) {
-                seg_ptr[sidx] = 0;
-            }
-        }
-        if (tid == 0) {
-            status[0] = 1;
-        }
-        return;
     }
-    // segments in (local expert, source rank) order: their first rows are an exclusive prefix in that order
     if (tid == 0) {
-        int64_t run = 0;
+        // the last local expert's cumulative count is the number of rows this rank holds
+        int64_t total = 0;
         for (int j = 0; j < e_local; ++j) {
-            const int e = rank * e_local + j;
-            for (int i = 0; i < P; ++i) {
-                const int sidx = j * P + i;
-                seg_first[sidx] = run;
-                seg_ptr[sidx] = peer_base[i] + off_back +
-                                static_cast<uint64_t>(s_base[i * E + e]) * static_cast<uint64_t>(back_row_bytes);
-                run += counts[static_cast<int64_t>(i) * E + e];
-            }
+            total += s_col[rank * e_local + j];
         }
-        seg_first[e_local * P] = run;
-        status[0] = s_bad;
+        seg_first[nseg] = bad ? 0 : total;
+        status[0] = bad ? 1 : 0;
     }
 }
 
