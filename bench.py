@@ -477,7 +477,7 @@ class ChainWorkload(Workload):
                             f"E={self.E} top-{self.TOPK}", "tokens_per_gpu": self.T // world,
                 "experts_per_gpu": self.E // world, "l2": "weights (11.3 GB) and activations larger than L2",
                 "parallelism": (f"ep{world} ({getattr(self, 'transport', 'p2p')} dispatch/combine"
-                                f"{', device-built tables' if getattr(self, 'device_tables', False) else ''})"
+                                f"{', device-built tables' if getattr(getattr(self, 'chain', None), 'device_tables', False) else ''})"
                                 if world > 1 else "single GPU")}
 
     def gpu_setup(self, torch, rank, world):
@@ -502,7 +502,7 @@ class ChainWorkload(Workload):
             torch.randint(-127, 128, (e_local, self.INTER, self.HID), generator=g, device="cuda", dtype=torch.int8),
             torch.empty((e_local, self.HID), device="cuda").uniform_(1e-3, 1e-2, generator=g))
         self.chain = MoeFfnChain(self.E, shard, transport=getattr(self, "transport", "p2p"),
-                                 device_tables=getattr(self, "device_tables", False))
+                                 device_tables=getattr(self, "device_tables", None))
         self.scaling = "strong"
 
     def gpu_step(self):
@@ -878,8 +878,9 @@ def main():
     ap.add_argument("--layout", choices=["kn", "nk"], default="kn", help="weight layout of the matmul workloads")
     ap.add_argument("--transport", choices=["p2p", "nccl"], default="p2p",
                     help="chain workload: fused peer-memory stores or NCCL all-to-all for dispatch / combine")
-    ap.add_argument("--device-tables", action="store_true",
-                    help="chain workload, p2p transport: build the address tables on the device (no host readback)")
+    ap.add_argument("--tables", choices=["auto", "host", "device"], default="auto",
+                    help="chain workload, p2p transport: where the address tables are built (device: no host "
+                         "readback in the step; auto: device from 4 ranks up)")
     ap.add_argument("--placement", choices=["replicate", "lpt"], default="replicate",
                     help="grouped workload on several GPUs: split hot experts across ranks (weights replicated) or "
                          "keep experts whole")
@@ -897,7 +898,7 @@ def main():
     wl.layout_nk = (args.layout == "nk")
     wl.transport = args.transport
     wl.placement = args.placement
-    wl.device_tables = args.device_tables
+    wl.device_tables = {"auto": None, "host": False, "device": True}[args.tables]
     if args.impl == "reference":
         run_reference(args, wl)
         return
