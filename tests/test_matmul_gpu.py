@@ -4,7 +4,6 @@ grouped_matmul.  int32 accumulators and int8 outputs are bit-exact; 16-bit
 float outputs of the int8 paths are bit-exact too (same fp32 chain, one
 rounding); only the float grouped_matmul, whose accumulation order the
 reference leaves to its matmul library, is compared with a tolerance."""
-import ctypes
 
 import numpy as np
 import pytest
