@@ -359,7 +359,9 @@ class MoeFfnChain:
         tables = np.stack([row_dst.view(np.int64), scale_dst.view(np.int64), base_of_rank[self.rank].astype(np.int64)])
         tables_dev = torch.from_numpy(tables).to(dev)
 
-        self._barrier(dev)   # nobody is still reading last step's buffers
+        # No barrier is needed before the stores: the count all-gather above has completed on this rank, so every
+        # other rank's stream has reached its own all-gather of this step, which it enqueued after everything
+        # that read its buffers in the previous step.
         b.dispatch_rows(xq, xs, expert_idx, pos, tables_dev[0], tables_dev[1], tables_dev[2])
         self._barrier(dev)   # every rank's rows have landed
 
@@ -430,7 +432,9 @@ class MoeFfnChain:
             st["gathered"].copy_(count.view(1, self.E))
         b.ep_tables(st["gathered"], self.rank, st["peer_base"], pb.off_x, pb.off_s, pb.off_back, hidden,
                     hidden * elem, cap, st)
-        self._barrier(dev)   # nobody is still reading last step's buffers
+        # No barrier is needed before the stores: the count all-gather above has completed on this rank, so every
+        # other rank's stream has reached its own all-gather of this step, which it enqueued after everything
+        # that read its buffers in the previous step.
         b.dispatch_rows(xq, xs, expert_idx, pos, st["row_dst"], st["scale_dst"], st["my_base"])
         self._barrier(dev)   # every rank's rows have landed
         b.grouped_matmul_swiglu_quant_capacity(pb.xe, self.shard.w_up, self.shard.s_up, pb.xs, st["group_list"],
