@@ -366,6 +366,99 @@ __global__ void __launch_bounds__(1024) rr_table_kernel(const CntT* __restrict__
     }
 }
 
+// The same tables for a matrix of at most RR_SMALL_CELLS cells (the usual case: ranks x local experts), with the
+// matrix and every prefix staged in shared memory: the sequential scans then cost a few cycles per step instead
+// of a global-memory round trip.
+constexpr int RR_SMALL_CELLS = 2048;
+
+template <typename CntT>
+__global__ void __launch_bounds__(1024) rr_table_small_kernel(const CntT* __restrict__ cnt, int N, int E, int64_t A,
+                                                              int32_t* __restrict__ hdr,
+                                                              int64_t* __restrict__ dst_first,
+                                                              int64_t* __restrict__ src_first,
+                                                              CntT* __restrict__ expert_num)
+{
+    __shared__ int64_t s_cnt[RR_SMALL_CELLS];
+    // E + N <= cells + 1, so one array of cells + 2 entries holds both prefixes: columns first, rows after them
+    __shared__ int64_t s_sums[RR_SMALL_CELLS + 2];
+    int64_t* s_col = s_sums;          // E + 1 entries: exclusive prefix of the column sums
+    int64_t* s_row = s_sums + E + 1;  // N + 1 entries: exclusive prefix of the row sums
+    __shared__ int s_bad;
+    const int tid = threadIdx.x;
+    const int cells = N * E;
+    if (tid == 0) {
+        s_bad = 0;
+    }
+    __syncthreads();
+    for (int c = tid; c < cells; c += blockDim.x) {
+        const int64_t v = static_cast<int64_t>(cnt[c]);
+        if (v < 0 || v > A) {
+            s_bad = 1;
+        }
+        s_cnt[c] = (v < 0 || v > A) ? 0 : v;
+    }
+    __syncthreads();
+    for (int j = tid; j < E; j += blockDim.x) {
+        int64_t sum = 0;
+        for (int i = 0; i < N; ++i) {
+            sum += s_cnt[i * E + j];
+        }
+        s_col[j + 1] = sum;
+    }
+    for (int i = tid; i < N; i += blockDim.x) {
+        int64_t sum = 0;
+        for (int j = 0; j < E; ++j) {
+            sum += s_cnt[i * E + j];
+        }
+        s_row[i + 1] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int64_t run = 0;
+        s_col[0] = 0;
+        for (int j = 0; j < E; ++j) {
+            run += s_col[j + 1];
+            s_col[j + 1] = run;
+        }
+        if (run > A) {
+            s_bad = 1;
+        }
+    }
+    if (tid == 32) {
+        int64_t run = 0;
+        s_row[0] = 0;
+        for (int i = 0; i < N; ++i) {
+            run += s_row[i + 1];
+            s_row[i + 1] = run;
+        }
+    }
+    __syncthreads();
+    const bool bad = (s_bad != 0);
+    if (tid == 0) {
+        dst_first[cells] = bad ? 0 : s_col[E];
+        hdr[0] = 0;
+        hdr[1] = bad ? 1 : 0;
+    }
+    if (bad) {
+        return;
+    }
+    for (int j = tid; j < E; j += blockDim.x) {
+        int64_t run = s_col[j];
+        for (int i = 0; i < N; ++i) {
+            dst_first[j * N + i] = run;
+            run += s_cnt[i * E + j];
+        }
+        expert_num[j] = static_cast<CntT>(run - s_col[j]);
+    }
+    for (int i = tid; i < N; i += blockDim.x) {
+        int64_t run = s_row[i];
+        for (int j = 0; j < E; ++j) {
+            src_first[j * N + i] = run;
+            run += s_cnt[i * E + j];
+        }
+    }
+}
+
 // index[d] = source row of destination row d (-1 past the routed rows); out_idx[d] the same as int32.
 __global__ void __launch_bounds__(256) rr_index_kernel(const int32_t* __restrict__ hdr,
                                                        const int64_t* __restrict__ dst_first,
@@ -986,7 +1079,17 @@ extern "C" int w8a8_moe_re_routing(const void* tokens, const void* counts, const
     ws += w8a8::align_up(static_cast<size_t>(N + 1) * sizeof(int64_t), 256);
     int64_t* index = reinterpret_cast<int64_t*>(ws);
 
-    if (count_bytes == 4) {
+    if (cells <= static_cast<size_t>(w8a8::RR_SMALL_CELLS)) {
+        if (count_bytes == 4) {
+            w8a8::rr_table_small_kernel<int32_t><<<1, 1024, 0, st>>>(
+                static_cast<const int32_t*>(counts), static_cast<int>(N), static_cast<int>(E), A, hdr, dst_first,
+                src_first, static_cast<int32_t*>(expert_token_num));
+        } else {
+            w8a8::rr_table_small_kernel<int64_t><<<1, 1024, 0, st>>>(
+                static_cast<const int64_t*>(counts), static_cast<int>(N), static_cast<int>(E), A, hdr, dst_first,
+                src_first, static_cast<int64_t*>(expert_token_num));
+        }
+    } else if (count_bytes == 4) {
         w8a8::rr_table_kernel<int32_t><<<1, 1024, 0, st>>>(static_cast<const int32_t*>(counts), N, E, A, hdr,
                                                           dst_first, src_first, col_start, row_start,
                                                           static_cast<int32_t*>(expert_token_num));
