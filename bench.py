@@ -11,6 +11,8 @@ shaped like the configuration the headline metric is quoted on.  Workloads:
     dq     dynamic_quant, [8192, 7168] bf16 (HBM GB/s)
     qmm    quant_matmul, M=8192 K=7168 N=18432 (int8 TOPS)
     chain  the full expert-parallel MoE FFN chain, T=65536 tokens (tokens/s; the all-to-all workload for N > 1)
+    mrr, mfr, gate, dqsq   the operators either side of the path: moe_re_routing, moe_finalize_routing,
+           moe_gating_top_k_softmax, dequant_swiglu_quant at the shapes they have inside the chain (HBM GB/s)
 
 Rank 0 prints ONE JSON line.  `value` is the device-timed throughput with
 inputs resident in HBM; `e2e` is the same metric through the operator call
@@ -21,10 +23,11 @@ is the CPU oracle timed on this machine's host cores on a bounded sample.
 build with the Ascend toolchain, so the oracle is the reference's CPU
 implementation of the path here).
 
-With N > 1 (torchrun) the grouped workload is expert-parallel: rank r owns
-experts [r*E/N, (r+1)*E/N) and their rows; there is no data-path collective,
-ranks only meet at the timing barriers.  Per-GPU work shrinks as N grows
-(strong scaling of the configuration's fixed total).
+With N > 1 (torchrun) the grouped workload is expert-parallel: every rank owns
+a set of experts and their rows (see place_experts for the two placements);
+there is no data-path collective, ranks only meet at the timing barriers.
+Per-GPU work shrinks as N grows (strong scaling of the configuration's fixed
+total).
 """
 from __future__ import annotations
 
