@@ -13,6 +13,8 @@ shaped like the configuration the headline metric is quoted on.  Workloads:
     chain  the full expert-parallel MoE FFN chain, T=65536 tokens (tokens/s; the all-to-all workload for N > 1)
     mrr, mfr, gate, dqsq   the operators either side of the path: moe_re_routing, moe_finalize_routing,
            moe_gating_top_k_softmax, dequant_swiglu_quant at the shapes they have inside the chain (HBM GB/s)
+    mma_peak   the int8 tensor-pipe ceiling: tcgen05.mma kind::i8 issued back to back on operands resident in
+           shared memory, per instruction shape (int8 TOPS; no loads, no epilogue; one GPU)
 
 Rank 0 prints ONE JSON line.  `value` is the device-timed throughput with
 inputs resident in HBM; `e2e` is the same metric through the operator call
@@ -869,12 +871,74 @@ def run_reference(args, wl):
 
 
 # --------------------------------------------------------------------------
+# the tensor pipe's own ceiling
+# --------------------------------------------------------------------------
+MMA_PEAK_SHAPES = [
+    # (cta_group, M, N, A MN-major, B MN-major, fill, accumulators): the production shapes first
+    (2, 256, 256, 0, 1, 1, 1), (2, 256, 256, 0, 1, 0, 1), (2, 256, 256, 0, 1, 1, 2), (1, 128, 256, 0, 1, 1, 1),
+    (1, 128, 256, 0, 1, 1, 2), (1, 128, 128, 0, 1, 1, 1), (1, 128, 128, 0, 1, 1, 4), (2, 256, 128, 0, 1, 1, 1),
+    (2, 256, 128, 0, 1, 1, 2), (2, 256, 128, 0, 1, 1, 4), (2, 128, 256, 0, 1, 1, 1), (2, 128, 256, 0, 1, 1, 2),
+    (1, 64, 256, 0, 1, 1, 1), (1, 64, 256, 0, 1, 1, 2),
+    # weights as the A operand (MN-major), a few activation rows as the narrow B operand
+    (2, 256, 256, 1, 0, 1, 1), (2, 256, 128, 1, 0, 1, 2), (2, 256, 64, 1, 0, 1, 1), (2, 256, 64, 1, 0, 1, 2),
+    (2, 256, 64, 1, 0, 1, 4), (2, 256, 32, 1, 0, 1, 2), (2, 256, 32, 1, 0, 1, 4), (2, 256, 16, 1, 0, 1, 1),
+    (2, 256, 16, 1, 0, 1, 4), (1, 128, 64, 1, 0, 1, 2), (1, 128, 64, 1, 0, 1, 4), (1, 128, 16, 1, 0, 1, 4),
+]
+
+
+def run_mma_peak(args):
+    """Issue-bound rate of tcgen05.mma kind::i8 per instruction shape (w8a8_mma_issue_probe), CUDA events around one
+    launch of about 20 ms each, SM clock sampled meanwhile.  Prints one JSON line."""
+    import torch
+
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    torch.cuda.set_device(0)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    sampler = ClockSampler(0)
+    sampler.start()
+    rows = []
+    for cg, m, n, a_mn, b_mn, fill, acc in MMA_PEAK_SHAPES:
+        batches = min(40000 * 256 // n, 1 << 21)
+        for _ in range(max(1, args.warmup // 3)):
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, batches // 8, err.data_ptr(), st)
+            assert rc == 0, L.status_string(rc)
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, batches, err.data_ptr(), st)
+            e1.record()
+            assert rc == 0, L.status_string(rc)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        ops = lib.w8a8_mma_issue_probe_ops(cg, m, n, batches)
+        rows.append({"cta_group": cg, "m": m, "n": n, "a_major": "MN" if a_mn else "K", "b_major": "MN" if b_mn else "K",
+                     "operands": "random" if fill else "zero", "accumulators": acc, "ms": round(best, 3),
+                     "tops": round(ops / (best * 1e-3) / 1e12, 1),
+                     "ns_per_mma": round(best * 1e6 / (batches * 4), 2)})
+    clocks = sampler.stop()
+    assert int(err[0]) == 0, "a probe wait ran out"
+    peaks = measured_peaks()
+    top = max(r["tops"] for r in rows if r["operands"] == "random")
+    print(json.dumps({"metric": "mma_issue_int8_tops", "value": top, "unit": "TOPS", "n_gpus": 1,
+                      "higher_is_better": True, "dtype": "int8", "data": "shared-memory resident operands",
+                      "config": {"workload": "tcgen05.mma kind::i8 issue loop, no loads, no epilogue"},
+                      "reference_peak": {"value": peaks["bf16_tflops"] * INT8_PER_BF16, "unit": "TOPS",
+                                         "source": f"2 x {peaks['source']} cuBLAS bf16 burst"},
+                      "clocks": clocks, "shapes": rows}), flush=True)
+
+
+# --------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gmsq")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["mma_peak"], default="gmsq")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--small", action="store_true", help="reduced grouped workload (for profiling captures)")
     ap.add_argument("--qmm-m", type=int, default=8192, help="rows of the dense quant_matmul workload")
@@ -893,6 +957,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.workload == "mma_peak":
+        if int(os.environ.get("RANK", "0")) == 0 and args.impl == "b200":
+            run_mma_peak(args)
+        return
 
     wl = (WORKLOADS[args.workload](small=True) if (args.workload in ("gmsq", "chain") and args.small)
           else WORKLOADS[args.workload]())

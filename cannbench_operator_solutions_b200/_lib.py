@@ -66,6 +66,9 @@ SIGNATURES = {
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i64]),
+    "w8a8_selftest_bounded_wait": (_i32, [_i64, _vp, _vp]),
 }
 
 _lib = None

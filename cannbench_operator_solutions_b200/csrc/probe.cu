@@ -1,0 +1,251 @@
+// Measurement and self-test entry points of the tensor-core layer.
+//
+// w8a8_mma_issue_probe: every SM (or SM pair) issues a long run of tcgen05.mma
+// kind::i8 instructions on operands that already sit in shared memory: no TMA,
+// no epilogue.  Timed by the caller with CUDA events it gives the rate the
+// tensor pipe sustains for one instruction shape (M, N, operand majors, one or
+// two CTAs per instruction) - the ceiling the full matmul kernels are compared
+// with, and the figure that says what a narrow or a half-height instruction
+// costs.
+//
+// w8a8_selftest_bounded_wait: one CTA waits on a barrier nobody arrives at,
+// with a caller-given cycle limit, and reports that the wait ran out the way
+// the matmul kernels do (error word 2).  Ends by itself after `limit` cycles.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace w8a8 {
+
+constexpr int PROBE_THREADS = 128;
+constexpr int PROBE_STAGES = 4;
+constexpr int PROBE_A_BYTES = 16384;                       // 128 rows x 128 bytes of K
+constexpr int PROBE_B_BYTES = 32768;                       // up to 256 columns x 128 bytes of K
+constexpr int PROBE_STAGE_BYTES = PROBE_A_BYTES + PROBE_B_BYTES;
+constexpr int PROBE_DEPTH = 4;                             // batches in flight
+constexpr int PROBE_KSTEPS = 4;                            // MMAs per batch: 128 bytes of K in steps of 32
+
+template <int CG>
+__global__ void __launch_bounds__(PROBE_THREADS, 1)
+    mma_issue_probe_kernel(uint32_t idesc, int a_mn, int b_mn, int fill, int accumulators, long long batches,
+                           int32_t* error)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PROBE_STAGES * PROBE_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PROBE_DEPTH);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5;
+    const uint32_t cta_rank = (CG == 2) ? tc::cluster_ctarank() : 0u;
+
+    // operands: zeros, or bytes from a multiplicative hash of the address (every bit toggles)
+    {
+        uint32_t* words = reinterpret_cast<uint32_t*>(smem);
+        const int n_words = PROBE_STAGES * PROBE_STAGE_BYTES / 4;
+        for (int i = threadIdx.x; i < n_words; i += PROBE_THREADS) {
+            uint32_t v = 0;
+            if (fill != 0) {
+                v = (static_cast<uint32_t>(i) + 0x9e3779b9u * (blockIdx.x + 1)) * 2654435761u;
+                v ^= v >> 15;
+                v *= 2246822519u;
+                v ^= v >> 13;
+            }
+            words[i] = v;
+        }
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < PROBE_DEPTH; ++i) {
+            tc::mbar_init(tc::smem_u32(bars + i), 1);
+        }
+        *abort_flag = 0;
+        tc::fence_mbar_init();
+    }
+    if (warp == 0) {
+        tc::tmem_alloc(tc::smem_u32(tmem_slot), 512);
+        tc::tmem_relinquish();
+    }
+    // generic-proxy writes of the operands must be visible to the tensor core's async-proxy reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if constexpr (CG == 2) {
+        tc::cluster_arrive();
+        tc::cluster_wait();
+    }
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (threadIdx.x == 0 && cta_rank == 0) {
+        const uint32_t smem_base = tc::smem_u32(smem);
+        const uint64_t a_desc0 = a_mn ? tc::smem_desc_sw128(smem_base, 128 * 128, 1024)
+                                      : tc::smem_desc_sw128(smem_base, 16, 1024);
+        const uint64_t b_desc0 = b_mn ? tc::smem_desc_sw128(smem_base + PROBE_A_BYTES, 128 * 128, 1024)
+                                      : tc::smem_desc_sw128(smem_base + PROBE_A_BYTES, 16, 1024);
+        const uint32_t a_hi = static_cast<uint32_t>(a_desc0 >> 32);
+        const uint32_t b_hi = static_cast<uint32_t>(b_desc0 >> 32);
+        const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0);
+        const uint32_t b_lo0 = static_cast<uint32_t>(b_desc0);
+        const uint32_t a_kstep = a_mn ? ((32 * 128) >> 4) : (32 >> 4);
+        const uint32_t b_kstep = b_mn ? ((32 * 128) >> 4) : (32 >> 4);
+        const uint32_t bar0 = tc::smem_u32(bars);
+        bool ok = true;
+        for (long long b = 0; ok && b < batches; ++b) {
+            const int slot = static_cast<int>(b % PROBE_DEPTH);
+            if (b >= PROBE_DEPTH) {
+                const uint32_t parity = static_cast<uint32_t>((b / PROBE_DEPTH - 1) & 1);
+                if (!tc::mbar_wait(bar0 + 8u * slot, parity, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+            }
+            const int stage = static_cast<int>(b % PROBE_STAGES);
+            // one accumulator: every MMA adds to the result of the one before it (alternating between two
+            // accumulator stages per batch, as a matmul's successive tiles do); several: successive MMAs add to
+            // different accumulators, so none waits for its predecessor's result
+            const uint32_t acc_stride = 512u / static_cast<uint32_t>(accumulators);
+            const uint32_t d_single = tmem_base + static_cast<uint32_t>((b & 1) * 256);
+            const uint32_t a_lo = a_lo0 + stage * (PROBE_STAGE_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + stage * (PROBE_STAGE_BYTES >> 4);
+#pragma unroll
+            for (int k = 0; k < PROBE_KSTEPS; ++k) {
+                const uint32_t d_tmem =
+                    (accumulators == 1) ? d_single : tmem_base + static_cast<uint32_t>(k % accumulators) * acc_stride;
+                tc::mma_lohi<CG, true>(d_tmem, a_lo + k * a_kstep, a_hi, b_lo + k * b_kstep, b_hi, idesc, 1u);
+            }
+            if constexpr (CG == 2) {
+                tc::tc_commit_pair(bar0 + 8u * slot);
+            } else {
+                tc::tc_commit(bar0 + 8u * slot);
+            }
+        }
+        // drain: the last min(batches, DEPTH) commits
+        const long long first = batches > PROBE_DEPTH ? batches - PROBE_DEPTH : 0;
+        for (long long b = first; ok && b < batches; ++b) {
+            const int slot = static_cast<int>(b % PROBE_DEPTH);
+            const uint32_t parity = static_cast<uint32_t>((b / PROBE_DEPTH) & 1);
+            if (!tc::mbar_wait(bar0 + 8u * slot, parity, abort_flag)) {
+                ok = false;
+            }
+        }
+        if (!ok && error != nullptr) {
+            atomicExch(error, 2);
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if constexpr (CG == 2) {
+        tc::cluster_arrive();
+        tc::cluster_wait();
+    }
+    if (warp == 0) {
+        tc::tc_fence_after_sync();
+        tc::tmem_dealloc(tmem_base, 512);
+    }
+}
+
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, int32_t* error)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(tc::smem_u32(&bar), 1);
+        abort_flag = 0;
+        tc::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // nothing ever arrives on this barrier: the wait has to give up by itself
+        const bool done = tc::mbar_wait(tc::smem_u32(&bar), 0u, &abort_flag, limit_cycles);
+        if (!done) {
+            atomicExch(error, 2);
+        }
+    }
+    __syncthreads();
+    // every other thread sees what the matmul kernels' roles see: the CTA-wide abort flag
+    if (threadIdx.x == 1 && abort_flag != 0) {
+        atomicAdd(error + 1, 1);
+    }
+}
+
+}  // namespace w8a8
+
+using namespace w8a8;
+
+extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
+                                    int accumulators, int64_t batches, int32_t* error_word, void* stream)
+{
+    if (batches <= 0 || batches > (int64_t(1) << 24)) {
+        return W8A8_ERR_INVALID;
+    }
+    if ((accumulators != 1 && accumulators != 2 && accumulators != 4) || umma_n * accumulators > 512) {
+        return W8A8_ERR_INVALID;
+    }
+    if (cta_group == 1) {
+        if (umma_m != 64 && umma_m != 128) {
+            return W8A8_ERR_INVALID;
+        }
+    } else if (cta_group == 2) {
+        if (umma_m != 128 && umma_m != 256) {
+            return W8A8_ERR_INVALID;
+        }
+    } else {
+        return W8A8_ERR_INVALID;
+    }
+    const int n_step = (umma_m == 64) ? 8 : 16;
+    if (umma_n < n_step || umma_n > 256 || (umma_n % n_step) != 0) {
+        return W8A8_ERR_INVALID;
+    }
+    const uint32_t idesc = tc::instr_desc(2u, 1u, b_mn_major ? 1u : 0u, static_cast<uint32_t>(umma_m),
+                                          static_cast<uint32_t>(umma_n), a_mn_major ? 1u : 0u);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t smem = static_cast<size_t>(PROBE_STAGES) * PROBE_STAGE_BYTES + 1024 + 256;
+    const int sms = sm_count();
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(PROBE_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    cudaError_t e;
+    if (cta_group == 2) {
+        e = cudaFuncSetAttribute(mma_issue_probe_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
+        cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2), 1, 1);
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<2>, idesc, a_mn_major, b_mn_major, fill,
+                               accumulators, static_cast<long long>(batches), error_word);
+    } else {
+        e = cudaFuncSetAttribute(mma_issue_probe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+        if (e != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
+        cfg.gridDim = dim3(static_cast<unsigned>(sms), 1, 1);
+        e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<1>, idesc, a_mn_major, b_mn_major, fill,
+                               accumulators, static_cast<long long>(batches), error_word);
+    }
+    return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+extern "C" int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int64_t batches)
+{
+    // integer operations (multiply and add counted separately) one probe launch issues on this device
+    const int64_t groups = (cta_group == 2) ? sm_count() / 2 : sm_count();
+    return groups * batches * PROBE_KSTEPS * 2 * umma_m * umma_n * 32;
+}
+
+extern "C" int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream)
+{
+    if (limit_cycles <= 0 || limit_cycles > 4000000000ll || error_words == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<long long>(limit_cycles),
+                                                                                  error_words);
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}

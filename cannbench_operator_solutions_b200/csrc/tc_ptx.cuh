@@ -68,7 +68,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 // The fast path is a bare try_wait loop: no timer is read until a wait has
 // already spun for a while (the global timer is slow to read), and the limit
 // is then checked against the SM clock.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES)
 {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
@@ -86,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag != 0) {
                 return false;
             }
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }
@@ -381,12 +382,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 //   bits  4-5   accumulator format (1 = f32, 2 = s32)
 //   bits  7-9   A format, bits 10-12 B format (kind::i8: 1 = signed 8 bit;
 //               kind::f16: 0 = f16, 1 = bf16)
-//   bit  15     A major (0 = K), bit 16 B major (1 = MN)
+//   bit  15     A major (0 = K, 1 = MN), bit 16 B major (1 = MN)
 //   bits 17-22  N >> 3, bits 24-28 M >> 4
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t c_fmt, uint32_t ab_fmt, uint32_t b_mn_major, uint32_t m,
-                                                  uint32_t n)
+                                                  uint32_t n, uint32_t a_mn_major = 0)
 {
-    return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+    return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace tc

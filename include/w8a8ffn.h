@@ -13,7 +13,9 @@
  *   - The caller owns every buffer, including workspaces, whose size comes
  *     from the matching *_workspace_size() query.  The library allocates
  *     nothing and keeps no mutable global state besides cached function
- *     attributes.
+ *     attributes, the kernel-shape override of w8a8_set_gemm_shape() and the
+ *     one deliberate exception: the device scratch built into the library
+ *     image that w8a8_grouped_matmul_swiglu_quant_static() works in.
  *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is
  *     the legacy default stream) and the call returns without synchronising.
  *   - Return value: W8A8_OK or a negative W8A8_ERR_* code.  Nothing throws.
@@ -365,6 +367,37 @@ int w8a8_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* 
 int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const float* activation_scale,
                               const float* quant_scale, int8_t* y, float* scale, int64_t M, int64_t H,
                               int x_dtype, int activate_left, int flags, void* stream);
+
+/*
+ * Measurement and self-test entry points of the tensor-core layer.  (No
+ * counterparts in the reference, whose matmuls are calls into the Ascend Matmul
+ * library.)
+ *
+ * w8a8_mma_issue_probe: every SM (cta_group 1) or SM pair (cta_group 2) issues
+ * `batches` x 4 tcgen05.mma kind::i8 instructions of shape umma_m x umma_n x 32
+ * on operands resident in shared memory (fill 0 = zeros, 1 = pseudo-random
+ * bytes), with no loads and no epilogue: timed with CUDA events it gives the
+ * rate the tensor pipe sustains for that shape, the ceiling the matmul kernels
+ * are compared with.  a_mn_major / b_mn_major select the operand majors the
+ * instruction descriptor names.  cta_group 1: umma_m 64 or 128; cta_group 2:
+ * umma_m 128 or 256 (both CTAs together); umma_n a multiple of 16 (8 for
+ * umma_m 64) up to 256.  accumulators = 1: every instruction adds to the
+ * result of the one before it, as in a matmul's K loop; 2 or 4: successive
+ * instructions add to different accumulators (umma_n x accumulators <= 512).  error_word (device, may be NULL) receives 2 if a wait
+ * ran out.  w8a8_mma_issue_probe_ops returns the integer operations one such
+ * launch performs on the current device.
+ *
+ * w8a8_selftest_bounded_wait: one thread waits, with the matmul kernels' wait
+ * helper and a limit of limit_cycles SM clocks, on a barrier nothing arrives
+ * at; the kernel ends by itself and reports the way the matmul kernels do:
+ * error_words[0] = 2 (a pipeline wait ran out), error_words[1] = 1 (the other
+ * threads of the CTA saw the abort flag).  error_words: two zeroed int32 in
+ * device memory.
+ */
+int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
+                         int accumulators, int64_t batches, int32_t* error_word, void* stream);
+int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int64_t batches);
+int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream);
 
 #ifdef __cplusplus
 }
