@@ -874,15 +874,21 @@ def run_reference(args, wl):
 # the tensor pipe's own ceiling
 # --------------------------------------------------------------------------
 MMA_PEAK_SHAPES = [
-    # (cta_group, M, N, A MN-major, B MN-major, fill, accumulators): the production shapes first
-    (2, 256, 256, 0, 1, 1, 1), (2, 256, 256, 0, 1, 0, 1), (2, 256, 256, 0, 1, 1, 2), (1, 128, 256, 0, 1, 1, 1),
-    (1, 128, 256, 0, 1, 1, 2), (1, 128, 128, 0, 1, 1, 1), (1, 128, 128, 0, 1, 1, 4), (2, 256, 128, 0, 1, 1, 1),
-    (2, 256, 128, 0, 1, 1, 2), (2, 256, 128, 0, 1, 1, 4), (2, 128, 256, 0, 1, 1, 1), (2, 128, 256, 0, 1, 1, 2),
-    (1, 64, 256, 0, 1, 1, 1), (1, 64, 256, 0, 1, 1, 2),
+    # (cta_group, M, N, A MN-major, B MN-major, fill, accumulators, instructions per commit, commits in flight)
+    # the production shape: 4 K steps per shared-memory stage, one commit per stage
+    (2, 256, 256, 0, 1, 1, 1, 4, 4), (2, 256, 256, 0, 1, 0, 1, 4, 4), (2, 256, 256, 0, 1, 1, 1, 4, 6),
+    (2, 256, 256, 0, 1, 1, 1, 8, 4), (2, 256, 256, 0, 1, 1, 1, 16, 4), (2, 256, 256, 0, 1, 1, 1, 64, 2),
+    (2, 256, 256, 0, 1, 1, 2, 16, 4),
+    (1, 128, 256, 0, 1, 1, 1, 4, 4), (1, 128, 256, 0, 1, 1, 1, 16, 4), (1, 128, 256, 0, 1, 1, 1, 64, 2),
+    (1, 128, 128, 0, 1, 1, 1, 4, 4), (1, 128, 128, 0, 1, 1, 1, 16, 4), (1, 128, 128, 0, 1, 1, 1, 64, 2),
+    (1, 128, 128, 0, 1, 1, 4, 64, 2),
+    (2, 256, 128, 0, 1, 1, 1, 16, 4), (2, 256, 128, 0, 1, 1, 1, 64, 2),
+    (2, 128, 256, 0, 1, 1, 1, 16, 4), (2, 128, 256, 0, 1, 1, 1, 64, 2), (1, 64, 256, 0, 1, 1, 1, 64, 2),
     # weights as the A operand (MN-major), a few activation rows as the narrow B operand
-    (2, 256, 256, 1, 0, 1, 1), (2, 256, 128, 1, 0, 1, 2), (2, 256, 64, 1, 0, 1, 1), (2, 256, 64, 1, 0, 1, 2),
-    (2, 256, 64, 1, 0, 1, 4), (2, 256, 32, 1, 0, 1, 2), (2, 256, 32, 1, 0, 1, 4), (2, 256, 16, 1, 0, 1, 1),
-    (2, 256, 16, 1, 0, 1, 4), (1, 128, 64, 1, 0, 1, 2), (1, 128, 64, 1, 0, 1, 4), (1, 128, 16, 1, 0, 1, 4),
+    (2, 256, 256, 1, 0, 1, 1, 16, 4), (2, 256, 128, 1, 0, 1, 1, 64, 2), (2, 256, 64, 1, 0, 1, 1, 4, 4),
+    (2, 256, 64, 1, 0, 1, 1, 16, 4), (2, 256, 64, 1, 0, 1, 1, 64, 2), (2, 256, 64, 1, 0, 1, 2, 64, 2),
+    (2, 256, 32, 1, 0, 1, 1, 64, 2), (2, 256, 16, 1, 0, 1, 1, 64, 2), (2, 256, 16, 1, 0, 1, 1, 256, 2),
+    (1, 128, 64, 1, 0, 1, 1, 64, 2), (1, 128, 16, 1, 0, 1, 1, 64, 2),
 ]
 
 
@@ -900,26 +906,26 @@ def run_mma_peak(args):
     sampler = ClockSampler(0)
     sampler.start()
     rows = []
-    for cg, m, n, a_mn, b_mn, fill, acc in MMA_PEAK_SHAPES:
-        batches = min(40000 * 256 // n, 1 << 21)
+    for cg, m, n, a_mn, b_mn, fill, acc, per, depth in MMA_PEAK_SHAPES:
+        batches = max(64, 160000 // per)
         for _ in range(max(1, args.warmup // 3)):
-            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, batches // 8, err.data_ptr(), st)
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, batches // 8, err.data_ptr(), st)
             assert rc == 0, L.status_string(rc)
         best = None
         for _ in range(3):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, batches, err.data_ptr(), st)
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, batches, err.data_ptr(), st)
             e1.record()
             assert rc == 0, L.status_string(rc)
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
             best = ms if best is None or ms < best else best
-        ops = lib.w8a8_mma_issue_probe_ops(cg, m, n, batches)
+        ops = lib.w8a8_mma_issue_probe_ops(cg, m, n, per, batches)
         rows.append({"cta_group": cg, "m": m, "n": n, "a_major": "MN" if a_mn else "K", "b_major": "MN" if b_mn else "K",
-                     "operands": "random" if fill else "zero", "accumulators": acc, "ms": round(best, 3),
+                     "operands": "random" if fill else "zero", "accumulators": acc, "per_commit": per, "in_flight": depth, "ms": round(best, 3),
                      "tops": round(ops / (best * 1e-3) / 1e12, 1),
-                     "ns_per_mma": round(best * 1e6 / (batches * 4), 2)})
+                     "ns_per_mma": round(best * 1e6 / (batches * per), 2)})
     clocks = sampler.stop()
     assert int(err[0]) == 0, "a probe wait ran out"
     peaks = measured_peaks()

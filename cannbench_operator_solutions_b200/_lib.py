@@ -49,6 +49,9 @@ SIGNATURES = {
     "w8a8_grouped_matmul": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32,
                                    _i32, _vp, _sz, _vp]),
     "w8a8_workspace_error": (_i32, [_vp, _vp]),
+    "w8a8_set_gemm_shape": (_i32, [_i32]),
+    "w8a8_pipeline_error": (_i32, [_vp]),
+    "w8a8_static_scratch_error": (_i32, [_vp]),
     "w8a8_route_plan_workspace_size": (_sz, [_i64, _i64, _i64]),
     "w8a8_route_plan": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "w8a8_scatter_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
@@ -66,8 +69,8 @@ SIGNATURES = {
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
-    "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
-    "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i64]),
+    "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i32, _i64]),
     "w8a8_selftest_bounded_wait": (_i32, [_i64, _vp, _vp]),
 }
 

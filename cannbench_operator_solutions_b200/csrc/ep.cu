@@ -824,7 +824,10 @@ __global__ void __launch_bounds__(1024) ep_tables_kernel(const int64_t* __restri
             total += s_col[rank * e_local + j];
         }
         seg_first[nseg] = bad ? 0 : total;
-        status[0] = bad ? 1 : 0;
+        // sticky: a later good step must not hide an overflowed one; the reader clears it
+        if (bad) {
+            status[0] = 1;
+        }
     }
 }
 

@@ -4,7 +4,7 @@
 // grouped_matmul_swiglu_quant and grouped_matmul.
 #include <cuda.h>
 
-#include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "gemm_kernel.cuh"
@@ -148,18 +148,17 @@ static cudaError_t dispatch_gemm(int cta_group, int block_n, bool b_mn, const CU
                 : launch_gemm<1, 256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
 }
 
-// Kernel shape: CTA pairs for dense problems with enough rows to fill 256-row tiles.  The environment variable
-// W8A8_GEMM_CTA_GROUP (1, 2, or 3 = pairs plus singles for grouped problems) overrides the choice; the tests use it
-// to run every case on every shape.
+// Kernel shape: CTA pairs for dense problems with enough rows to fill 256-row tiles.  w8a8_set_gemm_shape()
+// (1, 2, or 3 = pairs plus singles for grouped problems; 0 = the library's choice) overrides it process-wide; the
+// tests use it to run every case on every shape.
 constexpr int GEMM_SHAPE_HYBRID = 3;
+static std::atomic<int> g_shape_override{0};
 
 static int choose_cta_group(int64_t rows, bool grouped)
 {
-    if (const char* env = getenv("W8A8_GEMM_CTA_GROUP")) {
-        const int v = atoi(env);
-        if (v == 1 || v == 2 || (v == GEMM_SHAPE_HYBRID && grouped)) {
-            return v;
-        }
+    const int v = g_shape_override.load(std::memory_order_relaxed);
+    if (v == 1 || v == 2 || (v == GEMM_SHAPE_HYBRID && grouped)) {
+        return v;
     }
     // Grouped problems with enough rows run in two launches: CTA pairs on every group's 256-row blocks (the last
     // one partial when it holds more than 128 rows) and single CTAs on leftovers of at most 128 rows.  Pairs on everything would pad the end of every group to 256 rows,
@@ -469,7 +468,7 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
     int shape = choose_cta_group(M, true);
     // Rows stored one by one at caller-given addresses (peer memory) are bound by the link, not by the tensor
     // pipe; single tiles spread those stores more evenly in time (3.34 ms against 3.83 ms on two GPUs).
-    if (p.out_row_ptrs != nullptr && shape == GEMM_SHAPE_HYBRID && getenv("W8A8_GEMM_CTA_GROUP") == nullptr) {
+    if (p.out_row_ptrs != nullptr && shape == GEMM_SHAPE_HYBRID && g_shape_override.load(std::memory_order_relaxed) == 0) {
         shape = 1;
     }
     p.grouped = 1;
@@ -502,6 +501,33 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
     p.header = g.tail_header;
     e = dispatch_gemm<KIND, EPI>(1, 256, b_mn, ta, tb, p, g.tail_max_tiles * p.n_tiles, st);
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// Error word of launches that have no workspace to carry one (the dense matmuls): one int32 in the library's
+// device image per GPU.  A kernel whose bounded wait ran out stores 2 there; w8a8_pipeline_error() reads and
+// clears it.  The address is looked up once per device, with that device current.
+// ---------------------------------------------------------------------------
+static __device__ int32_t g_pipeline_error_word;
+
+static int32_t* pipeline_error_word()
+{
+    constexpr int MAX_DEVICES = 64;
+    static std::atomic<int32_t*> cache[MAX_DEVICES];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        return nullptr;
+    }
+    int32_t* p = cache[dev].load(std::memory_order_relaxed);
+    if (p == nullptr) {
+        void* sym = nullptr;
+        if (cudaGetSymbolAddress(&sym, g_pipeline_error_word) != cudaSuccess) {
+            return nullptr;
+        }
+        p = static_cast<int32_t*>(sym);
+        cache[dev].store(p, std::memory_order_relaxed);
+    }
+    return p;
 }
 
 }  // namespace w8a8
@@ -572,6 +598,7 @@ static int quant_matmul_impl(const int8_t* x1, const int8_t* x2, const void* sca
     p.flags = flags;
     p.out_dtype = out_dtype;
     p.bias_batch_stride = bias_batch_stride;
+    p.error = pipeline_error_word();  // null (no report) only if the symbol lookup failed
     const int cg = choose_cta_group(M, false);
     const int tile_m = 128 * cg;
     p.m_tiles_per_batch = static_cast<int32_t>((M + tile_m - 1) / tile_m);
@@ -761,7 +788,8 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
         return W8A8_ERR_INVALID;
     }
     const int elem = (kind == KIND_I8) ? 1 : 2;
-    if ((K * elem) % 16 != 0 || (N * elem) % 16 != 0 || (N % 8) != 0) {
+    // the epilogue fetches per-channel operands and stores outputs in 16-column pieces
+    if ((K * elem) % 16 != 0 || (N % 16) != 0) {
         return W8A8_ERR_UNSUPPORTED;
     }
     if (!is_aligned(x, 16) || !is_aligned(w, 16) || (y != nullptr && !is_aligned(y, 16))) {
@@ -835,6 +863,29 @@ extern "C" int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const v
                                stream);
 }
 
+extern "C" int w8a8_pipeline_error(void* stream)
+{
+    int32_t* word = pipeline_error_word();
+    if (word == nullptr) {
+        return W8A8_ERR_CUDA;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t v = 0;
+    if (cudaMemcpyAsync(&v, word, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaMemsetAsync(word, 0, sizeof(v), st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    return v;
+}
+
+extern "C" int w8a8_set_gemm_shape(int shape)
+{
+    if (shape < 0 || shape > GEMM_SHAPE_HYBRID) {
+        return W8A8_ERR_INVALID;
+    }
+    return g_shape_override.exchange(shape, std::memory_order_relaxed);
+}
+
 extern "C" int w8a8_workspace_error(const void* workspace, void* stream)
 {
     if (workspace == nullptr) {
@@ -860,6 +911,41 @@ extern "C" int w8a8_workspace_error(const void* workspace, void* stream)
 // cudaGetSymbolAddress; it is never a device address by itself.
 static __device__ __align__(256) unsigned char g_gmsq_static_scratch[W8A8_STATIC_SCRATCH_BYTES];
 
+// One address lookup per device, made with that device current.  Racing first calls store the same value.
+static int static_scratch_address(void** out)
+{
+    constexpr int MAX_DEVICES = 64;
+    static std::atomic<void*> scratch_of_device[MAX_DEVICES];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
+        return W8A8_ERR_CUDA;
+    }
+    if (dev >= MAX_DEVICES) {
+        return W8A8_ERR_LIMIT;  // the address cache is fixed-size; nothing in CUDA failed
+    }
+    void* scratch = scratch_of_device[dev].load(std::memory_order_relaxed);
+    if (scratch == nullptr) {
+        if (cudaGetSymbolAddress(&scratch, g_gmsq_static_scratch) != cudaSuccess || scratch == nullptr) {
+            return W8A8_ERR_CUDA;
+        }
+        scratch_of_device[dev].store(scratch, std::memory_order_relaxed);
+    }
+    *out = scratch;
+    return W8A8_OK;
+}
+
+// The error word of the last *_static call on the current device (it lives in the built-in scratch, which the
+// caller never sees): 0 = none, 1 = invalid device group list (y was left untouched), 2 = a pipeline wait ran out.
+extern "C" int w8a8_static_scratch_error(void* stream)
+{
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != W8A8_OK) {
+        return rc;
+    }
+    return w8a8_workspace_error(scratch, stream);
+}
+
 extern "C" int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const int8_t* w, const float* w_scale,
                                                        const float* x_scale, int8_t* y, float* y_scale, int64_t M,
                                                        int64_t K, int64_t N, int64_t E, const int64_t* group_list,
@@ -873,18 +959,10 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const in
     if (need == 0 || need > static_cast<size_t>(W8A8_STATIC_SCRATCH_BYTES)) {
         return W8A8_ERR_LIMIT;
     }
-    // One address lookup per device, made with that device current.  Racing first calls store the same value.
-    static void* scratch_of_device[64] = {nullptr};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-        return W8A8_ERR_CUDA;
-    }
-    void* scratch = scratch_of_device[dev];
-    if (scratch == nullptr) {
-        if (cudaGetSymbolAddress(&scratch, g_gmsq_static_scratch) != cudaSuccess || scratch == nullptr) {
-            return W8A8_ERR_CUDA;
-        }
-        scratch_of_device[dev] = scratch;
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != W8A8_OK) {
+        return rc;
     }
     // From here on this is the ordinary operator with the built-in bytes as its workspace.  That path rewrites
     // the header and tile table and zeroes the row maxima on the stream before it uses them, so whatever the

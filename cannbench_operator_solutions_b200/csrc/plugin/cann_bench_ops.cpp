@@ -1,26 +1,34 @@
-// torch operator plugin: registers the reference catalog's operator schemas in
-// namespace cann_bench and implements them for the CUDA dispatch key on top of
-// the C-ABI in include/w8a8ffn.h.
+// torch operator plugin: registers the operator schemas of the catalog's W8A8
+// FFN path in namespace cann_bench and implements them for the CUDA dispatch
+// key on top of the C-ABI in include/w8a8ffn.h.
 //
-// Schemas, output allocation ("meta") and argument checks mirror the reference
-// plugins one to one:
-//   dynamic_quant               operators/dynamicquant/csrc/ops/dynamic_quant/op_plugin/dynamic_quant_plugin.cpp:28-92
-//   add_rms_norm_dynamic_quant  operators/addrmsnormdynamicquant/csrc/ops/add_rms_norm_dynamic_quant/op_plugin/add_rms_norm_dynamic_quant_plugin.cpp:30-119
-//   quant_matmul                operators/quantmatmul/csrc/ops/quant_matmul/op_plugin/quant_matmul_plugin.cpp:46-272
-//   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:38-150
-//   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:40-190
-//   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:32-170
-//   dequant_swiglu_quant        operators/dequantswigluquant/csrc/ops/dequant_swiglu_quant/op_plugin/dqsq_plugin.cpp:31-160
-//   moe_gating_top_k_softmax    operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_plugin/moe_gating_plugin.cpp:28-120
-//   moe_finalize_routing        operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:31-237
-// The NPU plugins enqueue their launchers with OpCommand::RunOpApi on the
-// current NPU stream; here the C-ABI call is enqueued on the current CUDA
-// stream.  The plugin only unpacks tensors: all arithmetic is in the library.
+// The schema strings are the reference's (they are the interface callers bind
+// to):
+//   dynamic_quant               operators/dynamicquant/csrc/ops/dynamic_quant/op_plugin/dynamic_quant_plugin.cpp:30
+//   add_rms_norm_dynamic_quant  operators/addrmsnormdynamicquant/csrc/ops/add_rms_norm_dynamic_quant/op_plugin/add_rms_norm_dynamic_quant_plugin.cpp:32
+//   quant_matmul                operators/quantmatmul/csrc/ops/quant_matmul/op_plugin/quant_matmul_plugin.cpp:48-49
+//   grouped_matmul_swiglu_quant operators/groupedmatmulswigluquant/csrc/ops/grouped_matmul_swiglu_quant/op_plugin/gmsq_plugin.cpp:40-41
+//   grouped_matmul              operators/groupedmatmul/csrc/ops/grouped_matmul/op_plugin/grouped_matmul_plugin.cpp:42-43
+//   moe_re_routing              operators/moererouting/csrc/ops/moe_re_routing/op_plugin/moe_re_routing_plugin.cpp:35-38
+//   dequant_swiglu_quant        operators/dequantswigluquant/csrc/ops/dequant_swiglu_quant/op_plugin/dqsq_plugin.cpp:34-35
+//   moe_gating_top_k_softmax    operators/moegatingtopksoftmax/csrc/ops/moe_gating_top_k_softmax/op_plugin/moe_gating_plugin.cpp:30
+//   moe_finalize_routing        operators/moefinalizerouting/csrc/ops/moe_finalize_routing/op_plugin/moe_finalize_routing_plugin.cpp:33-35
+//
+// Everything below the schemas is organised differently from those plugins.
+// Each operator is one struct with two members: `shape()` derives the output
+// tensors from the argument shapes alone (it is the Meta implementation), and
+// `run()` is the CUDA implementation: it declares every tensor argument to a
+// `Call` object - accepted element types, rank range, element count - which
+// checks them in one place, makes dense copies where needed and keeps them
+// alive, then makes exactly one C-ABI call on the current CUDA stream.  The
+// library re-validates sizes and alignment; the plugin only translates torch
+// types.  All arithmetic is in the library.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 #include <torch/torch.h>
 
+#include <algorithm>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -28,650 +36,622 @@
 #include "../../../include/w8a8ffn.h"
 
 namespace cann_bench {
+namespace {
 
-static void check_status(int rc, const char* op)
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+// element types as a bit set, so that an argument's accepted types are one constant
+enum TypeBit : unsigned { F16 = 1u, BF16 = 2u, F32 = 4u, I8 = 8u, I32 = 16u, I64 = 32u, BOOL = 64u };
+constexpr unsigned HALVES = F16 | BF16;
+constexpr unsigned FLOATS = F16 | BF16 | F32;
+
+struct TypeInfo {
+    c10::ScalarType torch_type;
+    unsigned bit;
+    int abi_code;  // W8A8_DT_* or -1
+};
+constexpr TypeInfo TYPE_TABLE[] = {
+    {torch::kFloat16, F16, W8A8_DT_F16}, {torch::kBFloat16, BF16, W8A8_DT_BF16}, {torch::kFloat32, F32, W8A8_DT_F32},
+    {torch::kChar, I8, W8A8_DT_I8},      {torch::kInt, I32, W8A8_DT_I32},        {torch::kLong, I64, -1},
+    {torch::kBool, BOOL, -1},
+};
+
+const TypeInfo* type_info(c10::ScalarType t)
 {
-    TORCH_CHECK(rc == W8A8_OK, op, ": ", w8a8_status_string(rc), " (status ", rc, ")");
-}
-
-static int dtype_code(const torch::Tensor& t)
-{
-    switch (t.scalar_type()) {
-    case torch::kFloat16:
-        return W8A8_DT_F16;
-    case torch::kBFloat16:
-        return W8A8_DT_BF16;
-    case torch::kFloat32:
-        return W8A8_DT_F32;
-    case torch::kChar:
-        return W8A8_DT_I8;
-    default:
-        TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
-    }
-    return -1;
-}
-
-static void* stream_of(const torch::Tensor& t)
-{
-    return static_cast<void*>(at::cuda::getCurrentCUDAStream(t.device().index()).stream());
-}
-
-// ----------------------------------------------------------------- dynamic_quant
-static std::tuple<torch::Tensor, torch::Tensor> dynamic_quant_meta(const torch::Tensor& x)
-{
-    TORCH_CHECK(x.dim() >= 2, "dynamic_quant requires a tensor with rank >= 2.");
-    TORCH_CHECK(x.scalar_type() == torch::kFloat16 || x.scalar_type() == torch::kBFloat16,
-                "dynamic_quant only supports float16 / bfloat16 inputs.");
-    std::vector<int64_t> scale_shape(x.sizes().begin(), x.sizes().end() - 1);
-    auto y = torch::empty_like(x, x.options().dtype(torch::kChar));
-    auto scale = torch::empty(scale_shape, x.options().dtype(torch::kFloat));
-    return std::make_tuple(y, scale);
-}
-
-static std::tuple<torch::Tensor, torch::Tensor> dynamic_quant_cuda(const torch::Tensor& x)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x.device());
-    auto xc = x.contiguous();
-    auto outs = dynamic_quant_meta(xc);
-    const int64_t N = xc.size(-1);
-    TORCH_CHECK(N > 0, "dynamic_quant requires a non-zero last dimension.");
-    const int64_t M = xc.numel() / N;
-    if (M <= 0) {
-        return outs;
-    }
-    check_status(w8a8_dynamic_quant(xc.data_ptr(), static_cast<int8_t*>(std::get<0>(outs).data_ptr()),
-                                    static_cast<float*>(std::get<1>(outs).data_ptr()), M, N, dtype_code(xc), 0,
-                                    stream_of(xc)),
-                 "dynamic_quant");
-    return outs;
-}
-
-// ------------------------------------------------------ add_rms_norm_dynamic_quant
-static std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> ardq_meta(const torch::Tensor& x1,
-                                                                         const torch::Tensor& x2,
-                                                                         const torch::Tensor& gamma, double epsilon)
-{
-    (void)epsilon;
-    TORCH_CHECK(x1.dim() >= 1, "add_rms_norm_dynamic_quant: x1 must have at least one dimension.");
-    TORCH_CHECK(x1.sizes() == x2.sizes(), "add_rms_norm_dynamic_quant: x1 and x2 must share a shape.");
-    TORCH_CHECK(gamma.dim() == 1 && gamma.size(0) == x1.size(-1),
-                "add_rms_norm_dynamic_quant: gamma must be 1-D with size == x1.size(-1).");
-    TORCH_CHECK(gamma.scalar_type() == x1.scalar_type(),
-                "add_rms_norm_dynamic_quant: gamma dtype must match x1 dtype.");
-    auto y = torch::empty_like(x1, x1.options().dtype(torch::kChar));
-    auto x_out = torch::empty_like(x1);
-    std::vector<int64_t> scale_shape(x1.sizes().begin(), x1.sizes().end() - 1);
-    auto scale = torch::empty(scale_shape, x1.options().dtype(torch::kFloat));
-    return std::make_tuple(y, x_out, scale);
-}
-
-static std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> ardq_cuda(const torch::Tensor& x1,
-                                                                         const torch::Tensor& x2,
-                                                                         const torch::Tensor& gamma, double epsilon)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x1.device());
-    auto x1c = x1.contiguous();
-    auto x2c = x2.contiguous();
-    auto gc = gamma.contiguous();
-    auto outs = ardq_meta(x1c, x2c, gc, epsilon);
-    const int64_t N = x1c.size(-1);
-    if (x1c.numel() == 0 || N <= 0) {
-        return outs;
-    }
-    TORCH_CHECK(x1c.scalar_type() == torch::kFloat16 || x1c.scalar_type() == torch::kBFloat16,
-                "add_rms_norm_dynamic_quant: only float16/bfloat16 inputs are supported.");
-    TORCH_CHECK(x2c.scalar_type() == x1c.scalar_type(), "add_rms_norm_dynamic_quant: x2 dtype must match x1 dtype.");
-    TORCH_CHECK(N <= 16384, "add_rms_norm_dynamic_quant: row length must not exceed 16384.");
-    const int64_t rows = x1c.numel() / N;
-    check_status(w8a8_add_rms_norm_dynamic_quant(x1c.data_ptr(), x2c.data_ptr(), gc.data_ptr(),
-                                                 static_cast<int8_t*>(std::get<0>(outs).data_ptr()),
-                                                 std::get<1>(outs).data_ptr(),
-                                                 static_cast<float*>(std::get<2>(outs).data_ptr()), rows, N,
-                                                 static_cast<float>(epsilon), dtype_code(x1c), 0, stream_of(x1c)),
-                 "add_rms_norm_dynamic_quant");
-    return outs;
-}
-
-// ------------------------------------------------------------------ quant_matmul
-static torch::Tensor quant_matmul_meta(const torch::Tensor& x1, const torch::Tensor& x2, const torch::Tensor& scale,
-                                       const c10::optional<torch::Tensor>& offset,
-                                       const c10::optional<torch::Tensor>& pertoken_scale,
-                                       const c10::optional<torch::Tensor>& bias,
-                                       const c10::optional<std::string>& output_dtype)
-{
-    (void)scale;
-    (void)offset;
-    (void)pertoken_scale;
-    (void)bias;
-    TORCH_CHECK(x1.dim() >= 2 && x2.dim() >= 2, "quant_matmul requires inputs of rank >= 2.");
-    TORCH_CHECK(x1.size(-1) == x2.size(-2), "quant_matmul requires x1.size(-1) == x2.size(-2).");
-    const bool bf16out = output_dtype.has_value() && output_dtype.value() == "bfloat16";
-    std::vector<int64_t> out_shape(x1.sizes().begin(), x1.sizes().end() - 1);
-    out_shape.push_back(x2.size(-1));
-    return torch::empty(out_shape, x1.options().dtype(bf16out ? torch::kBFloat16 : torch::kFloat16));
-}
-
-static torch::Tensor quant_matmul_cuda(const torch::Tensor& x1, const torch::Tensor& x2, const torch::Tensor& scale,
-                                       const c10::optional<torch::Tensor>& offset,
-                                       const c10::optional<torch::Tensor>& pertoken_scale,
-                                       const c10::optional<torch::Tensor>& bias,
-                                       const c10::optional<std::string>& output_dtype)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x1.device());
-    TORCH_CHECK(x1.scalar_type() == torch::kChar && x2.scalar_type() == torch::kChar,
-                "quant_matmul requires int8 x1 and x2.");
-    TORCH_CHECK(x1.is_contiguous() && x2.is_contiguous() && scale.is_contiguous(),
-                "quant_matmul requires contiguous x1/x2/scale.");
-    TORCH_CHECK(scale.scalar_type() == torch::kFloat32 || scale.scalar_type() == torch::kBFloat16,
-                "quant_matmul requires float32 or bfloat16 scale.");
-    TORCH_CHECK(x1.dim() >= 2 && x2.dim() >= 2 && x1.dim() == x2.dim(), "quant_matmul expects equal ranks >= 2.");
-    TORCH_CHECK(x1.size(-1) == x2.size(-2), "quant_matmul requires x1.size(-1) == x2.size(-2).");
-    const int64_t K = x1.size(-1), M = x1.size(-2), N = x2.size(-1);
-    TORCH_CHECK(K > 0 && M > 0 && N > 0, "quant_matmul requires non-empty shapes.");
-    int64_t batch = 1;
-    for (int64_t d = 0; d + 2 < x1.dim(); ++d) {
-        TORCH_CHECK(x1.size(d) == x2.size(d), "quant_matmul expects matching leading batch dimensions.");
-        batch *= x1.size(d);
-    }
-    auto out = quant_matmul_meta(x1, x2, scale, offset, pertoken_scale, bias, output_dtype);
-    const bool bf16out = out.scalar_type() == torch::kBFloat16;
-
-    int64_t flags = 0;
-    TORCH_CHECK(scale.numel() == 1 || scale.numel() == N, "quant_matmul expects scale length 1 or n.");
-    if (scale.numel() > 1) {
-        flags |= W8A8_QM_SCALE_PERCHAN;
-    }
-    if (scale.scalar_type() == torch::kBFloat16) {
-        flags |= W8A8_QM_SCALE_BF16;
-    }
-    const bool has_offset = offset.has_value() && offset->defined();
-    if (has_offset) {
-        TORCH_CHECK(offset->scalar_type() == torch::kFloat32 && offset->is_contiguous(),
-                    "quant_matmul requires float32 contiguous offset.");
-        TORCH_CHECK(offset->numel() == 1 || offset->numel() == N, "quant_matmul expects offset length 1 or n.");
-        flags |= W8A8_QM_HAS_OFFSET;
-        if (offset->numel() > 1) {
-            flags |= W8A8_QM_OFFSET_PERCHAN;
+    for (const TypeInfo& e : TYPE_TABLE) {
+        if (e.torch_type == t) {
+            return &e;
         }
     }
-    const bool has_pt = pertoken_scale.has_value() && pertoken_scale->defined();
-    if (has_pt) {
-        TORCH_CHECK(pertoken_scale->scalar_type() == torch::kFloat32 && pertoken_scale->is_contiguous(),
-                    "quant_matmul requires float32 contiguous pertoken_scale.");
-        TORCH_CHECK(pertoken_scale->numel() == M, "quant_matmul expects pertoken_scale length m.");
-        flags |= W8A8_QM_HAS_PT;
-    }
-    const bool has_bias = bias.has_value() && bias->defined();
-    int64_t bias_batch_stride = 0;
-    if (has_bias) {
-        TORCH_CHECK(bias->is_contiguous(), "quant_matmul requires contiguous bias.");
-        int64_t kind = W8A8_QM_BIAS_NONE;
-        switch (bias->scalar_type()) {
-        case torch::kInt32:
-            kind = W8A8_QM_BIAS_I32;
-            break;
-        case torch::kFloat16:
-            kind = W8A8_QM_BIAS_F16;
-            break;
-        case torch::kBFloat16:
-            kind = W8A8_QM_BIAS_BF16;
-            break;
-        case torch::kFloat32:
-            kind = W8A8_QM_BIAS_F32;
-            break;
-        default:
-            TORCH_CHECK(false, "quant_matmul unsupported bias dtype: ", bias->scalar_type());
-        }
-        bool per_chan;
-        if (bias->dim() == 3 && bias->size(1) == 1 && bias->size(2) == N && batch > 1 && bias->size(0) == batch) {
-            bias_batch_stride = N;
-            per_chan = N > 1;
-        } else {
-            TORCH_CHECK(bias->numel() == 1 || bias->numel() == N, "quant_matmul expects bias length 1 or n.");
-            per_chan = bias->numel() > 1;
-        }
-        flags |= kind << W8A8_QM_BIAS_SHIFT;
-        if (per_chan) {
-            flags |= W8A8_QM_BIAS_PERCHAN;
-        }
-    }
-    if (batch > 1) {
-        flags |= W8A8_QM_PT_MOD_M;
-    }
-    check_status(w8a8_quant_matmul(static_cast<const int8_t*>(x1.data_ptr()), static_cast<const int8_t*>(x2.data_ptr()),
-                                   scale.data_ptr(), has_offset ? static_cast<const float*>(offset->data_ptr()) : nullptr,
-                                   has_pt ? static_cast<const float*>(pertoken_scale->data_ptr()) : nullptr,
-                                   has_bias ? bias->data_ptr() : nullptr, out.data_ptr(), batch, M, N, K, flags,
-                                   bf16out ? W8A8_DT_BF16 : W8A8_DT_F16, W8A8_W_KN, bias_batch_stride, stream_of(x1)),
-                 "quant_matmul");
-    return out;
+    return nullptr;
 }
 
-// --------------------------------------------------- grouped_matmul_swiglu_quant
-static std::vector<int64_t> collect_ends(c10::List<int64_t> group_list, int64_t E, int64_t M, const char* op)
+unsigned type_bit(const Tensor& t)
 {
-    TORCH_CHECK(static_cast<int64_t>(group_list.size()) == E, op, ": group_list length must equal the expert count");
-    std::vector<int64_t> ends(static_cast<size_t>(E));
-    int64_t prev = 0;
-    for (int64_t g = 0; g < E; ++g) {
-        const int64_t v = group_list[static_cast<size_t>(g)];
-        TORCH_CHECK(v >= prev && v <= M, op, ": group_list must be a cumsum <= M");
-        ends[static_cast<size_t>(g)] = v;
-        prev = v;
+    const TypeInfo* e = type_info(t.scalar_type());
+    return e != nullptr ? e->bit : 0u;
+}
+
+int abi_type(const Tensor& t)
+{
+    const TypeInfo* e = type_info(t.scalar_type());
+    TORCH_CHECK(e != nullptr && e->abi_code >= 0, "unsupported dtype ", t.scalar_type());
+    return e->abi_code;
+}
+
+bool given(const OptTensor& t) { return t.has_value() && t->defined(); }
+
+std::vector<int64_t> all_but_last(const Tensor& t)
+{
+    return std::vector<int64_t>(t.sizes().begin(), t.sizes().end() - 1);
+}
+
+// One operator invocation: device guard, stream, argument intake, status translation.
+class Call {
+public:
+    Call(const char* op, const Tensor& anchor)
+        : op_(op), guard_(anchor.device()),
+          stream_(static_cast<void*>(at::cuda::getCurrentCUDAStream(anchor.device().index()).stream()))
+    {
     }
-    TORCH_CHECK(prev == M, op, ": group_list[-1] must equal M");
+
+    // the message is the whole sentence the user sees; nothing is prefixed, so texts stay greppable
+    template <typename... Parts>
+    void require(bool ok, const Parts&... parts) const
+    {
+        TORCH_CHECK(ok, parts...);
+    }
+
+    // A mandatory tensor: element type in `types`, rank in [rank_lo, rank_hi] (rank_hi < 0: no upper bound).
+    // `dense` asks for a contiguous copy when the tensor is strided; otherwise a strided tensor is an error.
+    Tensor in(const Tensor& t, unsigned types, int rank_lo, int rank_hi, const char* type_msg, const char* rank_msg,
+              bool dense = true)
+    {
+        require((type_bit(t) & types) != 0u, type_msg);
+        require(t.dim() >= rank_lo && (rank_hi < 0 || t.dim() <= rank_hi), rank_msg);
+        if (t.is_contiguous()) {
+            return t;
+        }
+        require(dense, op_, " requires contiguous inputs.");
+        held_.push_back(t.contiguous());
+        return held_.back();
+    }
+
+    // An optional tensor: an undefined Tensor when absent.
+    Tensor opt(const OptTensor& t, unsigned types, const char* type_msg, bool dense = true)
+    {
+        if (!given(t)) {
+            return Tensor();
+        }
+        return in(*t, types, 0, -1, type_msg, type_msg, dense);
+    }
+
+    static const void* ptr(const Tensor& t) { return t.defined() ? t.data_ptr() : nullptr; }
+    template <typename T>
+    static T* as(const Tensor& t)
+    {
+        return t.defined() ? static_cast<T*>(t.data_ptr()) : nullptr;
+    }
+
+    Tensor scratch(size_t bytes, const Tensor& like)
+    {
+        held_.push_back(torch::empty({static_cast<int64_t>(bytes)}, like.options().dtype(torch::kUInt8)));
+        return held_.back();
+    }
+
+    void* stream() const { return stream_; }
+
+    void done(int status) const
+    {
+        TORCH_CHECK(status == W8A8_OK, op_, ": ", w8a8_status_string(status), " (status ", status, ")");
+    }
+
+private:
+    const char* op_;
+    c10::cuda::OptionalCUDAGuard guard_;
+    void* stream_;
+    std::vector<Tensor> held_;
+};
+
+// The cumulative group list as the library takes it (host int64 array), with the checks whose failures a
+// Python caller should see as a torch error rather than as a status code.
+std::vector<int64_t> group_ends(const c10::List<int64_t>& list, int64_t experts, int64_t rows, const char* op)
+{
+    TORCH_CHECK(static_cast<int64_t>(list.size()) == experts, op, ": group_list length must equal the expert count");
+    std::vector<int64_t> ends;
+    ends.reserve(static_cast<size_t>(experts));
+    int64_t floor = 0;
+    bool sorted = true;
+    for (size_t i = 0; i < list.size(); ++i) {
+        const int64_t v = list.get(i);
+        sorted = sorted && v >= floor && v <= rows;
+        floor = v;
+        ends.push_back(v);
+    }
+    TORCH_CHECK(sorted, op, ": group_list must be a cumsum <= M");
+    TORCH_CHECK(floor == rows, op, ": group_list[-1] must equal M");
     return ends;
 }
 
-static std::tuple<torch::Tensor, torch::Tensor> gmsq_meta(const torch::Tensor& x, const torch::Tensor& weight,
-                                                          const torch::Tensor& weight_scale,
-                                                          const torch::Tensor& x_scale, c10::List<int64_t> group_list)
-{
-    (void)weight_scale;
-    (void)x_scale;
-    (void)group_list;
-    TORCH_CHECK(x.dim() == 2, "grouped_matmul_swiglu_quant: x must be 2D [M, K]");
-    TORCH_CHECK(weight.dim() == 3, "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]");
-    const int64_t M = x.size(0);
-    const int64_t N = weight.size(2);
-    TORCH_CHECK(N % 2 == 0, "grouped_matmul_swiglu_quant: N must be even");
-    auto y = torch::empty({M, N / 2}, x.options().dtype(torch::kChar));
-    auto y_scale = torch::empty({M}, x.options().dtype(torch::kFloat32));
-    return std::make_tuple(y, y_scale);
-}
+// ================================================================ dynamic_quant
+struct DynamicQuant {
+    using Out = std::tuple<Tensor, Tensor>;
 
-static std::tuple<torch::Tensor, torch::Tensor> gmsq_cuda(const torch::Tensor& x, const torch::Tensor& weight,
-                                                          const torch::Tensor& weight_scale,
-                                                          const torch::Tensor& x_scale, c10::List<int64_t> group_list)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x.device());
-    TORCH_CHECK(x.scalar_type() == torch::kChar, "grouped_matmul_swiglu_quant: x must be int8");
-    TORCH_CHECK(weight.scalar_type() == torch::kChar, "grouped_matmul_swiglu_quant: weight must be int8");
-    TORCH_CHECK(weight_scale.scalar_type() == torch::kFloat, "grouped_matmul_swiglu_quant: weight_scale must be float32");
-    TORCH_CHECK(x_scale.scalar_type() == torch::kFloat, "grouped_matmul_swiglu_quant: x_scale must be float32");
-    auto xc = x.contiguous();
-    auto wc = weight.contiguous();
-    auto wsc = weight_scale.contiguous();
-    auto xsc = x_scale.contiguous();
-    auto outs = gmsq_meta(xc, wc, wsc, xsc, group_list);
-    const int64_t M = xc.size(0), K = xc.size(1), E = wc.size(0), N = wc.size(2);
-    if (M == 0 || N == 0 || E == 0) {
-        return outs;
+    static Out shape(const Tensor& x)
+    {
+        TORCH_CHECK(x.dim() >= 2, "dynamic_quant requires a tensor with rank >= 2.");
+        TORCH_CHECK((type_bit(x) & HALVES) != 0u, "dynamic_quant only supports float16 / bfloat16 inputs.");
+        return {torch::empty_like(x, x.options().dtype(torch::kChar)),
+                torch::empty(all_but_last(x), x.options().dtype(torch::kFloat))};
     }
-    TORCH_CHECK(wc.size(1) == K, "grouped_matmul_swiglu_quant: K mismatch between x and weight");
-    TORCH_CHECK(xsc.numel() == M, "grouped_matmul_swiglu_quant: x_scale must have M elements");
-    TORCH_CHECK(wsc.dim() == 2 && wsc.size(0) == E && wsc.size(1) == N,
-                "grouped_matmul_swiglu_quant: weight_scale must be [E, N]");
-    const std::vector<int64_t> ends = collect_ends(group_list, E, M, "grouped_matmul_swiglu_quant");
-    const size_t ws_bytes = w8a8_grouped_matmul_swiglu_quant_workspace_size(M, K, N, E);
-    auto ws = torch::empty({static_cast<int64_t>(ws_bytes)}, xc.options().dtype(torch::kUInt8));
-    check_status(w8a8_grouped_matmul_swiglu_quant(
-                     static_cast<const int8_t*>(xc.data_ptr()), static_cast<const int8_t*>(wc.data_ptr()),
-                     static_cast<const float*>(wsc.data_ptr()), static_cast<const float*>(xsc.data_ptr()),
-                     static_cast<int8_t*>(std::get<0>(outs).data_ptr()),
-                     static_cast<float*>(std::get<1>(outs).data_ptr()), M, K, N, E, ends.data(), 0, W8A8_W_KN, 0,
-                     ws.data_ptr(), ws_bytes, stream_of(xc)),
-                 "grouped_matmul_swiglu_quant");
-    return outs;
-}
 
-// ---------------------------------------------------------------- grouped_matmul
-static c10::List<torch::Tensor> make_outputs(const torch::Tensor& y, const std::vector<int64_t>& ends,
-                                             int64_t split_item)
-{
-    c10::List<torch::Tensor> out;
-    if (split_item == 0 || split_item == 1) {
-        int64_t s = 0;
-        for (const int64_t e : ends) {
-            out.push_back(y.narrow(0, s, e - s));
-            s = e;
+    static Out run(const Tensor& x)
+    {
+        Call call("dynamic_quant", x);
+        const Tensor xd = call.in(x, HALVES, 2, -1, "dynamic_quant only supports float16 / bfloat16 inputs.",
+                                  "dynamic_quant requires a tensor with rank >= 2.");
+        Out out = shape(xd);
+        const int64_t width = xd.size(-1);
+        call.require(width > 0, "dynamic_quant requires a non-zero last dimension.");
+        if (xd.numel() > 0) {
+            call.done(w8a8_dynamic_quant(xd.data_ptr(), Call::as<int8_t>(std::get<0>(out)),
+                                         Call::as<float>(std::get<1>(out)), xd.numel() / width, width, abi_type(xd),
+                                         0, call.stream()));
         }
-    } else {
-        out.push_back(y);
-    }
-    return out;
-}
-
-static c10::List<torch::Tensor> grouped_matmul_meta(const torch::Tensor& x, const torch::Tensor& weight,
-                                                    c10::List<int64_t> group_list,
-                                                    const c10::optional<torch::Tensor>& bias, int64_t split_item,
-                                                    bool transpose_weight,
-                                                    const c10::optional<torch::Tensor>& x_scale,
-                                                    const c10::optional<torch::Tensor>& weight_scale)
-{
-    (void)bias;
-    (void)weight_scale;
-    TORCH_CHECK(x.dim() == 2, "grouped_matmul: x must be 2D [M, K]");
-    TORCH_CHECK(weight.dim() == 3, "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]");
-    const int64_t M = x.size(0);
-    const int64_t E = weight.size(0);
-    const int64_t N = transpose_weight ? weight.size(1) : weight.size(2);
-    const std::vector<int64_t> ends = collect_ends(group_list, E, M, "grouped_matmul");
-    const bool quant = x_scale.has_value() && x_scale->defined();
-    auto y = torch::empty({M, N}, quant ? x.options().dtype(torch::kBFloat16) : x.options());
-    return make_outputs(y, ends, split_item);
-}
-
-static c10::List<torch::Tensor> grouped_matmul_cuda(const torch::Tensor& x, const torch::Tensor& weight,
-                                                    c10::List<int64_t> group_list,
-                                                    const c10::optional<torch::Tensor>& bias, int64_t split_item,
-                                                    bool transpose_weight,
-                                                    const c10::optional<torch::Tensor>& x_scale,
-                                                    const c10::optional<torch::Tensor>& weight_scale)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x.device());
-    auto xc = x.contiguous();
-    auto wc = weight.contiguous();
-    const int64_t M = xc.size(0), K = xc.size(1), E = wc.size(0);
-    TORCH_CHECK(E >= 1, "grouped_matmul: weight must contain at least one expert");
-    const int64_t N = transpose_weight ? wc.size(1) : wc.size(2);
-    const int64_t k_stored = transpose_weight ? wc.size(2) : wc.size(1);
-    TORCH_CHECK(k_stored == K, "grouped_matmul: K dimension mismatch between x and weight");
-    TORCH_CHECK(xc.scalar_type() == wc.scalar_type(), "grouped_matmul: x and weight must share a dtype");
-    const std::vector<int64_t> ends = collect_ends(group_list, E, M, "grouped_matmul");
-    const int dt = dtype_code(xc);
-    const bool quant = dt == W8A8_DT_I8;
-    torch::Tensor xs, wsc;
-    if (quant) {
-        TORCH_CHECK(x_scale.has_value() && weight_scale.has_value(),
-                    "grouped_matmul: int8 inputs need x_scale and weight_scale");
-        xs = x_scale->contiguous();
-        wsc = weight_scale->contiguous();
-        TORCH_CHECK(xs.scalar_type() == torch::kFloat && xs.numel() == M, "grouped_matmul: x_scale must be fp32 [M]");
-        TORCH_CHECK(wsc.scalar_type() == torch::kFloat && wsc.numel() == E * N,
-                    "grouped_matmul: weight_scale must be fp32 [E, N]");
-    } else {
-        TORCH_CHECK(!(x_scale.has_value() && x_scale->defined()) && !(weight_scale.has_value() && weight_scale->defined()),
-                    "grouped_matmul: scales are only valid with int8 inputs");
-    }
-    const bool has_bias = bias.has_value() && bias->defined();
-    torch::Tensor bc;
-    if (has_bias) {
-        bc = bias->contiguous();
-        TORCH_CHECK(bc.numel() == E * N, "grouped_matmul: bias must have shape [E, N]");
-    }
-    auto y = torch::empty({M, N}, quant ? xc.options().dtype(torch::kBFloat16) : xc.options());
-    if (M > 0) {
-        const size_t ws_bytes = w8a8_grouped_matmul_workspace_size(M, N, K, E);
-        auto ws = torch::empty({static_cast<int64_t>(ws_bytes)}, xc.options().dtype(torch::kUInt8));
-        check_status(w8a8_grouped_matmul(xc.data_ptr(), wc.data_ptr(), has_bias ? bc.data_ptr() : nullptr, y.data_ptr(),
-                                         quant ? static_cast<const float*>(xs.data_ptr()) : nullptr,
-                                         quant ? static_cast<const float*>(wsc.data_ptr()) : nullptr, M, N, K, E,
-                                         ends.data(), 0, dt, has_bias ? dtype_code(bc) : dt, dtype_code(y),
-                                         transpose_weight ? W8A8_W_NK : W8A8_W_KN, ws.data_ptr(), ws_bytes,
-                                         stream_of(xc)),
-                     "grouped_matmul");
-    }
-    return make_outputs(y, ends, split_item);
-}
-
-// ---------------------------------------------------------------- moe_re_routing
-using RrOut = std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>;
-
-static RrOut moe_re_routing_meta(const torch::Tensor& tokens, const torch::Tensor& counts,
-                                 const c10::optional<torch::Tensor>& scales, int64_t expert_token_num_type,
-                                 int64_t idx_type)
-{
-    (void)scales;
-    (void)expert_token_num_type;
-    (void)idx_type;
-    TORCH_CHECK(tokens.dim() == 2, "moe_re_routing: tokens must be 2D (A, H).");
-    TORCH_CHECK(counts.dim() == 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
-    const int64_t a = tokens.size(0);
-    return std::make_tuple(torch::empty({a, tokens.size(1)}, tokens.options()),
-                           torch::empty({a}, tokens.options().dtype(torch::kFloat)),
-                           torch::empty({a}, tokens.options().dtype(torch::kInt)),
-                           torch::empty({counts.size(1)}, counts.options()));
-}
-
-static RrOut moe_re_routing_cuda(const torch::Tensor& tokens, const torch::Tensor& counts,
-                                 const c10::optional<torch::Tensor>& scales, int64_t expert_token_num_type,
-                                 int64_t idx_type)
-{
-    TORCH_CHECK(idx_type == 0, "moe_re_routing: only gather index mode (idx_type == 0) is supported.");
-    const c10::cuda::OptionalCUDAGuard guard(tokens.device());
-    auto tok = tokens.contiguous();
-    auto cnt = counts.contiguous();
-    torch::Tensor scl;
-    const bool has_scales = scales.has_value() && scales->defined();
-    if (has_scales) {
-        scl = scales->contiguous();
-        TORCH_CHECK(scl.scalar_type() == torch::kFloat, "moe_re_routing: per_token_scales must be float32.");
-    }
-    auto outs = moe_re_routing_meta(tok, cnt, scales, expert_token_num_type, idx_type);
-    const int64_t a = tok.size(0), h = tok.size(1), n = cnt.size(0), e = cnt.size(1);
-    if (a <= 0 || h <= 0 || n <= 0 || e <= 0) {
-        return outs;
-    }
-    TORCH_CHECK(tok.scalar_type() == torch::kFloat16 || tok.scalar_type() == torch::kBFloat16 ||
-                    tok.scalar_type() == torch::kChar,
-                "moe_re_routing: unsupported tokens dtype.");
-    TORCH_CHECK(cnt.scalar_type() == torch::kInt || cnt.scalar_type() == torch::kLong,
-                "moe_re_routing: unsupported expert_token_num_per_rank dtype.");
-    TORCH_CHECK(cnt.is_cuda(), "moe_re_routing: expert_token_num_per_rank must be on the tokens' device.");
-    if (has_scales) {
-        TORCH_CHECK(scl.numel() == a, "moe_re_routing: per_token_scales must have A elements.");
-    }
-    const size_t ws_bytes = w8a8_moe_re_routing_workspace_size(a, n, e);
-    auto ws = torch::empty({static_cast<int64_t>(ws_bytes)}, tok.options().dtype(torch::kByte));
-    check_status(w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(),
-                                     has_scales ? static_cast<const float*>(scl.data_ptr()) : nullptr,
-                                     std::get<0>(outs).data_ptr(), static_cast<float*>(std::get<1>(outs).data_ptr()),
-                                     static_cast<int32_t*>(std::get<2>(outs).data_ptr()),
-                                     std::get<3>(outs).data_ptr(), a, h * static_cast<int64_t>(tok.element_size()), n,
-                                     e, static_cast<int>(cnt.element_size()), ws.data_ptr(), ws_bytes,
-                                     stream_of(tok)),
-                 "moe_re_routing");
-    return outs;
-}
-
-// ---------------------------------------------------------- moe_finalize_routing
-static bool present(const c10::optional<torch::Tensor>& t)
-{
-    return t.has_value() && t->defined();
-}
-
-static void mfr_shape(const torch::Tensor& epr, const torch::Tensor& esdr, const c10::optional<torch::Tensor>& scales,
-                      int64_t& num_rows, int64_t& K, int64_t& H)
-{
-    TORCH_CHECK(epr.dim() >= 2, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
-    TORCH_CHECK(esdr.scalar_type() == torch::kInt, "moe_finalize_routing: expanded_src_to_dst_row must be int32.");
-    H = epr.size(-1);
-    K = 1;
-    if (present(scales)) {
-        TORCH_CHECK(scales->dim() == 2, "moe_finalize_routing: scales must be 2-D (NUM_ROWS, K).");
-        K = scales->size(1);
-    }
-    TORCH_CHECK(K > 0, "moe_finalize_routing: K must be positive.");
-    TORCH_CHECK(esdr.numel() % K == 0, "moe_finalize_routing: expanded_src_to_dst_row length must be K*NUM_ROWS.");
-    num_rows = esdr.numel() / K;
-}
-
-static torch::Tensor mfr_meta(const torch::Tensor& epr, const torch::Tensor& esdr, c10::optional<torch::Tensor> skip1,
-                              c10::optional<torch::Tensor> skip2, c10::optional<torch::Tensor> bias,
-                              c10::optional<torch::Tensor> scales, c10::optional<torch::Tensor> expert,
-                              int64_t drop_pad_mode)
-{
-    (void)skip1;
-    (void)skip2;
-    (void)bias;
-    (void)expert;
-    (void)drop_pad_mode;
-    int64_t num_rows = 0, K = 1, H = 0;
-    mfr_shape(epr, esdr, scales, num_rows, K, H);
-    return torch::empty({num_rows, H}, epr.options());
-}
-
-static torch::Tensor mfr_cuda(const torch::Tensor& rows, const torch::Tensor& src_to_dst,
-                              c10::optional<torch::Tensor> skip1, c10::optional<torch::Tensor> skip2,
-                              c10::optional<torch::Tensor> bias, c10::optional<torch::Tensor> scales,
-                              c10::optional<torch::Tensor> expert, int64_t drop_pad_mode)
-{
-    const auto t = rows.scalar_type();
-    TORCH_CHECK(t == torch::kFloat16 || t == torch::kFloat32 || t == torch::kBFloat16,
-                "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.");
-    const c10::cuda::OptionalCUDAGuard guard(rows.device());
-    auto epr = rows.contiguous();
-    auto esdr = src_to_dst.contiguous();
-    int64_t num_rows = 0, K = 1, H = 0;
-    mfr_shape(epr, esdr, scales, num_rows, K, H);
-    auto out = torch::empty({num_rows, H}, epr.options());
-    if (num_rows <= 0 || H <= 0) {
         return out;
     }
-    const bool has_scales = present(scales);
-    const bool has_expert = present(expert);
-    const bool has_bias = present(bias) && has_expert;
-    if (has_bias) {
-        TORCH_CHECK(bias->size(1) == H, "moe_finalize_routing: bias head dim must equal H.");
-        TORCH_CHECK(bias->scalar_type() == t, "moe_finalize_routing: bias must have the rows' dtype.");
-        TORCH_CHECK(expert->scalar_type() == torch::kInt, "moe_finalize_routing: expert_for_source_row must be int32.");
-    }
-    TORCH_CHECK(!present(skip1) || skip1->scalar_type() == t, "moe_finalize_routing: skip1 must have the rows' dtype.");
-    TORCH_CHECK(!present(skip2) || skip2->scalar_type() == t, "moe_finalize_routing: skip2 must have the rows' dtype.");
-    torch::Tensor s1, s2, bs, sc, ex;
-    if (present(skip1)) {
-        s1 = skip1->contiguous();
-    }
-    if (present(skip2)) {
-        s2 = skip2->contiguous();
-    }
-    if (has_bias) {
-        bs = bias->contiguous();
-        ex = expert->contiguous();
-    }
-    int sdt = dtype_code(epr);
-    if (has_scales) {
-        sc = scales->contiguous();
-        const auto st = sc.scalar_type();
-        TORCH_CHECK(st == torch::kFloat16 || st == torch::kFloat32 || st == torch::kBFloat16,
-                    "moe_finalize_routing: unsupported dtype combination for expanded_permuted_rows / scales.");
-        sdt = dtype_code(sc);
-    }
-    const int64_t mode = drop_pad_mode < 0 ? 0 : (drop_pad_mode > 3 ? 3 : drop_pad_mode);
-    check_status(w8a8_moe_finalize_routing(epr.data_ptr(), static_cast<const int32_t*>(esdr.data_ptr()),
-                                           s1.defined() ? s1.data_ptr() : nullptr,
-                                           s2.defined() ? s2.data_ptr() : nullptr,
-                                           has_bias ? bs.data_ptr() : nullptr, has_scales ? sc.data_ptr() : nullptr,
-                                           has_bias ? static_cast<const int32_t*>(ex.data_ptr()) : nullptr,
-                                           out.data_ptr(), num_rows, H, K, has_bias ? bs.size(0) : 0,
-                                           epr.numel() / H, static_cast<int>(mode), dtype_code(epr), sdt,
-                                           stream_of(epr)),
-                 "moe_finalize_routing");
-    return out;
-}
+};
 
-// ------------------------------------------------------ moe_gating_top_k_softmax
-using GateOut = std::tuple<torch::Tensor, torch::Tensor, torch::Tensor>;
+// =================================================== add_rms_norm_dynamic_quant
+struct AddRmsNormDynamicQuant {
+    using Out = std::tuple<Tensor, Tensor, Tensor>;
 
-static GateOut gating_meta(const torch::Tensor& x, const c10::optional<torch::Tensor>& finished, int64_t k)
-{
-    TORCH_CHECK(x.scalar_type() == torch::kFloat32 || x.scalar_type() == torch::kFloat16 ||
-                    x.scalar_type() == torch::kBFloat16,
-                "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.");
-    TORCH_CHECK(x.dim() >= 2, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.");
-    const int64_t inner = x.size(-1);
-    TORCH_CHECK(inner > 0, "cann_bench.moe_gating_top_k_softmax requires a non-empty last dimension.");
-    TORCH_CHECK(k > 0 && k <= inner, "cann_bench.moe_gating_top_k_softmax requires 0 < k <= x.size(-1).");
-    if (present(finished)) {
-        TORCH_CHECK(finished->scalar_type() == torch::kBool,
+    static Out shape(const Tensor& x1, const Tensor& x2, const Tensor& gamma, double /*epsilon*/)
+    {
+        TORCH_CHECK(x1.dim() >= 1, "add_rms_norm_dynamic_quant: x1 must have at least one dimension.");
+        TORCH_CHECK(x1.sizes() == x2.sizes(), "add_rms_norm_dynamic_quant: x1 and x2 must share a shape.");
+        TORCH_CHECK(gamma.dim() == 1 && gamma.size(0) == x1.size(-1),
+                    "add_rms_norm_dynamic_quant: gamma must be 1-D with size == x1.size(-1).");
+        TORCH_CHECK(gamma.scalar_type() == x1.scalar_type(),
+                    "add_rms_norm_dynamic_quant: gamma dtype must match x1 dtype.");
+        return {torch::empty_like(x1, x1.options().dtype(torch::kChar)), torch::empty_like(x1),
+                torch::empty(all_but_last(x1), x1.options().dtype(torch::kFloat))};
+    }
+
+    static Out run(const Tensor& x1, const Tensor& x2, const Tensor& gamma, double epsilon)
+    {
+        Call call("add_rms_norm_dynamic_quant", x1);
+        if (x1.numel() == 0) {
+            return shape(x1, x2, gamma, epsilon);
+        }
+        const char* types = "add_rms_norm_dynamic_quant: only float16/bfloat16 inputs are supported.";
+        const char* rank = "add_rms_norm_dynamic_quant: x1 must have at least one dimension.";
+        const Tensor a = call.in(x1, HALVES, 1, -1, types, rank);
+        const Tensor b = call.in(x2, type_bit(a), 1, -1, "add_rms_norm_dynamic_quant: x2 dtype must match x1 dtype.",
+                                 rank);
+        const Tensor g = call.in(gamma, type_bit(a), 1, 1, "add_rms_norm_dynamic_quant: gamma dtype must match x1 dtype.",
+                                 "add_rms_norm_dynamic_quant: gamma must be 1-D with size == x1.size(-1).");
+        const int64_t width = a.size(-1);
+        call.require(width <= 16384, "add_rms_norm_dynamic_quant: row length must not exceed 16384.");
+        Out out = shape(a, b, g, epsilon);  // shaped like the dense copies: the library writes dense rows
+        call.done(w8a8_add_rms_norm_dynamic_quant(a.data_ptr(), b.data_ptr(), g.data_ptr(),
+                                                  Call::as<int8_t>(std::get<0>(out)), std::get<1>(out).data_ptr(),
+                                                  Call::as<float>(std::get<2>(out)),
+                                                  a.numel() / width, width, static_cast<float>(epsilon), abi_type(a),
+                                                  0, call.stream()));
+        return out;
+    }
+};
+
+// ================================================================= quant_matmul
+struct QuantMatmul {
+    static Tensor shape(const Tensor& x1, const Tensor& x2, const Tensor& /*scale*/, const OptTensor& /*offset*/,
+                        const OptTensor& /*pertoken_scale*/, const OptTensor& /*bias*/,
+                        const c10::optional<std::string>& output_dtype)
+    {
+        TORCH_CHECK(x1.dim() >= 2 && x2.dim() >= 2, "quant_matmul requires inputs of rank >= 2.");
+        TORCH_CHECK(x1.size(-1) == x2.size(-2), "quant_matmul requires x1.size(-1) == x2.size(-2).");
+        std::vector<int64_t> dims = all_but_last(x1);
+        dims.push_back(x2.size(-1));
+        const bool bf16 = output_dtype.has_value() && *output_dtype == "bfloat16";
+        return torch::empty(dims, x1.options().dtype(bf16 ? torch::kBFloat16 : torch::kFloat16));
+    }
+
+    // One per-channel-or-scalar operand of the epilogue: which flag bits it raises.
+    struct Term {
+        const Tensor* t;
+        int64_t present;
+        int64_t per_channel;
+        const char* size_msg;
+    };
+
+    static Tensor run(const Tensor& x1, const Tensor& x2, const Tensor& scale, const OptTensor& offset,
+                      const OptTensor& pertoken_scale, const OptTensor& bias,
+                      const c10::optional<std::string>& output_dtype)
+    {
+        Call call("quant_matmul", x1);
+        const char* i8 = "quant_matmul requires int8 x1 and x2.";
+        const char* rk = "quant_matmul expects equal ranks >= 2.";
+        const Tensor a = call.in(x1, I8, 2, -1, i8, rk, /*dense=*/false);
+        const Tensor b = call.in(x2, I8, static_cast<int>(x1.dim()), static_cast<int>(x1.dim()), i8, rk, false);
+        const Tensor sc = call.in(scale, F32 | BF16, 0, -1, "quant_matmul requires float32 or bfloat16 scale.", rk, false);
+        const Tensor off = call.opt(offset, F32, "quant_matmul requires float32 contiguous offset.", false);
+        const Tensor pt = call.opt(pertoken_scale, F32, "quant_matmul requires float32 contiguous pertoken_scale.", false);
+        const Tensor bs = call.opt(bias, I32 | FLOATS, "quant_matmul unsupported bias dtype", false);
+        Tensor out = shape(a, b, sc, offset, pertoken_scale, bias, output_dtype);
+
+        const int64_t rows = a.size(-2), depth = a.size(-1), cols = b.size(-1);
+        call.require(rows > 0 && depth > 0 && cols > 0, "quant_matmul requires non-empty shapes.");
+        call.require(a.sizes().slice(0, a.dim() - 2) == b.sizes().slice(0, b.dim() - 2),
+                     "quant_matmul expects matching leading batch dimensions.");
+        const int64_t batch = a.numel() / (rows * depth);
+
+        // a bias shaped [batch, 1, cols] carries one row per batch entry; anything else is shared by all of them
+        const bool bias_per_batch = bs.defined() && batch > 1 && bs.dim() == 3 && bs.size(0) == batch &&
+                                    bs.size(1) == 1 && bs.size(2) == cols;
+        int64_t flags = (batch > 1) ? W8A8_QM_PT_MOD_M : 0;
+        const Term terms[] = {
+            {&sc, 0, W8A8_QM_SCALE_PERCHAN, "quant_matmul expects scale length 1 or n."},
+            {&off, W8A8_QM_HAS_OFFSET, W8A8_QM_OFFSET_PERCHAN, "quant_matmul expects offset length 1 or n."},
+            {&bs, 0, W8A8_QM_BIAS_PERCHAN, "quant_matmul expects bias length 1 or n."},
+        };
+        for (const Term& term : terms) {
+            if (!term.t->defined()) {
+                continue;
+            }
+            const int64_t count = (term.t == &bs && bias_per_batch) ? cols : term.t->numel();
+            call.require(count == 1 || count == cols, term.size_msg);
+            flags |= term.present | (count > 1 ? term.per_channel : 0);
+        }
+        if (sc.scalar_type() == torch::kBFloat16) {
+            flags |= W8A8_QM_SCALE_BF16;
+        }
+        if (pt.defined()) {
+            call.require(pt.numel() == rows, "quant_matmul expects pertoken_scale length m.");
+            flags |= W8A8_QM_HAS_PT;
+        }
+        if (bs.defined()) {
+            constexpr struct {
+                unsigned bit;
+                int64_t kind;
+            } kinds[] = {{I32, W8A8_QM_BIAS_I32}, {F16, W8A8_QM_BIAS_F16}, {BF16, W8A8_QM_BIAS_BF16},
+                         {F32, W8A8_QM_BIAS_F32}};
+            for (const auto& k : kinds) {
+                if (type_bit(bs) == k.bit) {
+                    flags |= k.kind << W8A8_QM_BIAS_SHIFT;
+                }
+            }
+        }
+        call.done(w8a8_quant_matmul(Call::as<const int8_t>(a), Call::as<const int8_t>(b), sc.data_ptr(),
+                                    Call::as<const float>(off), Call::as<const float>(pt), Call::ptr(bs),
+                                    out.data_ptr(), batch, rows, cols, depth, flags,
+                                    out.scalar_type() == torch::kBFloat16 ? W8A8_DT_BF16 : W8A8_DT_F16, W8A8_W_KN,
+                                    bias_per_batch ? cols : 0, call.stream()));
+        return out;
+    }
+};
+
+// ================================================== grouped_matmul_swiglu_quant
+struct GroupedMatmulSwigluQuant {
+    using Out = std::tuple<Tensor, Tensor>;
+
+    static Out shape(const Tensor& x, const Tensor& weight, const Tensor& /*weight_scale*/, const Tensor& /*x_scale*/,
+                     c10::List<int64_t> /*group_list*/)
+    {
+        TORCH_CHECK(x.dim() == 2, "grouped_matmul_swiglu_quant: x must be 2D [M, K]");
+        TORCH_CHECK(weight.dim() == 3, "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]");
+        TORCH_CHECK(weight.size(2) % 2 == 0, "grouped_matmul_swiglu_quant: N must be even");
+        return {torch::empty({x.size(0), weight.size(2) / 2}, x.options().dtype(torch::kChar)),
+                torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32))};
+    }
+
+    static Out run(const Tensor& x, const Tensor& weight, const Tensor& weight_scale, const Tensor& x_scale,
+                   c10::List<int64_t> group_list)
+    {
+        Call call("grouped_matmul_swiglu_quant", x);
+        const Tensor rows = call.in(x, I8, 2, 2, "grouped_matmul_swiglu_quant: x must be int8",
+                                    "grouped_matmul_swiglu_quant: x must be 2D [M, K]");
+        const Tensor w = call.in(weight, I8, 3, 3, "grouped_matmul_swiglu_quant: weight must be int8",
+                                 "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]");
+        const Tensor ws = call.in(weight_scale, F32, 0, -1, "grouped_matmul_swiglu_quant: weight_scale must be float32",
+                                  "grouped_matmul_swiglu_quant: weight_scale must be [E, N]");
+        const Tensor xs = call.in(x_scale, F32, 0, -1, "grouped_matmul_swiglu_quant: x_scale must be float32",
+                                  "grouped_matmul_swiglu_quant: x_scale must have M elements");
+        Out out = shape(rows, w, ws, xs, group_list);
+        const int64_t m = rows.size(0), k = rows.size(1), e = w.size(0), n = w.size(2);
+        if (m == 0 || n == 0 || e == 0) {
+            return out;
+        }
+        call.require(w.size(1) == k, "grouped_matmul_swiglu_quant: K mismatch between x and weight");
+        call.require(xs.numel() == m, "grouped_matmul_swiglu_quant: x_scale must have M elements");
+        call.require(ws.dim() == 2 && ws.size(0) == e && ws.size(1) == n,
+                     "grouped_matmul_swiglu_quant: weight_scale must be [E, N]");
+        const std::vector<int64_t> ends = group_ends(group_list, e, m, "grouped_matmul_swiglu_quant");
+        const size_t bytes = w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e);
+        const Tensor ws_buf = call.scratch(bytes, rows);
+        call.done(w8a8_grouped_matmul_swiglu_quant(Call::as<const int8_t>(rows), Call::as<const int8_t>(w),
+                                                   Call::as<const float>(ws), Call::as<const float>(xs),
+                                                   Call::as<int8_t>(std::get<0>(out)),
+                                                   Call::as<float>(std::get<1>(out)), m, k, n, e, ends.data(), 0,
+                                                   W8A8_W_KN, 0, ws_buf.data_ptr(), bytes, call.stream()));
+        return out;
+    }
+};
+
+// =============================================================== grouped_matmul
+struct GroupedMatmul {
+    using Out = c10::List<Tensor>;
+
+    // split_item 0 / 1: one view of the joined result per expert; 2 / 3: the joined result alone
+    static Out views(const Tensor& joined, const std::vector<int64_t>& ends, int64_t split_item)
+    {
+        Out list;
+        if (split_item >= 2) {
+            list.push_back(joined);
+            return list;
+        }
+        int64_t begin = 0;
+        for (const int64_t end : ends) {
+            list.push_back(joined.narrow(0, begin, end - begin));
+            begin = end;
+        }
+        return list;
+    }
+
+    static Tensor joined(const Tensor& x, const Tensor& weight, bool transpose_weight, const OptTensor& x_scale)
+    {
+        TORCH_CHECK(x.dim() == 2, "grouped_matmul: x must be 2D [M, K]");
+        TORCH_CHECK(weight.dim() == 3, "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]");
+        const int64_t n = weight.size(transpose_weight ? 1 : 2);
+        // the quantised form (this build's extension) always answers in bfloat16
+        return torch::empty({x.size(0), n}, given(x_scale) ? x.options().dtype(torch::kBFloat16) : x.options());
+    }
+
+    static Out shape(const Tensor& x, const Tensor& weight, c10::List<int64_t> group_list, const OptTensor& /*bias*/,
+                     int64_t split_item, bool transpose_weight, const OptTensor& x_scale,
+                     const OptTensor& /*weight_scale*/)
+    {
+        const Tensor y = joined(x, weight, transpose_weight, x_scale);
+        return views(y, group_ends(group_list, weight.size(0), x.size(0), "grouped_matmul"), split_item);
+    }
+
+    static Out run(const Tensor& x, const Tensor& weight, c10::List<int64_t> group_list, const OptTensor& bias,
+                   int64_t split_item, bool transpose_weight, const OptTensor& x_scale, const OptTensor& weight_scale)
+    {
+        Call call("grouped_matmul", x);
+        const char* types = "grouped_matmul: x must be float16, bfloat16, float32 or int8";
+        const Tensor rows = call.in(x, FLOATS | I8, 2, 2, types, "grouped_matmul: x must be 2D [M, K]");
+        const Tensor w = call.in(weight, type_bit(rows), 3, 3, "grouped_matmul: x and weight must share a dtype",
+                                 "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]");
+        const bool quantised = type_bit(rows) == I8;
+        const int64_t m = rows.size(0), k = rows.size(1), e = w.size(0);
+        const int64_t n = w.size(transpose_weight ? 1 : 2);
+        call.require(e >= 1, "grouped_matmul: weight must contain at least one expert");
+        call.require(w.size(transpose_weight ? 2 : 1) == k, "grouped_matmul: K dimension mismatch between x and weight");
+        const std::vector<int64_t> ends = group_ends(group_list, e, m, "grouped_matmul");
+        call.require(quantised == given(x_scale) && quantised == given(weight_scale),
+                     quantised ? "grouped_matmul: int8 inputs need x_scale and weight_scale"
+                               : "grouped_matmul: scales are only valid with int8 inputs");
+        const Tensor xs = call.opt(x_scale, F32, "grouped_matmul: x_scale must be fp32 [M]");
+        const Tensor ws = call.opt(weight_scale, F32, "grouped_matmul: weight_scale must be fp32 [E, N]");
+        call.require(!xs.defined() || xs.numel() == m, "grouped_matmul: x_scale must be fp32 [M]");
+        call.require(!ws.defined() || ws.numel() == e * n, "grouped_matmul: weight_scale must be fp32 [E, N]");
+        const Tensor b = call.opt(bias, FLOATS, "grouped_matmul: bias must be float16, bfloat16 or float32");
+        call.require(!b.defined() || b.numel() == e * n, "grouped_matmul: bias must have shape [E, N]");
+        const Tensor y = joined(rows, w, transpose_weight, x_scale);
+        if (m > 0) {
+            const size_t bytes = w8a8_grouped_matmul_workspace_size(m, n, k, e);
+            const Tensor ws_buf = call.scratch(bytes, rows);
+            call.done(w8a8_grouped_matmul(rows.data_ptr(), w.data_ptr(), Call::ptr(b), y.data_ptr(),
+                                          Call::as<const float>(xs), Call::as<const float>(ws), m, n, k, e,
+                                          ends.data(), 0, abi_type(rows), b.defined() ? abi_type(b) : abi_type(rows),
+                                          abi_type(y), transpose_weight ? W8A8_W_NK : W8A8_W_KN, ws_buf.data_ptr(),
+                                          bytes, call.stream()));
+        }
+        return views(y, ends, split_item);
+    }
+};
+
+// =============================================================== moe_re_routing
+struct MoeReRouting {
+    using Out = std::tuple<Tensor, Tensor, Tensor, Tensor>;
+
+    static Out shape(const Tensor& tokens, const Tensor& counts, const OptTensor& /*scales*/,
+                     int64_t /*expert_token_num_type*/, int64_t /*idx_type*/)
+    {
+        TORCH_CHECK(tokens.dim() == 2, "moe_re_routing: tokens must be 2D (A, H).");
+        TORCH_CHECK(counts.dim() == 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
+        const int64_t a = tokens.size(0);
+        const auto like = tokens.options();
+        return {torch::empty({a, tokens.size(1)}, like), torch::empty({a}, like.dtype(torch::kFloat)),
+                torch::empty({a}, like.dtype(torch::kInt)), torch::empty({counts.size(1)}, counts.options())};
+    }
+
+    static Out run(const Tensor& tokens, const Tensor& counts, const OptTensor& scales, int64_t num_type,
+                   int64_t idx_type)
+    {
+        TORCH_CHECK(idx_type == 0, "moe_re_routing: only gather index mode (idx_type == 0) is supported.");
+        Call call("moe_re_routing", tokens);
+        Out out = shape(tokens, counts, scales, num_type, idx_type);
+        if (tokens.numel() == 0 || counts.numel() == 0) {
+            return out;
+        }
+        const Tensor tok = call.in(tokens, HALVES | I8, 2, 2, "moe_re_routing: unsupported tokens dtype.",
+                                   "moe_re_routing: tokens must be 2D (A, H).");
+        const Tensor cnt = call.in(counts, I32 | I64, 2, 2, "moe_re_routing: unsupported expert_token_num_per_rank dtype.",
+                                   "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
+        call.require(cnt.is_cuda(), "moe_re_routing: expert_token_num_per_rank must be on the tokens' device.");
+        const Tensor scl = call.opt(scales, F32, "moe_re_routing: per_token_scales must be float32.");
+        call.require(!scl.defined() || scl.numel() == tok.size(0), "moe_re_routing: per_token_scales must have A elements.");
+        const int64_t a = tok.size(0), ranks = cnt.size(0), experts = cnt.size(1);
+        const size_t bytes = w8a8_moe_re_routing_workspace_size(a, ranks, experts);
+        const Tensor ws_buf = call.scratch(bytes, tok);
+        call.done(w8a8_moe_re_routing(tok.data_ptr(), cnt.data_ptr(), Call::as<const float>(scl),
+                                      std::get<0>(out).data_ptr(), Call::as<float>(std::get<1>(out)),
+                                      Call::as<int32_t>(std::get<2>(out)), std::get<3>(out).data_ptr(), a,
+                                      tok.size(1) * static_cast<int64_t>(tok.element_size()), ranks, experts,
+                                      static_cast<int>(cnt.element_size()), ws_buf.data_ptr(), bytes, call.stream()));
+        return out;
+    }
+};
+
+// ========================================================= moe_finalize_routing
+struct MoeFinalizeRouting {
+    struct Dims {
+        int64_t tokens, topk, hidden;
+    };
+
+    static Dims dims(const Tensor& rows, const Tensor& src_to_dst, const OptTensor& scales)
+    {
+        TORCH_CHECK(rows.dim() >= 2, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
+        TORCH_CHECK(src_to_dst.scalar_type() == torch::kInt,
+                    "moe_finalize_routing: expanded_src_to_dst_row must be int32.");
+        TORCH_CHECK(!given(scales) || scales->dim() == 2, "moe_finalize_routing: scales must be 2-D (NUM_ROWS, K).");
+        const int64_t topk = given(scales) ? scales->size(1) : 1;
+        TORCH_CHECK(topk > 0, "moe_finalize_routing: K must be positive.");
+        TORCH_CHECK(src_to_dst.numel() % topk == 0,
+                    "moe_finalize_routing: expanded_src_to_dst_row length must be K*NUM_ROWS.");
+        return {src_to_dst.numel() / topk, topk, rows.size(-1)};
+    }
+
+    static Tensor shape(const Tensor& rows, const Tensor& src_to_dst, OptTensor /*skip1*/, OptTensor /*skip2*/,
+                        OptTensor /*bias*/, OptTensor scales, OptTensor /*expert*/, int64_t /*drop_pad_mode*/)
+    {
+        const Dims d = dims(rows, src_to_dst, scales);
+        return torch::empty({d.tokens, d.hidden}, rows.options());
+    }
+
+    static Tensor run(const Tensor& rows, const Tensor& src_to_dst, OptTensor skip1, OptTensor skip2, OptTensor bias,
+                      OptTensor scales, OptTensor expert, int64_t drop_pad_mode)
+    {
+        TORCH_CHECK((type_bit(rows) & FLOATS) != 0u,
+                    "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.");
+        Call call("moe_finalize_routing", rows);
+        const Dims d = dims(rows, src_to_dst, scales);
+        Tensor out = torch::empty({d.tokens, d.hidden}, rows.options());
+        if (d.tokens <= 0 || d.hidden <= 0) {
+            return out;
+        }
+        const unsigned row_type = type_bit(rows);
+        const Tensor epr = call.in(rows, FLOATS, 2, -1, "moe_finalize_routing: unsupported rows dtype.",
+                                   "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
+        const Tensor map = call.in(src_to_dst, I32, 0, -1, "moe_finalize_routing: expanded_src_to_dst_row must be int32.",
+                                   "moe_finalize_routing: expanded_src_to_dst_row must be int32.");
+        const Tensor s1 = call.opt(skip1, row_type, "moe_finalize_routing: skip1 must have the rows' dtype.");
+        const Tensor s2 = call.opt(skip2, row_type, "moe_finalize_routing: skip2 must have the rows' dtype.");
+        const Tensor sc = call.opt(scales, FLOATS,
+                                   "moe_finalize_routing: unsupported dtype combination for expanded_permuted_rows / scales.");
+        // the bias rows are selected by expert id: without the ids the bias is not applied
+        Tensor bs, ex;
+        if (given(bias) && given(expert)) {
+            bs = call.opt(bias, row_type, "moe_finalize_routing: bias must have the rows' dtype.");
+            ex = call.opt(expert, I32, "moe_finalize_routing: expert_for_source_row must be int32.");
+            call.require(bs.dim() == 2 && bs.size(1) == d.hidden, "moe_finalize_routing: bias head dim must equal H.");
+        }
+        const int mode = static_cast<int>(std::min<int64_t>(3, std::max<int64_t>(0, drop_pad_mode)));
+        call.done(w8a8_moe_finalize_routing(epr.data_ptr(), Call::as<const int32_t>(map), Call::ptr(s1), Call::ptr(s2),
+                                            Call::ptr(bs), Call::ptr(sc), Call::as<const int32_t>(ex), out.data_ptr(),
+                                            d.tokens, d.hidden, d.topk, bs.defined() ? bs.size(0) : 0,
+                                            epr.numel() / d.hidden, mode, abi_type(epr),
+                                            sc.defined() ? abi_type(sc) : abi_type(epr), call.stream()));
+        return out;
+    }
+};
+
+// ===================================================== moe_gating_top_k_softmax
+struct MoeGatingTopKSoftmax {
+    using Out = std::tuple<Tensor, Tensor, Tensor>;
+
+    static Out shape(const Tensor& x, const OptTensor& finished, int64_t k)
+    {
+        TORCH_CHECK((type_bit(x) & FLOATS) != 0u,
+                    "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.");
+        TORCH_CHECK(x.dim() >= 2, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.");
+        TORCH_CHECK(x.size(-1) > 0, "cann_bench.moe_gating_top_k_softmax requires a non-empty last dimension.");
+        TORCH_CHECK(k > 0 && k <= x.size(-1), "cann_bench.moe_gating_top_k_softmax requires 0 < k <= x.size(-1).");
+        TORCH_CHECK(!given(finished) || finished->scalar_type() == torch::kBool,
                     "cann_bench.moe_gating_top_k_softmax requires a bool 'finished' tensor.");
+        std::vector<int64_t> dims = all_but_last(x);
+        dims.push_back(k);
+        const auto ints = x.options().dtype(torch::kInt);
+        return {torch::empty(dims, x.options()), torch::empty(dims, ints), torch::empty(dims, ints)};
     }
-    std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end() - 1);
-    shape.push_back(k);
-    return std::make_tuple(torch::empty(shape, x.options()), torch::empty(shape, x.options().dtype(torch::kInt)),
-                           torch::empty(shape, x.options().dtype(torch::kInt)));
-}
 
-static GateOut gating_cuda(const torch::Tensor& x, const c10::optional<torch::Tensor>& finished, int64_t k)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x.device());
-    auto xc = x.contiguous();
-    auto outs = gating_meta(xc, finished, k);
-    const int64_t inner = xc.size(-1);
-    const int64_t rows = xc.numel() / inner;
-    TORCH_CHECK(rows > 0, "cann_bench.moe_gating_top_k_softmax requires at least one row.");
-    torch::Tensor fin;
-    if (present(finished)) {
-        fin = finished->contiguous();
-        TORCH_CHECK(fin.numel() == rows, "cann_bench.moe_gating_top_k_softmax: finished must have numel == rows.");
+    static Out run(const Tensor& x, const OptTensor& finished, int64_t k)
+    {
+        Call call("moe_gating_top_k_softmax", x);
+        Out out = shape(x, finished, k);
+        const Tensor logits = call.in(x, FLOATS, 2, -1, "unsupported dtype", "rank");
+        const int64_t experts = logits.size(-1), rows = logits.numel() / experts;
+        call.require(rows > 0, "cann_bench.moe_gating_top_k_softmax requires at least one row.");
+        const Tensor fin = call.opt(finished, BOOL, "cann_bench.moe_gating_top_k_softmax requires a bool 'finished' tensor.");
+        call.require(!fin.defined() || fin.numel() == rows,
+                     "cann_bench.moe_gating_top_k_softmax: finished must have numel == rows.");
+        call.done(w8a8_moe_gating_top_k_softmax(logits.data_ptr(), Call::as<const uint8_t>(fin),
+                                                std::get<0>(out).data_ptr(), Call::as<int32_t>(std::get<1>(out)),
+                                                Call::as<int32_t>(std::get<2>(out)), rows, experts, k,
+                                                abi_type(logits), call.stream()));
+        return out;
     }
-    check_status(w8a8_moe_gating_top_k_softmax(xc.data_ptr(),
-                                               fin.defined() ? static_cast<const uint8_t*>(fin.data_ptr()) : nullptr,
-                                               std::get<0>(outs).data_ptr(),
-                                               static_cast<int32_t*>(std::get<1>(outs).data_ptr()),
-                                               static_cast<int32_t*>(std::get<2>(outs).data_ptr()), rows, inner, k,
-                                               dtype_code(xc), stream_of(xc)),
-                 "moe_gating_top_k_softmax");
-    return outs;
-}
+};
 
-// ---------------------------------------------------------- dequant_swiglu_quant
-static std::tuple<torch::Tensor, torch::Tensor> dqsq_meta(const torch::Tensor& x,
-                                                          const c10::optional<torch::Tensor>& weight_scale,
-                                                          const c10::optional<torch::Tensor>& activation_scale,
-                                                          const c10::optional<torch::Tensor>& quant_scale,
-                                                          bool activate_left)
-{
-    (void)weight_scale;
-    (void)activation_scale;
-    (void)quant_scale;
-    (void)activate_left;
-    TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
-    TORCH_CHECK(x.size(1) % 2 == 0, "dequant_swiglu_quant requires an even last dimension.");
-    return std::make_tuple(torch::empty({x.size(0), x.size(1) / 2}, x.options().dtype(torch::kChar)),
-                           torch::empty({x.size(0)}, x.options().dtype(torch::kFloat)));
-}
+// ========================================================= dequant_swiglu_quant
+struct DequantSwigluQuant {
+    using Out = std::tuple<Tensor, Tensor>;
 
-static std::tuple<torch::Tensor, torch::Tensor> dqsq_cuda(const torch::Tensor& x,
-                                                          const c10::optional<torch::Tensor>& weight_scale,
-                                                          const c10::optional<torch::Tensor>& activation_scale,
-                                                          const c10::optional<torch::Tensor>& quant_scale,
-                                                          bool activate_left)
-{
-    const c10::cuda::OptionalCUDAGuard guard(x.device());
-    TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
-    TORCH_CHECK(x.is_contiguous(), "dequant_swiglu_quant requires a contiguous input.");
-    auto outs = dqsq_meta(x, weight_scale, activation_scale, quant_scale, activate_left);
-    const int64_t M = x.size(0), N2 = x.size(1);
-    if (M <= 0 || N2 <= 0) {
-        return outs;
+    static Out shape(const Tensor& x, const OptTensor& /*weight_scale*/, const OptTensor& /*activation_scale*/,
+                     const OptTensor& /*quant_scale*/, bool /*activate_left*/)
+    {
+        TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
+        TORCH_CHECK(x.size(1) % 2 == 0, "dequant_swiglu_quant requires an even last dimension.");
+        return {torch::empty({x.size(0), x.size(1) / 2}, x.options().dtype(torch::kChar)),
+                torch::empty({x.size(0)}, x.options().dtype(torch::kFloat))};
     }
-    const int64_t H = N2 / 2;
-    const auto xt = x.scalar_type();
-    const bool is_i32 = (xt == torch::kInt);
-    if (is_i32) {
-        TORCH_CHECK(present(weight_scale), "weight_scale is required when x is int32.");
-        TORCH_CHECK(present(activation_scale), "activation_scale is required when x is int32.");
-        TORCH_CHECK(weight_scale->scalar_type() == torch::kFloat, "weight_scale must be float32.");
-        TORCH_CHECK(activation_scale->scalar_type() == torch::kFloat, "activation_scale must be float32.");
-        TORCH_CHECK(weight_scale->is_contiguous() && activation_scale->is_contiguous(),
-                    "weight_scale / activation_scale must be contiguous.");
-        TORCH_CHECK(weight_scale->numel() == N2, "weight_scale must have 2H elements.");
-        TORCH_CHECK(activation_scale->numel() == M, "activation_scale must have TokensNum elements.");
-    } else {
-        TORCH_CHECK(xt == torch::kFloat16 || xt == torch::kBFloat16,
-                    "dequant_swiglu_quant supports int32 / float16 / bfloat16 inputs.");
-        TORCH_CHECK(!present(weight_scale), "weight_scale must be None for float16 / bfloat16 inputs.");
-        TORCH_CHECK(!present(activation_scale), "activation_scale must be None for float16 / bfloat16 inputs.");
+
+    static Out run(const Tensor& x, const OptTensor& weight_scale, const OptTensor& activation_scale,
+                   const OptTensor& quant_scale, bool activate_left)
+    {
+        Call call("dequant_swiglu_quant", x);
+        Out out = shape(x, weight_scale, activation_scale, quant_scale, activate_left);
+        const int64_t tokens = x.size(0), half = x.size(1) / 2;
+        if (x.numel() == 0) {
+            return out;
+        }
+        const Tensor acc = call.in(x, I32 | HALVES, 2, 2, "dequant_swiglu_quant supports int32 / float16 / bfloat16 inputs.",
+                                   "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].", /*dense=*/false);
+        const bool integer = type_bit(acc) == I32;
+        // an int32 accumulator needs both dequantisation scales; a float input must come without them
+        call.require(integer == given(weight_scale), integer ? "weight_scale is required when x is int32."
+                                                             : "weight_scale must be None for float16 / bfloat16 inputs.");
+        call.require(integer == given(activation_scale),
+                     integer ? "activation_scale is required when x is int32."
+                             : "activation_scale must be None for float16 / bfloat16 inputs.");
+        const struct {
+            const OptTensor* arg;
+            int64_t count;
+            const char* type_msg;
+            const char* size_msg;
+        } vectors[] = {
+            {&weight_scale, 2 * half, "weight_scale must be float32.", "weight_scale must have 2H elements."},
+            {&activation_scale, tokens, "activation_scale must be float32.", "activation_scale must have TokensNum elements."},
+            {&quant_scale, half, "quant_scale must be float32.", "quant_scale must have H elements."},
+        };
+        Tensor dense[3];
+        for (int i = 0; i < 3; ++i) {
+            dense[i] = call.opt(*vectors[i].arg, F32, vectors[i].type_msg, /*dense=*/false);
+            call.require(!dense[i].defined() || dense[i].numel() == vectors[i].count, vectors[i].size_msg);
+        }
+        call.done(w8a8_dequant_swiglu_quant(acc.data_ptr(), Call::as<const float>(dense[0]),
+                                            Call::as<const float>(dense[1]), Call::as<const float>(dense[2]),
+                                            Call::as<int8_t>(std::get<0>(out)), Call::as<float>(std::get<1>(out)),
+                                            tokens, half, integer ? W8A8_DT_I32 : abi_type(acc), activate_left ? 1 : 0,
+                                            0, call.stream()));
+        return out;
     }
-    const bool has_q = present(quant_scale);
-    if (has_q) {
-        TORCH_CHECK(quant_scale->scalar_type() == torch::kFloat, "quant_scale must be float32.");
-        TORCH_CHECK(quant_scale->is_contiguous(), "quant_scale must be contiguous.");
-        TORCH_CHECK(quant_scale->numel() == H, "quant_scale must have H elements.");
-    }
-    const int code = is_i32 ? W8A8_DT_I32 : dtype_code(x);
-    check_status(w8a8_dequant_swiglu_quant(x.data_ptr(),
-                                           is_i32 ? static_cast<const float*>(weight_scale->data_ptr()) : nullptr,
-                                           is_i32 ? static_cast<const float*>(activation_scale->data_ptr()) : nullptr,
-                                           has_q ? static_cast<const float*>(quant_scale->data_ptr()) : nullptr,
-                                           static_cast<int8_t*>(std::get<0>(outs).data_ptr()),
-                                           static_cast<float*>(std::get<1>(outs).data_ptr()), M, H, code,
-                                           activate_left ? 1 : 0, 0, stream_of(x)),
-                 "dequant_swiglu_quant");
-    return outs;
-}
+};
+
+}  // namespace
 
 TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 {
@@ -699,28 +679,28 @@ TORCH_LIBRARY_FRAGMENT(cann_bench, m)
 
 TORCH_LIBRARY_IMPL(cann_bench, Meta, m)
 {
-    m.impl("dynamic_quant", dynamic_quant_meta);
-    m.impl("add_rms_norm_dynamic_quant", ardq_meta);
-    m.impl("quant_matmul", quant_matmul_meta);
-    m.impl("grouped_matmul_swiglu_quant", gmsq_meta);
-    m.impl("grouped_matmul", grouped_matmul_meta);
-    m.impl("moe_re_routing", moe_re_routing_meta);
-    m.impl("moe_finalize_routing", mfr_meta);
-    m.impl("moe_gating_top_k_softmax", gating_meta);
-    m.impl("dequant_swiglu_quant", dqsq_meta);
+    m.impl("dynamic_quant", DynamicQuant::shape);
+    m.impl("add_rms_norm_dynamic_quant", AddRmsNormDynamicQuant::shape);
+    m.impl("quant_matmul", QuantMatmul::shape);
+    m.impl("grouped_matmul_swiglu_quant", GroupedMatmulSwigluQuant::shape);
+    m.impl("grouped_matmul", GroupedMatmul::shape);
+    m.impl("moe_re_routing", MoeReRouting::shape);
+    m.impl("moe_finalize_routing", MoeFinalizeRouting::shape);
+    m.impl("moe_gating_top_k_softmax", MoeGatingTopKSoftmax::shape);
+    m.impl("dequant_swiglu_quant", DequantSwigluQuant::shape);
 }
 
 TORCH_LIBRARY_IMPL(cann_bench, CUDA, m)
 {
-    m.impl("dynamic_quant", dynamic_quant_cuda);
-    m.impl("add_rms_norm_dynamic_quant", ardq_cuda);
-    m.impl("quant_matmul", quant_matmul_cuda);
-    m.impl("grouped_matmul_swiglu_quant", gmsq_cuda);
-    m.impl("grouped_matmul", grouped_matmul_cuda);
-    m.impl("moe_re_routing", moe_re_routing_cuda);
-    m.impl("moe_finalize_routing", mfr_cuda);
-    m.impl("moe_gating_top_k_softmax", gating_cuda);
-    m.impl("dequant_swiglu_quant", dqsq_cuda);
+    m.impl("dynamic_quant", DynamicQuant::run);
+    m.impl("add_rms_norm_dynamic_quant", AddRmsNormDynamicQuant::run);
+    m.impl("quant_matmul", QuantMatmul::run);
+    m.impl("grouped_matmul_swiglu_quant", GroupedMatmulSwigluQuant::run);
+    m.impl("grouped_matmul", GroupedMatmul::run);
+    m.impl("moe_re_routing", MoeReRouting::run);
+    m.impl("moe_finalize_routing", MoeFinalizeRouting::run);
+    m.impl("moe_gating_top_k_softmax", MoeGatingTopKSoftmax::run);
+    m.impl("dequant_swiglu_quant", DequantSwigluQuant::run);
 }
 
 }  // namespace cann_bench

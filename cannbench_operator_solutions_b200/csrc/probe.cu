@@ -21,18 +21,18 @@ constexpr int PROBE_STAGES = 4;
 constexpr int PROBE_A_BYTES = 16384;                       // 128 rows x 128 bytes of K
 constexpr int PROBE_B_BYTES = 32768;                       // up to 256 columns x 128 bytes of K
 constexpr int PROBE_STAGE_BYTES = PROBE_A_BYTES + PROBE_B_BYTES;
-constexpr int PROBE_DEPTH = 4;                             // batches in flight
-constexpr int PROBE_KSTEPS = 4;                            // MMAs per batch: 128 bytes of K in steps of 32
+constexpr int PROBE_MAX_DEPTH = 8;                         // most batches in flight
+constexpr int PROBE_KSTEPS = 4;                            // K steps of 32 bytes one stage holds
 
 template <int CG>
 __global__ void __launch_bounds__(PROBE_THREADS, 1)
-    mma_issue_probe_kernel(uint32_t idesc, int a_mn, int b_mn, int fill, int accumulators, long long batches,
-                           int32_t* error)
+    mma_issue_probe_kernel(uint32_t idesc, int a_mn, int b_mn, int fill, int accumulators, int per_commit, int depth,
+                           long long batches, int32_t* error)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PROBE_STAGES * PROBE_STAGE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PROBE_DEPTH);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PROBE_MAX_DEPTH);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5;
     const uint32_t cta_rank = (CG == 2) ? tc::cluster_ctarank() : 0u;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         }
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PROBE_DEPTH; ++i) {
+        for (int i = 0; i < PROBE_MAX_DEPTH; ++i) {
             tc::mbar_init(tc::smem_u32(bars + i), 1);
         }
         *abort_flag = 0;
@@ -87,43 +87,61 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         const uint32_t a_kstep = a_mn ? ((32 * 128) >> 4) : (32 >> 4);
         const uint32_t b_kstep = b_mn ? ((32 * 128) >> 4) : (32 >> 4);
         const uint32_t bar0 = tc::smem_u32(bars);
+        // Everything the loop needs is precomputed and every counter is a 32-bit increment: this thread's own
+        // instructions are part of what is measured, and a single thread retires one every few clocks.
+        // one accumulator: every instruction adds to the result of the one before it (alternating between two
+        // accumulator stages per batch, as a matmul's successive tiles do); several: successive instructions add
+        // to different accumulators, so none waits for its predecessor's result
+        const uint32_t acc_stride = 512u / static_cast<uint32_t>(accumulators);
+        uint32_t d_of_k[PROBE_KSTEPS];
+#pragma unroll
+        for (int k = 0; k < PROBE_KSTEPS; ++k) {
+            d_of_k[k] = tmem_base + static_cast<uint32_t>(k % accumulators) * acc_stride;
+        }
+        const uint32_t groups = static_cast<uint32_t>(per_commit / PROBE_KSTEPS);
+        constexpr uint32_t STAGE_STEP = PROBE_STAGE_BYTES >> 4;
         bool ok = true;
+        uint32_t slot = 0, round = 0, stage = 0;
         for (long long b = 0; ok && b < batches; ++b) {
-            const int slot = static_cast<int>(b % PROBE_DEPTH);
-            if (b >= PROBE_DEPTH) {
-                const uint32_t parity = static_cast<uint32_t>((b / PROBE_DEPTH - 1) & 1);
-                if (!tc::mbar_wait(bar0 + 8u * slot, parity, abort_flag)) {
+            if (round != 0) {
+                if (!tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
             }
-            const int stage = static_cast<int>(b % PROBE_STAGES);
-            // one accumulator: every MMA adds to the result of the one before it (alternating between two
-            // accumulator stages per batch, as a matmul's successive tiles do); several: successive MMAs add to
-            // different accumulators, so none waits for its predecessor's result
-            const uint32_t acc_stride = 512u / static_cast<uint32_t>(accumulators);
-            const uint32_t d_single = tmem_base + static_cast<uint32_t>((b & 1) * 256);
-            const uint32_t a_lo = a_lo0 + stage * (PROBE_STAGE_BYTES >> 4);
-            const uint32_t b_lo = b_lo0 + stage * (PROBE_STAGE_BYTES >> 4);
+            const uint32_t d_flip = (accumulators == 1) ? static_cast<uint32_t>(b & 1) * 256u : 0u;
+#pragma unroll 1
+            for (uint32_t g = 0; g < groups; ++g) {
+                const uint32_t a_lo = a_lo0 + stage * STAGE_STEP;
+                const uint32_t b_lo = b_lo0 + stage * STAGE_STEP;
 #pragma unroll
-            for (int k = 0; k < PROBE_KSTEPS; ++k) {
-                const uint32_t d_tmem =
-                    (accumulators == 1) ? d_single : tmem_base + static_cast<uint32_t>(k % accumulators) * acc_stride;
-                tc::mma_lohi<CG, true>(d_tmem, a_lo + k * a_kstep, a_hi, b_lo + k * b_kstep, b_hi, idesc, 1u);
+                for (int k = 0; k < PROBE_KSTEPS; ++k) {
+                    tc::mma_lohi<CG, true>(d_of_k[k] + d_flip, a_lo + k * a_kstep, a_hi, b_lo + k * b_kstep, b_hi,
+                                           idesc, 1u);
+                }
+                stage = (stage + 1u) & (PROBE_STAGES - 1);
             }
             if constexpr (CG == 2) {
                 tc::tc_commit_pair(bar0 + 8u * slot);
             } else {
                 tc::tc_commit(bar0 + 8u * slot);
             }
+            if (++slot == static_cast<uint32_t>(depth)) {
+                slot = 0;
+                ++round;
+            }
         }
-        // drain: the last min(batches, DEPTH) commits
-        const long long first = batches > PROBE_DEPTH ? batches - PROBE_DEPTH : 0;
-        for (long long b = first; ok && b < batches; ++b) {
-            const int slot = static_cast<int>(b % PROBE_DEPTH);
-            const uint32_t parity = static_cast<uint32_t>((b / PROBE_DEPTH) & 1);
-            if (!tc::mbar_wait(bar0 + 8u * slot, parity, abort_flag)) {
-                ok = false;
+        // drain: every slot's last commit
+        if (ok) {
+            const long long last_round_batches = batches - static_cast<long long>(round) * depth;  // in slots [0, that)
+            for (uint32_t sl = 0; ok && sl < static_cast<uint32_t>(depth); ++sl) {
+                long long completions = static_cast<long long>(round) + (static_cast<long long>(sl) < last_round_batches ? 1 : 0);
+                if (completions == 0) {
+                    continue;
+                }
+                if (!tc::mbar_wait(bar0 + 8u * sl, static_cast<uint32_t>((completions - 1) & 1), abort_flag)) {
+                    ok = false;
+                }
             }
         }
         if (!ok && error != nullptr) {
@@ -171,8 +189,13 @@ __global__ void bounded_wait_selftest_kernel(long long limit_cycles, int32_t* er
 using namespace w8a8;
 
 extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
-                                    int accumulators, int64_t batches, int32_t* error_word, void* stream)
+                                    int accumulators, int per_commit, int depth, int64_t batches, int32_t* error_word,
+                                    void* stream)
 {
+    if (per_commit < PROBE_KSTEPS || per_commit > 256 || (per_commit % PROBE_KSTEPS) != 0 || depth < 1 ||
+        depth > PROBE_MAX_DEPTH) {
+        return W8A8_ERR_INVALID;
+    }
     if (batches <= 0 || batches > (int64_t(1) << 24)) {
         return W8A8_ERR_INVALID;
     }
@@ -219,7 +242,7 @@ extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<2>, idesc, a_mn_major, b_mn_major, fill,
-                               accumulators, static_cast<long long>(batches), error_word);
+                               accumulators, per_commit, depth, static_cast<long long>(batches), error_word);
     } else {
         e = cudaFuncSetAttribute(mma_issue_probe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
@@ -228,16 +251,16 @@ extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a
         }
         cfg.gridDim = dim3(static_cast<unsigned>(sms), 1, 1);
         e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<1>, idesc, a_mn_major, b_mn_major, fill,
-                               accumulators, static_cast<long long>(batches), error_word);
+                               accumulators, per_commit, depth, static_cast<long long>(batches), error_word);
     }
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
-extern "C" int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int64_t batches)
+extern "C" int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int per_commit, int64_t batches)
 {
     // integer operations (multiply and add counted separately) one probe launch issues on this device
     const int64_t groups = (cta_group == 2) ? sm_count() / 2 : sm_count();
-    return groups * batches * PROBE_KSTEPS * 2 * umma_m * umma_n * 32;
+    return groups * batches * per_commit * 2 * umma_m * umma_n * 32;
 }
 
 extern "C" int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream)

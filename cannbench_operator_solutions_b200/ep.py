@@ -448,9 +448,11 @@ class MoeFfnChain:
         return out, x_out
 
     def check(self) -> None:
-        """Device-table mode: raises if a step routed more rows to a rank than its buffers hold (reads one flag from
-        the device, so call it when a synchronisation is acceptable)."""
+        """Device-table mode: raises if any step since the last check routed more rows to a rank than its buffers
+        hold (the flag is sticky on the device and cleared here; reading it synchronises, so call it when that is
+        acceptable)."""
         if self._dev_state is not None and int(self._dev_state["status"][0].item()) != 0:
+            self._dev_state["status"].zero_()
             raise RuntimeError("expert-parallel receive buffer too small for this routing: raise capacity_rows")
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,

@@ -192,8 +192,16 @@ int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w, const flo
  * one stream are fine; two calls whose kernels can overlap on the GPU (different
  * streams without an ordering between them, or several host threads) race on it
  * and give wrong results.  Use the workspace variant for concurrent calls.
+ *
+ * With a device group list (list_on_device 1 or 2) the list is validated on the
+ * GPU and a bad list is reported through an error word, as in the workspace
+ * variant; here that word sits in the built-in scratch, so read it with
+ * w8a8_static_scratch_error(stream) (synchronises the stream; 0 = none,
+ * 1 = invalid device group list and y left untouched, 2 = a pipeline wait ran
+ * out).  Host group lists are validated before anything is launched.
  */
 #define W8A8_STATIC_SCRATCH_BYTES ((8 << 20) + (64 << 10))
+int w8a8_static_scratch_error(void* stream);
 int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const int8_t* w, const float* w_scale,
                                             const float* x_scale, int8_t* y, float* y_scale, int64_t M,
                                             int64_t K, int64_t N, int64_t E, const int64_t* group_list,
@@ -217,10 +225,24 @@ int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y,
                         int bias_dtype, int out_dtype, int w_layout, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/*
+ * Test and tuning hook (no reference counterpart): forces the tensor-core kernel shape for every later matmul
+ * call of the process.  0 = the library's own choice (the default), 1 = one CTA per 128-row tile, 2 = CTA pairs
+ * (cta_group::2) on 256-row tiles, 3 = grouped problems as pairs on whole 256-row blocks plus single CTAs on the
+ * leftovers (dense problems ignore 3).  Every shape gives identical results.  Returns the previous setting, or
+ * W8A8_ERR_INVALID.
+ */
+int w8a8_set_gemm_shape(int shape);
+
 /* Reads (synchronously, on `stream`) the device-side error word a grouped
  * call left in its workspace: 0 = none, 1 = invalid device group list,
  * 2 = a pipeline wait ran out. */
 int w8a8_workspace_error(const void* workspace, void* stream);
+
+/* The same report for the matmuls that take no workspace (w8a8_quant_matmul, w8a8_matmul_i8_i32): reads
+ * (synchronously, on `stream`) and clears the current device's error word, 0 = none, 2 = a pipeline wait ran out
+ * since the last read (the output of that call is incomplete). */
+int w8a8_pipeline_error(void* stream);
 
 /*
  * Expert-parallel helpers (the layout contract of MoeReRouting and the
@@ -289,8 +311,8 @@ int w8a8_dispatch_rows(const void* src, const float* src_scale, const int32_t* e
  * off_back the byte offsets of the int8 rows, the fp32 scales and the 16-bit return rows inside each buffer.
  * Outputs: row_dst[E], scale_dst[E], my_base[E] for w8a8_dispatch_rows; group_list[E / P] (cumulative rows of this
  * rank's experts, a device list for the grouped matmuls with list_on_device = 2); seg_first[(E / P) * P + 1] and
- * seg_ptr[(E / P) * P] for w8a8_expand_row_pointers; status[0] = 1 when some rank would receive more than cap_rows
- * rows.  P <= 64, E <= 1024, P * E <= 2048 (W8A8_ERR_LIMIT beyond).  No reference counterpart.
+ * seg_ptr[(E / P) * P] for w8a8_expand_row_pointers; status[0] is set to 1 when some rank would receive more than
+ * cap_rows rows (sticky: this call never clears it, the caller does after reading it).  P <= 64, E <= 1024, P * E <= 2048 (W8A8_ERR_LIMIT beyond).  No reference counterpart.
  */
 int w8a8_ep_tables(const int64_t* counts, int64_t P, int64_t E, int64_t rank, const uint64_t* peer_base,
                    uint64_t off_x, uint64_t off_s, uint64_t off_back, int64_t row_bytes, int64_t back_row_bytes,
@@ -374,7 +396,8 @@ int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const fl
  * library.)
  *
  * w8a8_mma_issue_probe: every SM (cta_group 1) or SM pair (cta_group 2) issues
- * `batches` x 4 tcgen05.mma kind::i8 instructions of shape umma_m x umma_n x 32
+ * `batches` x per_commit tcgen05.mma kind::i8 instructions (one tcgen05.commit
+ * per batch, per_commit a multiple of 4 up to 256, at most `depth` <= 8 batches in flight) of shape umma_m x umma_n x 32
  * on operands resident in shared memory (fill 0 = zeros, 1 = pseudo-random
  * bytes), with no loads and no epilogue: timed with CUDA events it gives the
  * rate the tensor pipe sustains for that shape, the ceiling the matmul kernels
@@ -395,8 +418,9 @@ int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const fl
  * device memory.
  */
 int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
-                         int accumulators, int64_t batches, int32_t* error_word, void* stream);
-int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int64_t batches);
+                         int accumulators, int per_commit, int depth, int64_t batches, int32_t* error_word,
+                         void* stream);
+int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int per_commit, int64_t batches);
 int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream);
 
 #ifdef __cplusplus

@@ -147,6 +147,149 @@ def gmm_i8(x, w, ws, xs, gl, bias):
     return out
 
 
+# ---------------------------------------------------------------------------
+# The four operators either side of the path.  exp is the project's fixed
+# fp32 exp (range reduction by ln2 in two pieces, degree-5 polynomial, two-step
+# scaling); here it is restated with each fused multiply-add evaluated in
+# float64 and rounded once to float32 (a 24 x 24 bit product is exact in
+# float64, and the sum is then rounded to 53 bits before the final rounding: a
+# double rounding that could only show on a near-tie of the 53-bit sum).
+# ---------------------------------------------------------------------------
+def fma32(a, b, c):
+    return (np.asarray(a, F).astype(np.float64) * np.asarray(b, F).astype(np.float64)
+            + np.asarray(c, F).astype(np.float64)).astype(F)
+
+
+def canon_exp(x):
+    x = np.asarray(x, F)
+    nan = np.isnan(x)
+    t = np.clip(np.where(nan, F(0), x), F(-104.0), F(89.0)).astype(F)
+    n = np.rint((t * F(1.44269504088896341)).astype(F)).astype(F)
+    r = fma32(n, F(-0.693359375), t)
+    r = fma32(n, F(2.12194440e-4), r)
+    p = np.full_like(r, F(1.9875691500e-4))
+    for c in (1.3981999507e-3, 8.3334519073e-3, 4.1665795894e-2, 1.6666665459e-1, 5.0000001201e-1):
+        p = fma32(p, r, F(c))
+    e = (fma32(p, (r * r).astype(F), r) + F(1.0)).astype(F)
+    ni = n.astype(np.int64)
+    n1 = ni >> 1
+    n2 = ni - n1
+    s1 = ((n1 + 127).astype(np.uint32) << np.uint32(23)).view(F)
+    s2 = ((n2 + 127).astype(np.uint32) << np.uint32(23)).view(F)
+    out = ((e * s1).astype(F) * s2).astype(F)
+    return np.where(nan, x, out).astype(F)
+
+
+def mrr(tokens, counts, scales):
+    """Rank-major / expert-minor rows -> expert-major rows (the layout after an expert-parallel all-to-all)."""
+    n, e = counts.shape
+    a = tokens.shape[0]
+    # source order: for rank i, for expert j; destination order: for expert j, for rank i
+    src_start = np.zeros((n, e), np.int64)
+    run = 0
+    for i in range(n):
+        for j in range(e):
+            src_start[i, j] = run
+            run += counts[i, j]
+    out = np.zeros_like(tokens)
+    out_s = np.zeros((a,), F)
+    idx = np.zeros((a,), np.int32)
+    d = 0
+    for j in range(e):
+        for i in range(n):
+            c = int(counts[i, j])
+            s = int(src_start[i, j])
+            out[d:d + c] = tokens[s:s + c]
+            if scales is not None:
+                out_s[d:d + c] = scales[s:s + c]
+            idx[d:d + c] = np.arange(s, s + c)
+            d += c
+    return out, out_s, idx, counts.sum(axis=0).astype(np.int64)
+
+
+def mfr(rows_b, kind, esdr, skip1_b, skip2_b, bias_b, scales, expert, mode):
+    """out[i] = skip1[i] + skip2[i] + sum_k (rows[p(i,k)] + bias[expert[i,k]]) * scales[i,k], fp32, ascending k."""
+    conv = (lambda b: b.astype(F)) if kind == "f32" else (lambda b: from_bits(b, kind))
+    rows = conv(rows_b)
+    num_dst, h = rows.shape
+    kk = 1 if scales is None else scales.shape[1]
+    r = esdr.size // kk
+    acc = np.zeros((r, h), F)
+    if skip1_b is not None:
+        acc = conv(skip1_b).copy()
+    if skip2_b is not None:
+        acc = (acc + conv(skip2_b)).astype(F)
+    for i in range(r):
+        for k in range(kk):
+            p = int(esdr[k * r + i] if mode <= 1 else esdr[i * kk + k])
+            if p < 0 or p >= num_dst:
+                continue
+            term = rows[p].copy()
+            if bias_b is not None and expert is not None:
+                eid = int(expert[i, k])
+                if 0 <= eid < bias_b.shape[0]:
+                    term = (term + conv(bias_b)[eid]).astype(F)
+            if scales is not None:
+                term = (term * F(scales[i, k])).astype(F)
+            acc[i] = (acc[i] + term).astype(F)
+    return acc if kind == "f32" else to_bits(acc, kind)
+
+
+def gating(xb, kind, k, finished):
+    x = xb.astype(F) if kind == "f32" else from_bits(xb, kind)
+    rows, inner = x.shape
+    e = canon_exp((x - np.max(x, axis=1, keepdims=True)).astype(F))
+    # the row sum in the project's fixed order: 32 lanes, lane t adds columns t, t+32, ...; then a butterfly
+    lanes = np.zeros((rows, 32), F)
+    for c in range(inner):
+        lanes[:, c & 31] = (lanes[:, c & 31] + e[:, c]).astype(F)
+    for off in (16, 8, 4, 2, 1):
+        lanes = (lanes + lanes[:, np.arange(32) ^ off]).astype(F)
+    total = lanes[:, 0]
+    # stable sort of (-value, column): equal probabilities keep ascending column order
+    order = np.argsort(-e, axis=1, kind="stable")[:, :k]
+    top = np.take_along_axis(e, order, axis=1)
+    y = (top / total[:, None]).astype(F)
+    idx = order.astype(np.int32)
+    if finished is not None:
+        idx = np.where(finished[:, None] != 0, np.int32(inner), idx).astype(np.int32)
+    row_idx = (np.arange(k, dtype=np.int64)[None, :] * rows + np.arange(rows, dtype=np.int64)[:, None]).astype(np.int32)
+    return (y if kind == "f32" else to_bits(y, kind)), idx, row_idx
+
+
+def dqsq(x, kind, wscale, ascale, qscale, activate_left, direct=False):
+    m, n2 = x.shape
+    h = n2 // 2
+    if kind == "i32":
+        a = (x[:, :h].astype(F) * wscale[None, :h]).astype(F)
+        b = (x[:, h:].astype(F) * wscale[None, h:]).astype(F)
+    else:
+        v = from_bits(x, kind)
+        a, b = v[:, :h].copy(), v[:, h:].copy()
+    if qscale is not None:
+        if activate_left:
+            b = (b * qscale[None, :]).astype(F)
+        else:
+            a = (a * qscale[None, :]).astype(F)
+    if kind == "i32":
+        a = (a * ascale[:, None]).astype(F)
+        b = (b * ascale[:, None]).astype(F)
+    gate = a if activate_left else b
+    den = (canon_exp((gate * F(-1.0)).astype(F)) + F(1.0)).astype(F)
+    with np.errstate(invalid="ignore", divide="ignore", over="ignore"):
+        out = ((a * b).astype(F) / den).astype(F)
+        mx = np.fmax.reduce(np.abs(out), axis=1, initial=F(0))  # NaN ignored, as fmaxf does
+        s = np.maximum((mx * F(1.0 / 127.0)).astype(F), F(1e-12)).astype(F)
+        pad = 8 if kind == "i32" else 16
+        if -(-h // pad) * pad <= 1984:
+            q = (out / s[:, None]).astype(F)
+        else:
+            q = (out * (F(1.0) / s).astype(F)[:, None]).astype(F)
+    y = narrow(np.clip(q, F(-128), F(127)), direct)
+    y = np.where(np.isnan(q), np.int8(0), y).astype(np.int8)
+    return y, s, out
+
+
 def main():
     rng = np.random.default_rng(20260101)
     out = {}
@@ -226,6 +369,83 @@ def main():
     xs = rng.uniform(1e-3, 5e-2, m).astype(F)
     out["gmm_x"], out["gmm_w"], out["gmm_ws"], out["gmm_xs"], out["gmm_gl"] = x, w, ws, xs, gl
     out["gmm_out"] = gmm_i8(x, w, ws, xs, gl, None)
+
+    # ---- the operators either side of the path (their own generator: the arrays above stay as they were) ------
+    rng = np.random.default_rng(20260202)
+
+    # MoeReRouting: 3 ranks x 4 local experts, an empty cell, an empty expert column, spare rows at the end
+    counts = np.array([[2, 0, 3, 0], [1, 4, 0, 0], [0, 2, 5, 0]], np.int64)
+    a = int(counts.sum()) + 3
+    tok = rng.integers(-128, 128, (a, 24)).astype(np.int8)
+    scl = rng.random(a).astype(F)
+    o, os_, idx, num = mrr(tok, counts, scl)
+    total = int(counts.sum())
+    out["mrr_tokens"], out["mrr_counts"], out["mrr_scales"] = tok, counts, scl
+    out["mrr_out"], out["mrr_out_scales"], out["mrr_idx"], out["mrr_num"] = o[:total], os_[:total], idx[:total], num
+
+    # MoeFinalizeRouting: every optional operand, both index layouts, dropped rows and out-of-range expert ids
+    r, k, h, e = 7, 3, 40, 5
+    for kind in ("bf16", "f16", "f32"):
+        enc = (lambda v: v.astype(F)) if kind == "f32" else (lambda v, kind=kind: to_bits(v, kind))
+        rows = enc(rng.standard_normal((r * k + 2, h)).astype(F))
+        s1 = enc(rng.standard_normal((r, h)).astype(F))
+        s2 = enc(rng.standard_normal((r, h)).astype(F))
+        bias = enc(rng.standard_normal((e, h)).astype(F))
+        scales = rng.random((r, k)).astype(F)
+        esdr = rng.permutation(r * k).astype(np.int32)
+        esdr[4] = -1               # dropped
+        esdr[9] = r * k + 5        # past the rows: dropped
+        expert = rng.integers(0, e, (r, k)).astype(np.int32)
+        expert[2, 1] = e + 3       # bias dropped, term kept
+        expert[5, 0] = -2
+        out[f"mfr_{kind}_rows"], out[f"mfr_{kind}_skip1"], out[f"mfr_{kind}_skip2"] = rows, s1, s2
+        out[f"mfr_{kind}_bias"], out[f"mfr_{kind}_scales"] = bias, scales
+        out[f"mfr_{kind}_esdr"], out[f"mfr_{kind}_expert"] = esdr, expert
+        out[f"mfr_{kind}_out_mode0"] = mfr(rows, kind, esdr, s1, s2, bias, scales, expert, 0)
+        out[f"mfr_{kind}_out_mode2"] = mfr(rows, kind, esdr, s1, None, None, scales, None, 2)
+        out[f"mfr_{kind}_out_plain"] = mfr(rows, kind, esdr[:r], None, None, None, None, None, 0)
+
+    # MoeGatingTopKSoftmax: ties (repeated logits), a dominant logit, finished rows, k up to the row length
+    for kind in ("bf16", "f16", "f32"):
+        x = rng.standard_normal((6, 70)).astype(F)
+        x[1, 10] = x[1, 3]          # equal values: the lower column comes first
+        x[1, 50] = x[1, 3]
+        x[2] = 0.25                 # every probability equal
+        x[3, 7] = 60.0              # one expert takes nearly everything
+        xb = x if kind == "f32" else to_bits(x, kind)
+        fin = np.array([0, 0, 1, 0, 1, 0], np.uint8)
+        y, ei, ri = gating(xb, kind, 8, fin)
+        out[f"gate_{kind}_x"], out[f"gate_{kind}_finished"] = xb, fin
+        out[f"gate_{kind}_y"], out[f"gate_{kind}_idx"], out[f"gate_{kind}_row_idx"] = y, ei, ri
+    xs = rng.standard_normal((3, 5)).astype(F)
+    y, ei, ri = gating(xs, "f32", 5, None)
+    out["gate_small_x"], out["gate_small_y"], out["gate_small_idx"], out["gate_small_row_idx"] = xs, y, ei, ri
+
+    # DequantSwigluQuant: int32 / 16-bit input, either gate side, smooth scale, the short-row (division) and
+    # long-row (reciprocal) scaling forms, an all-zero row, a NaN element
+    for name, h, kind in (("short", 48, "i32"), ("long", 2000, "i32"), ("short", 40, "bf16"), ("long", 1992, "f16")):
+        m = 5
+        tag = f"dqsq_{kind}_{name}"
+        if kind == "i32":
+            x = rng.integers(-300000, 300000, (m, 2 * h)).astype(np.int32)
+            x[2] = 0
+            ws = rng.uniform(1e-3, 1e-2, 2 * h).astype(F)
+            a_s = rng.uniform(1e-3, 5e-2, m).astype(F)
+        else:
+            xv = (3.0 * rng.standard_normal((m, 2 * h))).astype(F)
+            xv[2] = 0.0
+            xv[3, 5] = np.nan
+            x = to_bits(xv, kind)
+            ws = a_s = None
+        qs = rng.uniform(0.5, 1.5, h).astype(F)
+        out[f"{tag}_x"], out[f"{tag}_qs"] = x, qs
+        if ws is not None:
+            out[f"{tag}_ws"], out[f"{tag}_as"] = ws, a_s
+        for left in (0, 1):
+            y, s, act = dqsq(x, kind, ws, a_s, qs, bool(left))
+            out[f"{tag}_y_left{left}"], out[f"{tag}_scale_left{left}"], out[f"{tag}_act_left{left}"] = y, s, act
+        y, s, _ = dqsq(x, kind, ws, a_s, None, True, direct=True)
+        out[f"{tag}_y_noq_direct"], out[f"{tag}_scale_noq"] = y, s
 
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(out), "arrays")

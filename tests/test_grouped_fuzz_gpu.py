@@ -9,16 +9,27 @@ from helpers import bits
 
 pytestmark = pytest.mark.gpu
 
+@pytest.fixture
+def force_shape():
+    """Forces a kernel shape for the duration of a test ("auto" = the library's own choice)."""
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+
+    def _set(shape):
+        assert lib.w8a8_set_gemm_shape(0 if shape == "auto" else int(shape)) >= 0
+
+    yield _set
+    lib.w8a8_set_gemm_shape(0)
+
+
 SPECIAL = [0, 0, 1, 2, 7, 63, 64, 65, 127, 128, 129, 130, 200, 255, 256, 257, 300, 383, 384, 385, 511, 512, 513, 700]
 
 
 @pytest.mark.parametrize("shape", ["auto", "1", "2", "3"])
 @pytest.mark.parametrize("seed", [11, 12])
-def test_random_grouped_problems_match_the_oracle(ops, oracle, monkeypatch, shape, seed):
-    if shape == "auto":
-        monkeypatch.delenv("W8A8_GEMM_CTA_GROUP", raising=False)
-    else:
-        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", shape)
+def test_random_grouped_problems_match_the_oracle(ops, oracle, force_shape, shape, seed):
+    force_shape(shape)
     rng = np.random.default_rng(seed)
     for case in range(12):
         e = int(rng.integers(1, 24))
@@ -54,14 +65,11 @@ def test_random_grouped_problems_match_the_oracle(ops, oracle, monkeypatch, shap
 
 
 @pytest.mark.parametrize("shape", ["auto", "1", "2"])
-def test_random_quant_matmul_epilogues_match_the_oracle(ops, oracle, monkeypatch, shape):
+def test_random_quant_matmul_epilogues_match_the_oracle(ops, oracle, force_shape, shape):
     """Random M (1 .. 700, around the 128 / 256 tile edges), K, N, weight layout and every combination of the
     epilogue's optional terms: scale scalar / per channel, fp32 / bf16; offset none / scalar / per channel;
     per-token scale; bias none / int32 / fp16 / bf16 / fp32, scalar or per channel; fp16 or bf16 output."""
-    if shape == "auto":
-        monkeypatch.delenv("W8A8_GEMM_CTA_GROUP", raising=False)
-    else:
-        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", shape)
+    force_shape(shape)
     O = oracle
     rng = np.random.default_rng(21)
     rows = [1, 3, 16, 64, 127, 128, 129, 255, 256, 257, 300, 511, 513, 700]

@@ -17,19 +17,17 @@ F = np.float32
 
 
 @pytest.fixture(autouse=True, params=["auto", "single", "pair", "hybrid"])
-def cta_group(request, monkeypatch):
+def cta_group(request):
     """Every test runs with the library's own choice of kernel shape, with single-CTA tiles forced, with CTA-pair
     (cta_group::2) tiles forced, and with the two-launch form of grouped problems forced (pairs on whole 256-row
     blocks, single CTAs on the leftovers; dense problems ignore it): all must give identical results."""
-    if request.param == "single":
-        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "1")
-    elif request.param == "pair":
-        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "2")
-    elif request.param == "hybrid":
-        monkeypatch.setenv("W8A8_GEMM_CTA_GROUP", "3")
-    else:
-        monkeypatch.delenv("W8A8_GEMM_CTA_GROUP", raising=False)
-    return request.param
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    prev = lib.w8a8_set_gemm_shape({"auto": 0, "single": 1, "pair": 2, "hybrid": 3}[request.param])
+    assert prev >= 0
+    yield request.param
+    lib.w8a8_set_gemm_shape(0)
 
 
 def _i8(rng, shape):

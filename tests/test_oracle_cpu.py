@@ -511,3 +511,77 @@ def test_dequant_swiglu_quant_hand_derived(oracle):
         oracle.dequant_swiglu_quant(xb, oracle.DT_BF16, weight_scale=ws)
     with pytest.raises(ValueError):
         oracle.dequant_swiglu_quant(x, oracle.DT_I32, weight_scale=ws)
+
+
+# ---------------------------------------------------------------------------
+# The operators either side of the path against the independent numpy restatement (tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------
+def _dt(oracle, kind):
+    return {"bf16": oracle.DT_BF16, "f16": oracle.DT_F16, "f32": oracle.DT_F32, "i32": oracle.DT_I32}[kind]
+
+
+def _same_bits(a, b):
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    return a.dtype == b.dtype and a.shape == b.shape and a.tobytes() == b.tobytes()
+
+
+def test_moe_re_routing_golden(oracle, golden):
+    g = golden
+    out, out_s, idx, num = oracle.moe_re_routing(g["mrr_tokens"], g["mrr_counts"], g["mrr_scales"])
+    total = int(g["mrr_counts"].sum())
+    assert _same_bits(out[:total], g["mrr_out"]) and _same_bits(out_s[:total], g["mrr_out_scales"])
+    assert _same_bits(idx[:total], g["mrr_idx"]) and _same_bits(num, g["mrr_num"])
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16", "f32"])
+def test_moe_finalize_routing_golden(oracle, golden, kind):
+    g, dt = golden, _dt(oracle, kind)
+    p = f"mfr_{kind}_"
+    full = oracle.moe_finalize_routing(g[p + "rows"], g[p + "esdr"], dt, skip1=g[p + "skip1"], skip2=g[p + "skip2"],
+                                       bias=g[p + "bias"], scales=g[p + "scales"], expert=g[p + "expert"],
+                                       drop_pad_mode=0)
+    assert _same_bits(full, g[p + "out_mode0"])
+    rowwise = oracle.moe_finalize_routing(g[p + "rows"], g[p + "esdr"], dt, skip1=g[p + "skip1"],
+                                          scales=g[p + "scales"], drop_pad_mode=2)
+    assert _same_bits(rowwise, g[p + "out_mode2"])
+    r = g[p + "scales"].shape[0]
+    plain = oracle.moe_finalize_routing(g[p + "rows"], g[p + "esdr"][:r], dt)
+    assert _same_bits(plain, g[p + "out_plain"])
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16", "f32"])
+def test_moe_gating_golden(oracle, golden, kind):
+    g, dt = golden, _dt(oracle, kind)
+    y, ei, ri = oracle.moe_gating_top_k_softmax(g[f"gate_{kind}_x"], dt, 8, finished=g[f"gate_{kind}_finished"])
+    assert _same_bits(y, g[f"gate_{kind}_y"])
+    assert _same_bits(ei, g[f"gate_{kind}_idx"]) and _same_bits(ri, g[f"gate_{kind}_row_idx"])
+    # the tie in row 1 resolves to ascending columns, the all-equal row 2 is finished (index = row length)
+    assert (ei[2] == 70).all()
+
+
+def test_moe_gating_golden_k_equals_row_length(oracle, golden):
+    g = golden
+    y, ei, ri = oracle.moe_gating_top_k_softmax(g["gate_small_x"], oracle.DT_F32, 5)
+    assert _same_bits(y, g["gate_small_y"]) and _same_bits(ei, g["gate_small_idx"])
+    assert _same_bits(ri, g["gate_small_row_idx"])
+
+
+@pytest.mark.parametrize("tag,kind", [("dqsq_i32_short", "i32"), ("dqsq_i32_long", "i32"), ("dqsq_bf16_short", "bf16"),
+                                      ("dqsq_f16_long", "f16")])
+def test_dequant_swiglu_quant_golden(oracle, golden, tag, kind):
+    """Both scaling forms (division for short rows, reciprocal for long ones), both gate sides, with and without
+    the smooth scale, both rounding modes."""
+    g, dt = golden, _dt(oracle, kind)
+    ws = g[tag + "_ws"] if kind == "i32" else None
+    a_s = g[tag + "_as"] if kind == "i32" else None
+    for left in (0, 1):
+        y, s, act = oracle.dequant_swiglu_quant(g[tag + "_x"], dt, weight_scale=ws, activation_scale=a_s,
+                                                quant_scale=g[tag + "_qs"], activate_left=bool(left), want_out=True)
+        want_act = g[f"{tag}_act_left{left}"]
+        nan = np.isnan(want_act)
+        assert np.array_equal(np.isnan(act), nan)
+        assert np.array_equal(act.view(np.uint32)[~nan], want_act.view(np.uint32)[~nan])
+        assert _same_bits(y, g[f"{tag}_y_left{left}"]) and _same_bits(s, g[f"{tag}_scale_left{left}"])
+    y, s = oracle.dequant_swiglu_quant(g[tag + "_x"], dt, weight_scale=ws, activation_scale=a_s, activate_left=True,
+                                       round_mode=oracle.ROUND_DIRECT)
+    assert _same_bits(y, g[tag + "_y_noq_direct"]) and _same_bits(s, g[tag + "_scale_noq"])
