@@ -871,24 +871,167 @@ def run_reference(args, wl):
 
 
 # --------------------------------------------------------------------------
+# secondary measurements carried by the default line
+# --------------------------------------------------------------------------
+def _launch_count():
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    return int(L.load().w8a8_kernel_launch_count())
+
+
+def _max_over_ranks(torch, dist, world, values):
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def _sum_over_ranks(torch, dist, world, values):
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return [float(v) for v in t]
+
+
+def timed_regions(torch, barrier, step, steps, repeats, graph=None):
+    """`repeats` regions of `steps` steps each, every region bracketed by a barrier + synchronize on both sides and
+    timed with CUDA events on the launching stream.  Returns the per-step milliseconds of every region."""
+    out = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(steps):
+                step()
+        e1.record()
+        barrier()
+        out.append(e0.elapsed_time(e1) / steps)
+    return out
+
+
+def measure_secondary(torch, dist, wl, rank, world, barrier, steps, peaks, repeats=5):
+    """One of the other operators of the path at N GPUs, device-resident inputs: median per-step time over `repeats`
+    regions (max over ranks), aggregate throughput, roofline fraction of rank 0's share."""
+    wl.gpu_setup(torch, rank, world)
+    for _ in range(3):
+        wl.gpu_step()
+    torch.cuda.synchronize()
+    graph = None
+    if wl.bound == "hbm":
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(steps):
+                wl.gpu_step()
+        graph.replay()
+        torch.cuda.synchronize()
+    n0 = _launch_count()
+    wl.gpu_step()
+    launches = _launch_count() - n0
+    regions = timed_regions(torch, barrier, wl.gpu_step, steps, repeats, graph)
+    regions = [_max_over_ranks(torch, dist, world, [r])[0] for r in regions]
+    ms = float(np.median(regions))
+    units = _sum_over_ranks(torch, dist, world, [wl.units_per_step()])[0]
+    peak = peaks["hbm_gbs"] if wl.bound == "hbm" else peaks["bf16_tflops"] * INT8_PER_BF16
+    achieved = wl.roofline_units() / (ms * 1e-3)
+    return {"metric": wl.metric, "value": units / (ms * 1e-3), "unit": wl.unit, "ms_per_step": ms,
+            "ms_min": min(regions), "ms_max": max(regions), "config": wl.config(world), "scaling": wl.scaling,
+            "launches_per_step": launches,
+            "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "frac": achieved / peak,
+                         "unit": "GB/s" if wl.bound == "hbm" else "TOPS", "share": "rank 0",
+                         "traffic": getattr(wl, "traffic", None)}}
+
+
+def measure_chain(torch, dist, rank, world, barrier, steps, peaks):
+    """Benchmark configuration 5 of 5 (the expert-parallel MoE FFN chain, T=65536) at N GPUs: per-step time (max
+    over ranks, median of 3 regions), tokens/s, the transport used, a per-phase CUDA-event breakdown of rank 0's
+    stream, and for N > 1 a parity word: one step with the NCCL all-to-all transport and one with the default
+    (fused peer-store) transport on the same inputs must agree bit for bit on every rank."""
+    wl = ChainWorkload()
+    wl.transport, wl.device_tables = "p2p", None
+    wl.gpu_setup(torch, rank, world)
+    chain = wl.chain
+    for _ in range(3):
+        out_default, xo_default = wl.gpu_step()
+    torch.cuda.synchronize()
+    n0 = _launch_count()
+    wl.gpu_step()
+    launches = _launch_count() - n0
+    steps = max(3, min(steps, 10))
+    regions = timed_regions(torch, barrier, wl.gpu_step, steps, 3)
+    regions = [_max_over_ranks(torch, dist, world, [r])[0] for r in regions]
+    ms = float(np.median(regions))
+    # per-phase breakdown: events on the launching stream after each phase, averaged over a few steps
+    marks = []
+    chain.phase_hook = lambda name: marks.append((name, _event(torch)))
+    phase_ms = {}
+    n_prof = 3
+    for _ in range(n_prof):
+        marks.clear()
+        barrier()
+        start = _event(torch)
+        wl.gpu_step()
+        torch.cuda.synchronize()
+        prev = start
+        for name, ev in marks:
+            phase_ms[name] = phase_ms.get(name, 0.0) + prev.elapsed_time(ev) / n_prof
+            prev = ev
+    chain.phase_hook = None
+    names = list(phase_ms)
+    phase_max = _max_over_ranks(torch, dist, world, [phase_ms[n] for n in names])
+    try:
+        chain.check()
+        overflow = False
+    except RuntimeError:
+        overflow = True
+    res = {"metric": wl.metric, "value": wl.T / (ms * 1e-3), "unit": wl.unit, "ms_per_step": ms, "ms_min": min(regions),
+           "ms_max": max(regions), "config": wl.config(world), "transport": chain.transport,
+           "device_tables": bool(chain.device_tables), "launches_per_step": launches,
+           "phases_ms_rank0": {n: round(phase_ms[n], 4) for n in names},
+           "phases_ms_max_over_ranks": {n: round(v, 4) for n, v in zip(names, phase_max)},
+           "receive_buffer_overflow": overflow,
+           "tensor_roofline_frac": (wl.roofline_units() / (ms * 1e-3)) / (peaks["bf16_tflops"] * INT8_PER_BF16)}
+    if world > 1:
+        from cannbench_operator_solutions_b200.ep import MoeFfnChain
+
+        ref = MoeFfnChain(wl.E, chain.shard, transport="nccl")
+        out_nccl, xo_nccl = ref.forward(wl.x, wl.res, wl.gamma, 1e-6, wl.idx, wl.probs)
+        out_default, xo_default = wl.gpu_step()
+        torch.cuda.synchronize()
+        same = float(torch.equal(out_nccl, out_default) and torch.equal(xo_nccl, xo_default))
+        t = torch.tensor([same], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        res["parity"] = {"bit_identical_nccl_vs_default_transport_all_ranks": bool(t[0] > 0.5),
+                         "compared": "ffn output and residual output of one step, every rank"}
+    return res
+
+
+def _event(torch):
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    return ev
+
+
+# --------------------------------------------------------------------------
 # the tensor pipe's own ceiling
 # --------------------------------------------------------------------------
 MMA_PEAK_SHAPES = [
-    # (cta_group, M, N, A MN-major, B MN-major, fill, accumulators, instructions per commit, commits in flight)
-    # the production shape: 4 K steps per shared-memory stage, one commit per stage
-    (2, 256, 256, 0, 1, 1, 1, 4, 4), (2, 256, 256, 0, 1, 0, 1, 4, 4), (2, 256, 256, 0, 1, 1, 1, 4, 6),
-    (2, 256, 256, 0, 1, 1, 1, 8, 4), (2, 256, 256, 0, 1, 1, 1, 16, 4), (2, 256, 256, 0, 1, 1, 1, 64, 2),
-    (2, 256, 256, 0, 1, 1, 2, 16, 4),
-    (1, 128, 256, 0, 1, 1, 1, 4, 4), (1, 128, 256, 0, 1, 1, 1, 16, 4), (1, 128, 256, 0, 1, 1, 1, 64, 2),
-    (1, 128, 128, 0, 1, 1, 1, 4, 4), (1, 128, 128, 0, 1, 1, 1, 16, 4), (1, 128, 128, 0, 1, 1, 1, 64, 2),
-    (1, 128, 128, 0, 1, 1, 4, 64, 2),
-    (2, 256, 128, 0, 1, 1, 1, 16, 4), (2, 256, 128, 0, 1, 1, 1, 64, 2),
-    (2, 128, 256, 0, 1, 1, 1, 16, 4), (2, 128, 256, 0, 1, 1, 1, 64, 2), (1, 64, 256, 0, 1, 1, 1, 64, 2),
+    # (cta_group, M, N, A MN-major, B MN-major, fill, accumulators, instructions per commit, commits in flight, pattern)
+    # the matmul kernels' shape: 4 K steps per shared-memory stage
+    (2, 256, 256, 0, 1, 1, 1, 4, 4, 0), (2, 256, 256, 0, 1, 0, 1, 4, 4, 0), (2, 256, 256, 0, 1, 1, 1, 4, 4, 3),
+    (2, 256, 256, 0, 1, 1, 1, 8, 4, 0), (2, 256, 256, 0, 1, 1, 1, 8, 4, 1), (2, 256, 256, 0, 1, 1, 1, 8, 4, 2),
+    (2, 256, 256, 0, 1, 1, 1, 8, 4, 3), (2, 256, 256, 0, 1, 1, 1, 8, 3, 0), (2, 256, 256, 0, 1, 1, 1, 12, 2, 0),
+    (2, 256, 256, 0, 1, 1, 1, 16, 4, 0), (2, 256, 256, 0, 1, 1, 1, 64, 2, 0),
+    (1, 128, 256, 0, 1, 1, 1, 4, 4, 0), (1, 128, 256, 0, 1, 1, 1, 8, 4, 0), (1, 128, 256, 0, 1, 1, 1, 8, 2, 0),
+    (1, 128, 256, 0, 1, 1, 1, 16, 4, 0),
+    (1, 128, 128, 0, 1, 1, 1, 8, 4, 0), (1, 128, 128, 0, 1, 1, 1, 64, 2, 0),
+    (2, 256, 128, 0, 1, 1, 1, 64, 2, 0), (2, 128, 256, 0, 1, 1, 1, 8, 4, 0), (2, 128, 256, 0, 1, 1, 1, 64, 2, 0),
+    (1, 64, 256, 0, 1, 1, 1, 64, 2, 0),
     # weights as the A operand (MN-major), a few activation rows as the narrow B operand
-    (2, 256, 256, 1, 0, 1, 1, 16, 4), (2, 256, 128, 1, 0, 1, 1, 64, 2), (2, 256, 64, 1, 0, 1, 1, 4, 4),
-    (2, 256, 64, 1, 0, 1, 1, 16, 4), (2, 256, 64, 1, 0, 1, 1, 64, 2), (2, 256, 64, 1, 0, 1, 2, 64, 2),
-    (2, 256, 32, 1, 0, 1, 1, 64, 2), (2, 256, 16, 1, 0, 1, 1, 64, 2), (2, 256, 16, 1, 0, 1, 1, 256, 2),
-    (1, 128, 64, 1, 0, 1, 1, 64, 2), (1, 128, 16, 1, 0, 1, 1, 64, 2),
+    (2, 256, 256, 1, 0, 1, 1, 16, 4, 0), (2, 256, 64, 1, 0, 1, 1, 64, 2, 0), (2, 256, 16, 1, 0, 1, 1, 64, 2, 0),
+    (1, 128, 64, 1, 0, 1, 1, 64, 2, 0),
 ]
 
 
@@ -906,16 +1049,16 @@ def run_mma_peak(args):
     sampler = ClockSampler(0)
     sampler.start()
     rows = []
-    for cg, m, n, a_mn, b_mn, fill, acc, per, depth in MMA_PEAK_SHAPES:
+    for cg, m, n, a_mn, b_mn, fill, acc, per, depth, pattern in MMA_PEAK_SHAPES:
         batches = max(64, 160000 // per)
         for _ in range(max(1, args.warmup // 3)):
-            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, batches // 8, err.data_ptr(), st)
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, pattern, batches // 8, err.data_ptr(), st)
             assert rc == 0, L.status_string(rc)
         best = None
         for _ in range(3):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, batches, err.data_ptr(), st)
+            rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, fill, acc, per, depth, pattern, batches, err.data_ptr(), st)
             e1.record()
             assert rc == 0, L.status_string(rc)
             torch.cuda.synchronize()
@@ -923,7 +1066,7 @@ def run_mma_peak(args):
             best = ms if best is None or ms < best else best
         ops = lib.w8a8_mma_issue_probe_ops(cg, m, n, per, batches)
         rows.append({"cta_group": cg, "m": m, "n": n, "a_major": "MN" if a_mn else "K", "b_major": "MN" if b_mn else "K",
-                     "operands": "random" if fill else "zero", "accumulators": acc, "per_commit": per, "in_flight": depth, "ms": round(best, 3),
+                     "operands": "random" if fill else "zero", "accumulators": acc, "per_commit": per, "in_flight": depth, "pattern": pattern, "ms": round(best, 3),
                      "tops": round(ops / (best * 1e-3) / 1e12, 1),
                      "ns_per_mma": round(best * 1e6 / (batches * per), 2)})
     clocks = sampler.stop()
@@ -959,6 +1102,9 @@ def main():
                          "keep experts whole")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                     help="time the K steps as one CUDA-graph replay (auto: the bandwidth-bound workloads)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of K steps each; the median is reported")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="default workload only: skip the other operators of the path and the chain")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -1027,18 +1173,12 @@ def main():
                 wl.gpu_step()
         graph.replay()
         torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # `--repeats` regions of exactly K steps each (barrier + synchronize on both sides of every region, CUDA events
+    # on the launching stream); the headline is the median region, min and max are reported beside it
     hold(0.6)
-    barrier()
-    ev0.record()
-    if graph is not None:
-        graph.replay()
-    else:
-        for _ in range(args.steps):
-            wl.gpu_step()
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    launches_before = _launch_count()
+    regions = timed_regions(torch, barrier, wl.gpu_step, args.steps, args.repeats, graph)
+    launches_per_region = (_launch_count() - launches_before) // args.repeats
     hold(0.4)
 
     # ---- dominant kernel alone (same stream, CUDA events) ----
@@ -1074,18 +1214,35 @@ def main():
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ---- max over ranks ----
-    times = torch.tensor([ms_total, e2e_ms if e2e_ms is not None else 0.0], dtype=torch.float64, device="cuda")
-    units = torch.tensor([wl.units_per_step()], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        dist.all_reduce(units, op=dist.ReduceOp.SUM)
-    ms_total = float(times[0])
-    e2e_ms = float(times[1]) if e2e_ms is not None else None
-    total_units = float(units[0])
+    regions = _max_over_ranks(torch, dist, world, regions)
+    if e2e_ms is not None:
+        e2e_ms = _max_over_ranks(torch, dist, world, [e2e_ms])[0]
+    total_units = _sum_over_ranks(torch, dist, world, [wl.units_per_step()])[0]
+    ms_per_step = float(np.median(regions))
+    primary = {"config": wl.config(world), "scaling": wl.scaling, "roofline_units": wl.roofline_units(),
+               "traffic": getattr(wl, "traffic", None), "traffic_source": getattr(wl, "traffic_source", None)}
+
+    # ---- the rest of the path at the same N (default workload only) ----
+    secondary = None
+    if args.workload == "gmsq" and not args.no_secondary:
+        peaks = measured_peaks()
+        cpu_sample = wl.cpu_sample
+        for name in [k for k in vars(wl) if k not in ("scaling",)]:
+            delattr(wl, name)  # frees the primary workload's device memory
+        torch.cuda.empty_cache()
+        secondary = {}
+        for key, cls in (("rmsnorm_quant", ArdqWorkload), ("dynamic_quant", DqWorkload), ("quant_matmul_m8192", QmmWorkload)):
+            w2 = cls()
+            w2.layout_nk = False
+            secondary[key] = measure_secondary(torch, dist, w2, rank, world, barrier, args.steps, peaks)
+            del w2
+            torch.cuda.empty_cache()
+        secondary["moe_ffn_chain"] = measure_chain(torch, dist, rank, world, barrier, args.steps, peaks)
+        torch.cuda.empty_cache()
+        wl.cpu_sample = cpu_sample
 
     if rank == 0:
         peaks = measured_peaks()
-        ms_per_step = ms_total / args.steps
         value = total_units / (ms_per_step * 1e-3)
         if wl.bound == "hbm":
             peak, punit = peaks["hbm_gbs"], "GB/s"
@@ -1093,18 +1250,25 @@ def main():
         else:
             peak, punit = peaks["bf16_tflops"] * INT8_PER_BF16, "TOPS"
             peak_note = f"2 x {peaks['source']} cuBLAS bf16 burst (int8 MMA rate is twice bf16's); nominal dense int8 is 4500"
-        achieved = wl.roofline_units() / (ms_kernel * 1e-3)  # TOPS or GB/s of the rank-0 share
+        achieved = primary["roofline_units"] / (ms_kernel * 1e-3)  # TOPS or GB/s of the rank-0 share
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
-            "config": wl.config(world), "clocks": clocks,
-            "gpu_launches": wl.kernels_per_step * args.steps,
+            "scaling": primary["scaling"], "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
+            "config": primary["config"], "clocks": clocks,
+            "timed_regions": {"repeats": args.repeats, "steps_each": args.steps, "ms_per_step_median": ms_per_step,
+                              "ms_per_step_min": min(regions), "ms_per_step_max": max(regions)},
+            "gpu_launches": int(launches_per_region),
+            "gpu_launches_note": "kernels the library launched in one timed region of K steps (its own counter)",
+            "sm_cycles_per_step": (ms_per_step * 1e-3 * clocks["sm_mhz"] * 1e6) if clocks and clocks.get("sm_mhz")
+            else None,
             "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": punit,
-                         "frac": achieved / peak, "traffic": getattr(wl, "traffic", None),
-                         "traffic_source": getattr(wl, "traffic_source", None), "kernel_ms": ms_kernel,
+                         "frac": achieved / peak, "traffic": primary["traffic"],
+                         "traffic_source": primary["traffic_source"], "kernel_ms": ms_kernel,
                          "peak_source": peak_note},
         }
+        if secondary is not None:
+            line["secondary"] = secondary
         if e2e_ms is not None:
             line["e2e"] = {"value": total_units / (e2e_ms * 1e-3), "unit": wl.unit, "h2d_bytes_per_step": int(h2d),
                            "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms}

@@ -34,6 +34,7 @@ _vp, _i64, _i32, _f32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctyp
 _u64 = ctypes.c_uint64
 SIGNATURES = {
     "w8a8_version": (_i32, []),
+    "w8a8_kernel_launch_count": (_i64, []),
     "w8a8_status_string": (ctypes.c_char_p, [_i32]),
     "w8a8_dynamic_quant": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "w8a8_add_rms_norm_dynamic_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32, _i32, _vp]),
@@ -69,7 +70,7 @@ SIGNATURES = {
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
-    "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
     "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i32, _i64]),
     "w8a8_selftest_bounded_wait": (_i32, [_i64, _vp, _vp]),
 }

@@ -255,5 +255,6 @@ __device__ __forceinline__ uint32_t chunk_absmax16(uint4 v, uint32_t m2)
 inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 int sm_count();  // cached multiprocessor count of the current device
+void note_launch();  // counts one kernel launch of this library (w8a8_kernel_launch_count)
 
 }  // namespace w8a8

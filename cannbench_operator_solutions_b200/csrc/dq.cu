@@ -135,7 +135,7 @@ static cudaError_t launch_rows(const void* x, int8_t* y, float* scale, int64_t M
     }
     const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
     const unsigned grid = static_cast<unsigned>(M < cap ? M : cap);
-    kern<<<grid, THREADS, 0, st>>>(static_cast<const uint16_t*>(x), y, scale, M, N);
+    kern<<<grid, THREADS, 0, st>>>(static_cast<const uint16_t*>(x), y, scale, M, N); w8a8::note_launch();
     return cudaGetLastError();
 }
 
@@ -163,7 +163,7 @@ static cudaError_t dispatch_cpt(const void* x, int8_t* y, float* scale, int64_t 
     }
     const int64_t cap = static_cast<int64_t>(sm_count()) * 2;
     const unsigned grid = static_cast<unsigned>(M < cap ? M : cap);
-    dq_long_rows_kernel<DT, DIRECT><<<grid, 1024, 0, st>>>(static_cast<const uint16_t*>(x), y, scale, M, N);
+    dq_long_rows_kernel<DT, DIRECT><<<grid, 1024, 0, st>>>(static_cast<const uint16_t*>(x), y, scale, M, N); w8a8::note_launch();
     return cudaGetLastError();
 }
 

@@ -304,7 +304,7 @@ static cudaError_t dispatch_dqsq(const void* x, const float* ws, const float* as
     }
     const int64_t cap = static_cast<int64_t>(sm_count()) * (per_sm < 1 ? 1 : per_sm);
     const unsigned grid = static_cast<unsigned>(M < cap ? M : cap);
-    kern<<<grid, DQSQ_THREADS, 0, st>>>(x, ws, as, qs, y, scale, M, H, left, direct, divide);
+    kern<<<grid, DQSQ_THREADS, 0, st>>>(x, ws, as, qs, y, scale, M, H, left, direct, divide); w8a8::note_launch();
     return cudaGetLastError();
 }
 

@@ -877,12 +877,12 @@ extern "C" int w8a8_route_plan(const int32_t* expert_idx, int64_t T, int64_t top
         return W8A8_ERR_CUDA;
     }
     if (B > 0) {
-        w8a8::rp_count_kernel<<<static_cast<unsigned>(B), w8a8::RP_BLOCK, 0, st>>>(expert_idx, P, E, block_count, bad);
+        w8a8::rp_count_kernel<<<static_cast<unsigned>(B), w8a8::RP_BLOCK, 0, st>>>(expert_idx, P, E, block_count, bad); w8a8::note_launch();
     }
-    w8a8::rp_scan_kernel<<<1, 1024, 0, st>>>(block_count, B, E, base, count, cumsum);
+    w8a8::rp_scan_kernel<<<1, 1024, 0, st>>>(block_count, B, E, base, count, cumsum); w8a8::note_launch();
     if (B > 0) {
         w8a8::rp_place_kernel<<<static_cast<unsigned>(B), w8a8::RP_BLOCK, 0, st>>>(expert_idx, P, E, block_count, base,
-                                                                                  expanded_pos);
+                                                                                  expanded_pos); w8a8::note_launch();
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -907,11 +907,11 @@ extern "C" int w8a8_scatter_rows(const void* src, const float* src_scale, void* 
     if (vec) {
         w8a8::scatter_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                              static_cast<uint8_t*>(dst), dst_scale, expanded_pos, T,
-                                                             static_cast<int>(topk), row_bytes);
+                                                             static_cast<int>(topk), row_bytes); w8a8::note_launch();
     } else {
         w8a8::scatter_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                               static_cast<uint8_t*>(dst), dst_scale, expanded_pos, T,
-                                                              static_cast<int>(topk), row_bytes);
+                                                              static_cast<int>(topk), row_bytes); w8a8::note_launch();
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -936,11 +936,11 @@ extern "C" int w8a8_permute_rows(const void* src, const float* src_scale, void* 
     if (vec) {
         w8a8::permute_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                              static_cast<uint8_t*>(dst), dst_scale, index, rows,
-                                                             row_bytes);
+                                                             row_bytes); w8a8::note_launch();
     } else {
         w8a8::permute_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                               static_cast<uint8_t*>(dst), dst_scale, index, rows,
-                                                              row_bytes);
+                                                              row_bytes); w8a8::note_launch();
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -967,11 +967,11 @@ extern "C" int w8a8_dispatch_rows(const void* src, const float* src_scale, const
     if (vec) {
         w8a8::dispatch_rows_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale, expert_idx,
                                                               expanded_pos, row_dst, scale_dst, my_base, T,
-                                                              static_cast<int>(topk), row_bytes);
+                                                              static_cast<int>(topk), row_bytes); w8a8::note_launch();
     } else {
         w8a8::dispatch_rows_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(src), src_scale,
                                                                expert_idx, expanded_pos, row_dst, scale_dst, my_base,
-                                                               T, static_cast<int>(topk), row_bytes);
+                                                               T, static_cast<int>(topk), row_bytes); w8a8::note_launch();
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -991,7 +991,7 @@ extern "C" int w8a8_expand_row_pointers(const int64_t* seg_first, const uint64_t
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const unsigned grid = static_cast<unsigned>((rows + 255) / 256);
     w8a8::expand_row_pointers_kernel<<<grid, 256, 0, st>>>(seg_first, seg_ptr, static_cast<int>(nseg), rows, row_bytes,
-                                                           out);
+                                                           out); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -1024,7 +1024,7 @@ extern "C" int w8a8_combine(const void* rows, const float* probs, const int64_t*
                     : (vec ? w8a8::mfr_kernel<W8A8_DT_F16, true, false, int64_t>
                            : w8a8::mfr_kernel<W8A8_DT_F16, false, false, int64_t>);
     kern<<<grid, 256, 0, st>>>(rows, expanded_pos, nullptr, nullptr, nullptr, probs, nullptr, out, T, H,
-                               static_cast<int>(topk), 0, INT64_MAX, 0, W8A8_DT_F32);
+                               static_cast<int>(topk), 0, INT64_MAX, 0, W8A8_DT_F32); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -1086,20 +1086,20 @@ extern "C" int w8a8_moe_re_routing(const void* tokens, const void* counts, const
         if (count_bytes == 4) {
             w8a8::rr_table_small_kernel<int32_t><<<1, 1024, 0, st>>>(
                 static_cast<const int32_t*>(counts), static_cast<int>(N), static_cast<int>(E), A, hdr, dst_first,
-                src_first, static_cast<int32_t*>(expert_token_num));
+                src_first, static_cast<int32_t*>(expert_token_num)); w8a8::note_launch();
         } else {
             w8a8::rr_table_small_kernel<int64_t><<<1, 1024, 0, st>>>(
                 static_cast<const int64_t*>(counts), static_cast<int>(N), static_cast<int>(E), A, hdr, dst_first,
-                src_first, static_cast<int64_t*>(expert_token_num));
+                src_first, static_cast<int64_t*>(expert_token_num)); w8a8::note_launch();
         }
     } else if (count_bytes == 4) {
         w8a8::rr_table_kernel<int32_t><<<1, 1024, 0, st>>>(static_cast<const int32_t*>(counts), N, E, A, hdr,
                                                           dst_first, src_first, col_start, row_start,
-                                                          static_cast<int32_t*>(expert_token_num));
+                                                          static_cast<int32_t*>(expert_token_num)); w8a8::note_launch();
     } else {
         w8a8::rr_table_kernel<int64_t><<<1, 1024, 0, st>>>(static_cast<const int64_t*>(counts), N, E, A, hdr,
                                                           dst_first, src_first, col_start, row_start,
-                                                          static_cast<int64_t*>(expert_token_num));
+                                                          static_cast<int64_t*>(expert_token_num)); w8a8::note_launch();
     }
     if (cudaGetLastError() != cudaSuccess) {
         return W8A8_ERR_CUDA;
@@ -1109,7 +1109,7 @@ extern "C" int w8a8_moe_re_routing(const void* tokens, const void* counts, const
     }
     const unsigned blocks = static_cast<unsigned>((A + 255) / 256);
     w8a8::rr_index_kernel<<<blocks, 256, 0, st>>>(hdr, dst_first, src_first, static_cast<int64_t>(cells), A, index,
-                                                  out_idx);
+                                                  out_idx); w8a8::note_launch();
     if (cudaGetLastError() != cudaSuccess) {
         return W8A8_ERR_CUDA;
     }
@@ -1129,7 +1129,7 @@ static int launch_mfr(const void* rows, const int32_t* esdr, const void* skip1, 
                     : (has_bias ? w8a8::mfr_kernel<DT, false, true, int32_t>
                                 : w8a8::mfr_kernel<DT, false, false, int32_t>);
     kern<<<grid, 256, 0, st>>>(rows, esdr, skip1, skip2, bias, scales, expert, out, R, H, static_cast<int>(K), E,
-                               num_dst, col_mode, scale_dt);
+                               num_dst, col_mode, scale_dt); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -1202,6 +1202,6 @@ extern "C" int w8a8_ep_tables(const int64_t* counts, int64_t P, int64_t E, int64
     }
     w8a8::ep_tables_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         counts, static_cast<int>(P), static_cast<int>(E), static_cast<int>(rank), peer_base, off_x, off_s, off_back,
-        row_bytes, back_row_bytes, cap_rows, row_dst, scale_dst, my_base, group_list, seg_first, seg_ptr, status);
+        row_bytes, back_row_bytes, cap_rows, row_dst, scale_dst, my_base, group_list, seg_first, seg_ptr, status); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

@@ -133,7 +133,7 @@ static cudaError_t launch_gating(const void* x, const uint8_t* finished, void* y
     const int64_t want = (rows + GATING_WARPS - 1) / GATING_WARPS;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-    gating_kernel<DT, VPT><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k);
+    gating_kernel<DT, VPT><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k); w8a8::note_launch();
     return cudaGetLastError();
 }
 

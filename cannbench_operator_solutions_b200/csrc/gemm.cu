@@ -127,6 +127,7 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+    note_launch();
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
 }
 
@@ -455,7 +456,7 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
         return W8A8_ERR_UNSUPPORTED;
     }
     plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, header, tiles, max_tiles, tile_m, mode,
-                                             shared_error, list_on_device == 2 ? 1 : 0);
+                                             shared_error, list_on_device == 2 ? 1 : 0); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -727,10 +728,10 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
     }
     if (flags & W8A8_F_ROUND_DIRECT) {
         gmsq_requant_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, st>>>(g.act, g.amax, y, y_scale, M, H,
-                                                                                g.header);
+                                                                                g.header); w8a8::note_launch();
     } else {
         gmsq_requant_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, st>>>(g.act, g.amax, y, y_scale, M, H,
-                                                                                 g.header);
+                                                                                 g.header); w8a8::note_launch();
     }
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

@@ -53,6 +53,19 @@ __host__ __device__ constexpr int gemm_stages(int cg, int block_n)
     return (GEMM_A_BYTES + (block_n / cg) * GEMM_KBYTES) <= 32768 ? 6 : 4;
 }
 
+// K blocks (128 bytes of K each) per pipeline stage.  The thread that issues the MMAs pays a fixed price for every
+// barrier wait, satisfied or not (measured with the issue probe: about 0.3 us per wait-and-commit against 45 ns
+// per instruction, so 4 instructions per wait sustain 2.5 - 3.0 POPS at full clock, 8 per wait 3.5 - 4.3): a stage
+// therefore carries two K blocks wherever that still leaves three stages.
+__host__ __device__ constexpr int gemm_kblocks_per_stage(int cg, int block_n)
+{
+#ifdef W8A8_ONE_KBLOCK_PER_STAGE  // comparison builds only
+    return 1;
+#else
+    return (GEMM_A_BYTES + (block_n / cg) * GEMM_KBYTES) <= 32768 ? 2 : 1;
+#endif
+}
+
 enum GemmKind { KIND_I8 = 0, KIND_F16 = 1, KIND_BF16 = 2 };
 enum GemmEpi { EPI_RAW = 0, EPI_QMM = 1, EPI_GMSQ = 2, EPI_GMM = 3 };
 
@@ -436,8 +449,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     constexpr int CTA_N = BLOCK_N / CG;            // B columns this CTA loads
     constexpr int NBOX = CTA_N * ELEM / 128;       // MN-major: 128-byte-wide column blocks this CTA loads
     constexpr int B_BYTES = CTA_N * GEMM_KBYTES;
-    constexpr int STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
-    constexpr int STAGES = gemm_stages(CG, BLOCK_N);
+    constexpr int KB_BYTES = GEMM_A_BYTES + B_BYTES;           // one K block: 128 bytes of K of A and of B
+    constexpr int KPS = gemm_kblocks_per_stage(CG, BLOCK_N);   // K blocks per stage
+    constexpr int STAGE_BYTES = KPS * KB_BYTES;
+    constexpr int STAGES = gemm_stages(CG, BLOCK_N) / KPS;
     constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;    // 256 or 512: power of two
     constexpr uint32_t UMMA_M = 128 * CG;
     constexpr uint32_t IDESC =
@@ -562,21 +577,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             const uint32_t full0 = (CG == 2) ? tc::map_to_cta(full_bar(0), 0) : full_bar(0);
             for (int64_t t = worker; ok && t < total_tiles; t += num_workers) {
                 const TileInfo tl = decode(t);
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb0 = 0; kb0 < p.num_k_blocks; kb0 += KPS) {
                     if (!tc::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
+                    const int left = p.num_k_blocks - kb0;
+                    const int n_sub = left < KPS ? left : KPS;  // K blocks this stage carries (the tile's last may be short)
                     const uint32_t fb = full0 + 8u * stage;
-                    {
-                        const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-                        const uint32_t b_dst = a_dst + GEMM_A_BYTES;
-                        // Only the leader announces the bytes (its own and its partner's).  The partner's copies may
-                        // complete first: the barrier's phase cannot end before the leader's arrival, and a
-                        // transaction count may run ahead of its announcement.
-                        if (leader) {
-                            tc::mbar_arrive_expect_tx(full_bar(stage), CG * (static_cast<uint32_t>(p.a_box_bytes) + B_BYTES));
+                    // Only the leader announces the bytes (its own and its partner's).  The partner's copies may
+                    // complete first: the barrier's phase cannot end before the leader's arrival, and a
+                    // transaction count may run ahead of its announcement.
+                    if (leader) {
+                        tc::mbar_arrive_expect_tx(full_bar(stage),
+                                                  CG * n_sub * (static_cast<uint32_t>(p.a_box_bytes) + B_BYTES));
+                    }
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        if (sub >= n_sub) {
+                            break;
                         }
+                        const int kb = kb0 + sub;
+                        const uint32_t a_dst = smem_base + stage * STAGE_BYTES + sub * KB_BYTES;
+                        const uint32_t b_dst = a_dst + GEMM_A_BYTES;
                         if constexpr (CG == 2) {
                             tc::tma_load_2d_pair(a_dst, &tm_a, fb, kb * BLOCK_K, tl.a_row0);
                         } else {
@@ -631,6 +654,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             const uint32_t a_lo0 = static_cast<uint32_t>(a_desc0);
             const uint32_t b_lo0 = static_cast<uint32_t>(b_desc0);
             constexpr uint32_t STAGE_STEP = STAGE_BYTES >> 4;
+            constexpr uint32_t KB_STEP = KB_BYTES >> 4;
             constexpr uint32_t A_KSTEP = 32 >> 4;                                   // 32 bytes of K
             constexpr uint32_t B_KSTEP = B_MN ? ((UMMA_K * 128) >> 4) : (32 >> 4);  // UMMA_K rows of 128 bytes, or 32 bytes
             constexpr int KSTEPS = BLOCK_K / UMMA_K;
@@ -648,26 +672,36 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 tc::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
                 uint32_t accumulate = 0;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    if (!tc::mbar_wait_cluster(full_bar(stage), phase, abort_flag)) {
+                for (int kb0 = 0; kb0 < p.num_k_blocks; kb0 += KPS) {
+                    // The copies are consumed by the tensor core (async proxy), not by this thread: the barrier's
+                    // default acquire plus the tcgen05 fence is what orders them, also for the partner CTA's
+                    // copies that complete on this barrier.
+                    if (!tc::mbar_wait(full_bar(stage), phase, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc::tc_fence_after_sync();
-                    {
-                        const uint32_t a_lo = a_lo0 + stage * STAGE_STEP;
-                        const uint32_t b_lo = b_lo0 + stage * STAGE_STEP;
+                    const int left = p.num_k_blocks - kb0;
+                    const int n_sub = left < KPS ? left : KPS;
+#pragma unroll
+                    for (int sub = 0; sub < KPS; ++sub) {
+                        if (sub >= n_sub) {
+                            break;
+                        }
+                        const uint32_t a_lo = a_lo0 + stage * STAGE_STEP + sub * KB_STEP;
+                        const uint32_t b_lo = b_lo0 + stage * STAGE_STEP + sub * KB_STEP;
 #pragma unroll
                         for (int k = 0; k < KSTEPS; ++k) {
                             tc::mma_lohi<CG, KIND == KIND_I8>(d_tmem, a_lo + k * A_KSTEP, a_hi, b_lo + k * B_KSTEP, b_hi,
                                                              IDESC, accumulate);
                             accumulate = 1;
                         }
-                        if constexpr (CG == 2) {
-                            tc::tc_commit_pair(empty_bar(stage));
-                        } else {
-                            tc::tc_commit(empty_bar(stage));
-                        }
+                    }
+                    // one commit hands the whole stage back to the producer
+                    if constexpr (CG == 2) {
+                        tc::tc_commit_pair(empty_bar(stage));
+                    } else {
+                        tc::tc_commit(empty_bar(stage));
                     }
                     if (++stage == STAGES) {
                         stage = 0;

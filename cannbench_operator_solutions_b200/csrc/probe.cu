@@ -27,12 +27,12 @@ constexpr int PROBE_KSTEPS = 4;                            // K steps of 32 byte
 template <int CG>
 __global__ void __launch_bounds__(PROBE_THREADS, 1)
     mma_issue_probe_kernel(uint32_t idesc, int a_mn, int b_mn, int fill, int accumulators, int per_commit, int depth,
-                           long long batches, int32_t* error)
+                           int pattern, long long batches, int32_t* error)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PROBE_STAGES * PROBE_STAGE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PROBE_MAX_DEPTH);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PROBE_MAX_DEPTH + 1);  // one spare barrier
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5;
     const uint32_t cta_rank = (CG == 2) ? tc::cluster_ctarank() : 0u;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         }
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PROBE_MAX_DEPTH; ++i) {
+        for (int i = 0; i < PROBE_MAX_DEPTH + 1; ++i) {
             tc::mbar_init(tc::smem_u32(bars + i), 1);
         }
         *abort_flag = 0;
@@ -104,9 +104,18 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         uint32_t slot = 0, round = 0, stage = 0;
         for (long long b = 0; ok && b < batches; ++b) {
             if (round != 0) {
-                if (!tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag)) {
+                // pattern 3: the wait a matmul's issuing thread makes on a barrier other CTAs' copies complete
+                const bool got = (pattern == 3) ? tc::mbar_wait_cluster(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag)
+                                                : tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                if (!got) {
                     ok = false;
                     break;
+                }
+                if (pattern == 1) {  // a second wait, on a phase that is certainly over
+                    (void)tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                }
+                if (pattern == 3) {
+                    tc::tc_fence_after_sync();
                 }
             }
             const uint32_t d_flip = (accumulators == 1) ? static_cast<uint32_t>(b & 1) * 256u : 0u;
@@ -120,6 +129,13 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
                                            idesc, 1u);
                 }
                 stage = (stage + 1u) & (PROBE_STAGES - 1);
+                if (pattern == 2 && g + 1 < groups) {  // an extra commit after every four instructions, never waited for
+                    if constexpr (CG == 2) {
+                        tc::tc_commit_pair(bar0 + 8u * PROBE_MAX_DEPTH);
+                    } else {
+                        tc::tc_commit(bar0 + 8u * PROBE_MAX_DEPTH);
+                    }
+                }
             }
             if constexpr (CG == 2) {
                 tc::tc_commit_pair(bar0 + 8u * slot);
@@ -189,9 +205,12 @@ __global__ void bounded_wait_selftest_kernel(long long limit_cycles, int32_t* er
 using namespace w8a8;
 
 extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
-                                    int accumulators, int per_commit, int depth, int64_t batches, int32_t* error_word,
-                                    void* stream)
+                                    int accumulators, int per_commit, int depth, int pattern, int64_t batches,
+                                    int32_t* error_word, void* stream)
 {
+    if (pattern < 0 || pattern > 3) {
+        return W8A8_ERR_INVALID;
+    }
     if (per_commit < PROBE_KSTEPS || per_commit > 256 || (per_commit % PROBE_KSTEPS) != 0 || depth < 1 ||
         depth > PROBE_MAX_DEPTH) {
         return W8A8_ERR_INVALID;
@@ -242,7 +261,7 @@ extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<2>, idesc, a_mn_major, b_mn_major, fill,
-                               accumulators, per_commit, depth, static_cast<long long>(batches), error_word);
+                               accumulators, per_commit, depth, pattern, static_cast<long long>(batches), error_word);
     } else {
         e = cudaFuncSetAttribute(mma_issue_probe_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
@@ -251,8 +270,9 @@ extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a
         }
         cfg.gridDim = dim3(static_cast<unsigned>(sms), 1, 1);
         e = cudaLaunchKernelEx(&cfg, mma_issue_probe_kernel<1>, idesc, a_mn_major, b_mn_major, fill,
-                               accumulators, per_commit, depth, static_cast<long long>(batches), error_word);
+                               accumulators, per_commit, depth, pattern, static_cast<long long>(batches), error_word);
     }
+    note_launch();
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -269,6 +289,6 @@ extern "C" int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_w
         return W8A8_ERR_INVALID;
     }
     bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<long long>(limit_cycles),
-                                                                                  error_words);
+                                                                                  error_words); w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }

@@ -1,4 +1,6 @@
 // Library identification, status strings and small host utilities.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace w8a8 {
@@ -21,7 +23,16 @@ int sm_count()
     return cached[dev];
 }
 
+static std::atomic<int64_t> g_kernel_launches{0};
+
+void note_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
+
 }  // namespace w8a8
+
+extern "C" int64_t w8a8_kernel_launch_count(void)
+{
+    return w8a8::g_kernel_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" int w8a8_version(void) { return 100; }
 

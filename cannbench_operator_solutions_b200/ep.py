@@ -293,6 +293,13 @@ class MoeFfnChain:
         self.shard = shard
         self.backend = backend if backend is not None else CudaBackend()
         self.last_counts: Optional[np.ndarray] = None
+        # measurement hook: called with a phase name after each phase of a step has been enqueued (the benchmark
+        # records a CUDA event there); None in normal use
+        self.phase_hook = None
+
+    def _mark(self, name: str) -> None:
+        if self.phase_hook is not None:
+            self.phase_hook(name)
 
     # -- collectives --------------------------------------------------------
     def _all_to_all(self, send: torch.Tensor, send_rows: List[int], recv_rows: List[int]) -> torch.Tensor:
@@ -325,7 +332,9 @@ class MoeFfnChain:
         t, topk = expert_idx.shape
         hidden = x.shape[1]
         xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)
+        self._mark("add_rms_norm_dynamic_quant")
         count, _cumsum, pos = b.route_plan(expert_idx, self.E)
+        self._mark("route_plan")
 
         # every rank learns every rank's per-expert counts (P x E integers), then all index arithmetic is local
         if self.world > 1:
@@ -334,6 +343,7 @@ class MoeFfnChain:
             C = gathered.cpu().numpy()
         else:
             C = count.cpu().numpy().reshape(1, self.E)
+        self._mark("count_all_gather_and_host_tables")
         self.last_counts = C[:, self.rank * self.e_local:(self.rank + 1) * self.e_local]
         col = C.sum(0)                                               # rows per expert over all ranks
         base_of_rank = np.cumsum(C, 1) - C                            # [P, E]: rank i's own expert-major positions
@@ -363,13 +373,16 @@ class MoeFfnChain:
         # other rank's stream has reached its own all-gather of this step, which it enqueued after everything
         # that read its buffers in the previous step.
         b.dispatch_rows(xq, xs, expert_idx, pos, tables_dev[0], tables_dev[1], tables_dev[2])
+        self._mark("dispatch_stores")
         self._barrier(dev)   # every rank's rows have landed
+        self._mark("barrier_after_dispatch")
 
         mine = slice(self.rank * self.e_local, (self.rank + 1) * self.e_local)
         rows_me = int(rows_on[self.rank])
         gl = [int(v) for v in ex_incl[self.rank]]
         xe = pb.xe[:rows_me]
         h, hs = b.grouped_matmul_swiglu_quant(xe, self.shard.w_up, self.shard.s_up, pb.xs[:rows_me], gl)
+        self._mark("grouped_matmul_swiglu_quant")
 
         # one segment per (local expert, source rank): where its rows start here, and where they go home
         cm = C[:, mine]                                               # [P, E_loc]
@@ -384,10 +397,13 @@ class MoeFfnChain:
         out_ptrs = b.expand_row_pointers(seg_dev[:nseg + 1], seg_dev[nseg + 1:], rows_me, hidden * elem)
         if rows_me > 0:
             b.grouped_matmul_int8_to_rows(h, self.shard.w_down, gl, hs, self.shard.s_down, out_ptrs, x.dtype)
+        self._mark("down_projection_with_peer_stores")
         self._barrier(dev)   # every rank's output rows have landed at home
+        self._mark("barrier_after_down_projection")
 
         back = pb.buf[pb.off_back:pb.off_back + t * topk * hidden * elem].view(x.dtype).view(t * topk, hidden)
         out = b.combine(back, probs, pos)
+        self._mark("combine")
         return out, x_out
 
     def _forward_p2p_device_tables(self, x, residual, gamma, eps, expert_idx, probs):
@@ -425,26 +441,35 @@ class MoeFfnChain:
             }
         st = self._dev_state
         xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)
+        self._mark("add_rms_norm_dynamic_quant")
         count, _cumsum, pos = b.route_plan(expert_idx, self.E)
+        self._mark("route_plan")
         if self.world > 1:
             dist.all_gather_into_tensor(st["gathered"], count, group=self.group)
         else:
             st["gathered"].copy_(count.view(1, self.E))
         b.ep_tables(st["gathered"], self.rank, st["peer_base"], pb.off_x, pb.off_s, pb.off_back, hidden,
                     hidden * elem, cap, st)
+        self._mark("count_all_gather_and_device_tables")
         # No barrier is needed before the stores: the count all-gather above has completed on this rank, so every
         # other rank's stream has reached its own all-gather of this step, which it enqueued after everything
         # that read its buffers in the previous step.
         b.dispatch_rows(xq, xs, expert_idx, pos, st["row_dst"], st["scale_dst"], st["my_base"])
+        self._mark("dispatch_stores")
         self._barrier(dev)   # every rank's rows have landed
+        self._mark("barrier_after_dispatch")
         b.grouped_matmul_swiglu_quant_capacity(pb.xe, self.shard.w_up, self.shard.s_up, pb.xs, st["group_list"],
                                                st["h"], st["hs"], st["workspace"])
+        self._mark("grouped_matmul_swiglu_quant")
         b.expand_row_pointers_into(st["seg_first"], st["seg_ptr"], nseg, cap, hidden * elem, st["out_ptrs"])
         b.grouped_matmul_int8_to_rows_capacity(st["h"], self.shard.w_down, st["group_list"], st["hs"],
                                                self.shard.s_down, st["out_ptrs"], x.dtype, st["workspace"])
+        self._mark("down_projection_with_peer_stores")
         self._barrier(dev)   # every rank's output rows have landed at home
+        self._mark("barrier_after_down_projection")
         back = pb.buf[pb.off_back:pb.off_back + t * topk * hidden * elem].view(x.dtype).view(t * topk, hidden)
         out = b.combine(back, probs, pos)
+        self._mark("combine")
         return out, x_out
 
     def check(self) -> None:
@@ -466,28 +491,39 @@ class MoeFfnChain:
         b = self.backend
         t, topk = expert_idx.shape
         xq, x_out, xs = b.add_rms_norm_dynamic_quant(x, residual, gamma, eps)
+        self._mark("add_rms_norm_dynamic_quant")
         count, _cumsum, pos = b.route_plan(expert_idx, self.E)
+        self._mark("route_plan")
         send_rows_t, send_scale = b.scatter_rows(xq, xs, pos, t * topk)
+        self._mark("scatter_rows")
 
         recv_counts = self._exchange_counts(count)                      # one small all-to-all + host read
         send_per_rank = count.cpu().numpy().reshape(self.world, self.e_local).sum(1)
         send_rows = [int(v) for v in send_per_rank]
         recv_rows = [int(v) for v in recv_counts.sum(1)]
         self.last_counts = recv_counts
+        self._mark("count_exchange_and_host_read")
 
         got = self._all_to_all(send_rows_t, send_rows, recv_rows)       # dispatch: int8 rows
         got_scale = self._all_to_all(send_scale, send_rows, recv_rows)  #           fp32 scales
+        self._mark("dispatch_all_to_all")
 
         src_of_dst, group_cumsum = regroup_index(recv_counts)
         idx = torch.from_numpy(src_of_dst).to(x.device)
         xe, xe_scale = b.permute_rows(got, got_scale, idx)              # rank-major -> expert-major
         gl = [int(v) for v in group_cumsum]
+        self._mark("regroup_rows")
 
         h, hs = b.grouped_matmul_swiglu_quant(xe, self.shard.w_up, self.shard.s_up, xe_scale, gl)
+        self._mark("grouped_matmul_swiglu_quant")
         y = b.grouped_matmul_int8(h, self.shard.w_down, gl, hs, self.shard.s_down)
+        self._mark("down_projection")
 
         inv = torch.from_numpy(invert_index(src_of_dst)).to(x.device)
         y_rank_major, _ = b.permute_rows(y, None, inv)                  # expert-major -> rank-major
+        self._mark("inverse_regroup")
         back = self._all_to_all(y_rank_major, recv_rows, send_rows)     # combine transport: bf16 rows
+        self._mark("combine_all_to_all")
         out = b.combine(back, probs, pos)
+        self._mark("combine")
         return out, x_out

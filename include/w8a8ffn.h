@@ -85,6 +85,10 @@ extern "C" {
 
 /* Library identification and error text. */
 int w8a8_version(void);
+
+/* Kernels this library has launched so far in this process (every entry point counts its own launches; memsets
+ * and copies are not kernels).  Difference two readings to count the launches of a region. */
+int64_t w8a8_kernel_launch_count(void);
 const char* w8a8_status_string(int status);
 
 /*
@@ -233,6 +237,7 @@ int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y,
  * W8A8_ERR_INVALID.
  */
 int w8a8_set_gemm_shape(int shape);
+
 
 /* Reads (synchronously, on `stream`) the device-side error word a grouped
  * call left in its workspace: 0 = none, 1 = invalid device group list,
@@ -406,7 +411,11 @@ int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const fl
  * umma_m 128 or 256 (both CTAs together); umma_n a multiple of 16 (8 for
  * umma_m 64) up to 256.  accumulators = 1: every instruction adds to the
  * result of the one before it, as in a matmul's K loop; 2 or 4: successive
- * instructions add to different accumulators (umma_n x accumulators <= 512).  error_word (device, may be NULL) receives 2 if a wait
+ * instructions add to different accumulators (umma_n x accumulators <= 512).
+ * pattern varies what the issuing thread does around a batch, to price each
+ * piece: 0 = wait, instructions, commit; 1 = a second (already satisfied) wait;
+ * 2 = an extra commit after every four instructions; 3 = the cluster-scope
+ * wait plus tcgen05.fence the matmul kernels use.  error_word (device, may be NULL) receives 2 if a wait
  * ran out.  w8a8_mma_issue_probe_ops returns the integer operations one such
  * launch performs on the current device.
  *
@@ -418,8 +427,8 @@ int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const fl
  * device memory.
  */
 int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, int b_mn_major, int fill,
-                         int accumulators, int per_commit, int depth, int64_t batches, int32_t* error_word,
-                         void* stream);
+                         int accumulators, int per_commit, int depth, int pattern, int64_t batches,
+                         int32_t* error_word, void* stream);
 int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int per_commit, int64_t batches);
 int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream);
 

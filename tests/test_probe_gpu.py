@@ -44,17 +44,17 @@ def test_bounded_wait_rejects_bad_arguments():
 def test_mma_issue_probe_shapes(cg, m, n, a_mn, b_mn, acc):
     L, lib = _lib()
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, 1, acc, 4, 4, 2000, err.data_ptr(),
+    rc = lib.w8a8_mma_issue_probe(cg, m, n, a_mn, b_mn, 1, acc, 8, 4, acc % 4, 2000, err.data_ptr(),
                                   torch.cuda.current_stream().cuda_stream)
     assert rc == 0, L.status_string(rc)
     torch.cuda.synchronize()
     assert int(err[0]) == 0
-    assert lib.w8a8_mma_issue_probe_ops(cg, m, n, 4, 2000) > 0
+    assert lib.w8a8_mma_issue_probe_ops(cg, m, n, 8, 2000) > 0
 
 
 def test_mma_issue_probe_rejects_bad_shapes():
     L, lib = _lib()
     for cg, m, n in [(1, 256, 256), (2, 64, 64), (3, 128, 128), (1, 128, 264), (1, 128, 8), (2, 256, 24)]:
-        assert lib.w8a8_mma_issue_probe(cg, m, n, 0, 1, 0, 1, 4, 4, 10, None, None) == L.ERR_INVALID
-    assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 4, 4, 4, 10, None, None) == L.ERR_INVALID
-    assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 1, 4, 9, 10, None, None) == L.ERR_INVALID
+        assert lib.w8a8_mma_issue_probe(cg, m, n, 0, 1, 0, 1, 4, 4, 0, 10, None, None) == L.ERR_INVALID
+    assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 4, 4, 4, 0, 10, None, None) == L.ERR_INVALID
+    assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 1, 4, 9, 0, 10, None, None) == L.ERR_INVALID
