@@ -968,6 +968,8 @@ def measure_chain(torch, dist, rank, world, barrier, steps, peaks):
     chain.phase_hook = lambda name: marks.append((name, _event(torch)))
     phase_ms = {}
     n_prof = 3
+    wl.gpu_step()  # the instrumented path allocates its own buffers on first use: keep that out of the numbers
+    torch.cuda.synchronize()
     for _ in range(n_prof):
         marks.clear()
         barrier()
@@ -988,7 +990,10 @@ def measure_chain(torch, dist, rank, world, barrier, steps, peaks):
         overflow = True
     res = {"metric": wl.metric, "value": wl.T / (ms * 1e-3), "unit": wl.unit, "ms_per_step": ms, "ms_min": min(regions),
            "ms_max": max(regions), "config": wl.config(world), "transport": chain.transport,
-           "device_tables": bool(chain.device_tables), "launches_per_step": launches,
+           "device_tables": bool(chain.device_tables),
+           "host_code": ("one call of the library's C++ step function (w8a8_moe_ffn_step) per step"
+                         if chain._native is not None else "Python sequence of C-ABI calls"),
+           "launches_per_step": launches,
            "phases_ms_rank0": {n: round(phase_ms[n], 4) for n in names},
            "phases_ms_max_over_ranks": {n: round(v, 4) for n, v in zip(names, phase_max)},
            "receive_buffer_overflow": overflow,
@@ -1096,7 +1101,7 @@ def main():
                     help="chain workload: fused peer-memory stores or NCCL all-to-all for dispatch / combine")
     ap.add_argument("--tables", choices=["auto", "host", "device"], default="auto",
                     help="chain workload, p2p transport: where the address tables are built (device: no host "
-                         "readback in the step; auto: device from 4 ranks up)")
+                         "readback in the step, the step is one call of the library's C++ step function; auto: device)")
     ap.add_argument("--placement", choices=["replicate", "lpt"], default="replicate",
                     help="grouped workload on several GPUs: split hot experts across ranks (weights replicated) or "
                          "keep experts whole")

@@ -47,6 +47,7 @@ SIGNATURES = {
     "w8a8_grouped_matmul_swiglu_quant_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32,
                                                        _i32, _i32, _vp]),
     "w8a8_grouped_matmul_workspace_size": (_sz, [_i64, _i64, _i64, _i64]),
+    "w8a8_grouped_matmul_f32_workspace_size": (_sz, [_i64, _i64, _i64, _i64]),
     "w8a8_grouped_matmul": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32, _i32,
                                    _i32, _vp, _sz, _vp]),
     "w8a8_workspace_error": (_i32, [_vp, _vp]),
@@ -70,10 +71,26 @@ SIGNATURES = {
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "w8a8_ep_unique_id": (_i32, [_vp]),
+    "w8a8_ep_comm_create": (_i32, [_vp, _i32, _i32, ctypes.POINTER(_vp)]),
+    "w8a8_ep_comm_destroy": (_i32, [_vp]),
+    "w8a8_moe_ffn_step_workspace_size": (_sz, [_vp]),
+    "w8a8_moe_ffn_step": (_i32, [_vp, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp]),
+    "w8a8_moe_ffn_step_status": (_i32, [_vp, _vp]),
     "w8a8_mma_issue_probe": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
     "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i32, _i64]),
     "w8a8_selftest_bounded_wait": (_i32, [_i64, _vp, _vp]),
 }
+
+class MoeFfnStep(ctypes.Structure):
+    """W8A8MoeFfnStep of include/w8a8ffn.h."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("num_experts", ctypes.c_int32),
+                ("topk", ctypes.c_int32), ("dtype", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("tokens", _i64), ("hidden", _i64), ("inter", _i64), ("cap_rows", _i64), ("home_rows", _i64),
+                ("peer_base", _vp), ("local_base", _vp), ("off_x", _u64), ("off_s", _u64), ("off_back", _u64),
+                ("w_up", _vp), ("s_up", _vp), ("w_down", _vp), ("s_down", _vp), ("comm", _vp), ("workspace", _vp),
+                ("workspace_bytes", _sz)]
+
 
 _lib = None
 

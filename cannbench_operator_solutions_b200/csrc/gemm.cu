@@ -358,6 +358,66 @@ __global__ void __launch_bounds__(256) gmsq_requant_kernel(const float* __restri
 
 static inline size_t align_up_sz(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// ---------------------------------------------------------------------------
+// fp32 operands on the bf16 tensor path: v = hi + mid + lo with three bf16 pieces (8 + 8 + 8 significand bits,
+// each remainder exact in fp32), and x.w is the sum of the six piece products whose orders add up to at most two
+// (hi.hi, hi.mid, mid.hi, hi.lo, mid.mid, lo.hi; what is dropped is below 2^-24 of |x||w|).  The pieces are laid
+// out along K, small terms first, so that ONE bf16 matmul over 6K accumulates all six in fp32:
+//   x' [M, 6K]  = [ lo | mid | mid | hi | hi  | hi ]
+//   w' [.., 6K] = [ hi | mid | hi  | lo | mid | hi ]   (K-blocks of the weight's K dimension, either layout)
+// ---------------------------------------------------------------------------
+constexpr int SPLIT_TERMS = 6;
+
+__device__ __forceinline__ void split3(float v, __nv_bfloat16 (&piece)[3])
+{
+    piece[0] = __float2bfloat16_rn(v);
+    const float r1 = __fsub_rn(v, __bfloat162float(piece[0]));
+    piece[1] = __float2bfloat16_rn(r1);
+    const float r2 = __fsub_rn(r1, __bfloat162float(piece[1]));
+    piece[2] = __float2bfloat16_rn(r2);
+}
+
+// src [rows, K] fp32 -> dst [rows, 6K] bf16; which piece (0 hi, 1 mid, 2 lo) fills K-block b is pick[b]
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                         int64_t rows, int64_t K, int is_weight)
+{
+    const int pick_x[SPLIT_TERMS] = {2, 1, 1, 0, 0, 0};
+    const int pick_w[SPLIT_TERMS] = {0, 1, 0, 2, 1, 0};
+    const int64_t total = rows * K;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / K, c = i - r * K;
+        __nv_bfloat16 piece[3];
+        split3(src[i], piece);
+        __nv_bfloat16* out = dst + r * (SPLIT_TERMS * K) + c;
+#pragma unroll
+        for (int b = 0; b < SPLIT_TERMS; ++b) {
+            out[b * K] = piece[is_weight ? pick_w[b] : pick_x[b]];
+        }
+    }
+}
+
+// weight [E, K, N] fp32 (N contiguous) -> [E, 6K, N] bf16: K-block b of expert e holds piece pick_w[b]
+__global__ void __launch_bounds__(256) split_weight_kn_kernel(const float* __restrict__ src,
+                                                              __nv_bfloat16* __restrict__ dst, int64_t E, int64_t K,
+                                                              int64_t N)
+{
+    const int pick_w[SPLIT_TERMS] = {0, 1, 0, 2, 1, 0};
+    const int64_t per_expert = K * N;
+    const int64_t total = E * per_expert;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = i / per_expert, rest = i - e * per_expert;  // rest = k * N + n
+        __nv_bfloat16 piece[3];
+        split3(src[i], piece);
+        __nv_bfloat16* out = dst + e * (SPLIT_TERMS * per_expert) + rest;
+#pragma unroll
+        for (int b = 0; b < SPLIT_TERMS; ++b) {
+            out[b * per_expert] = piece[pick_w[b]];
+        }
+    }
+}
+
 struct GroupedWorkspace {
     GroupedHeader* header;
     TileEntry* tiles;
@@ -749,6 +809,17 @@ extern "C" size_t w8a8_grouped_matmul_workspace_size(int64_t M, int64_t N, int64
     return carve_workspace(nullptr, M, E, 0).total;
 }
 
+extern "C" size_t w8a8_grouped_matmul_f32_workspace_size(int64_t M, int64_t N, int64_t K, int64_t E)
+{
+    if (M < 0 || N <= 0 || K <= 0 || E <= 0) {
+        return 0;
+    }
+    const size_t base = carve_workspace(nullptr, M, E, 0).total;
+    const size_t xs = align_up_sz(static_cast<size_t>(M) * SPLIT_TERMS * K * 2, 256);
+    const size_t ws = align_up_sz(static_cast<size_t>(E) * SPLIT_TERMS * K * N * 2, 256);
+    return base + xs + ws;
+}
+
 static int grouped_matmul_impl(const void* x, const void* w, const void* bias, void* y, const uint64_t* out_row_ptrs,
                                const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
                                const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
@@ -775,7 +846,10 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
             return W8A8_ERR_INVALID;  // the reference's output takes x's dtype
         }
     } else if (dtype == W8A8_DT_F32) {
-        return W8A8_ERR_UNSUPPORTED;  // fp32 operands have no exact tensor-core path
+        kind = KIND_BF16;  // three-piece bf16 split of both operands, fp32 accumulation (see split3)
+        if (out_dtype != W8A8_DT_F32 || out_row_ptrs != nullptr) {
+            return W8A8_ERR_INVALID;
+        }
     } else {
         return W8A8_ERR_INVALID;
     }
@@ -789,6 +863,7 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
         return W8A8_ERR_INVALID;
     }
     const int elem = (kind == KIND_I8) ? 1 : 2;
+    const bool f32 = (dtype == W8A8_DT_F32);
     // the epilogue fetches per-channel operands and stores outputs in 16-column pieces
     if ((K * elem) % 16 != 0 || (N % 16) != 0) {
         return W8A8_ERR_UNSUPPORTED;
@@ -799,7 +874,8 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
     if (M >= (int64_t(1) << 31) - 256 || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) {
         return W8A8_ERR_UNSUPPORTED;
     }
-    const size_t need = w8a8_grouped_matmul_workspace_size(M, N, K, E);
+    const size_t need = f32 ? w8a8_grouped_matmul_f32_workspace_size(M, N, K, E)
+                            : w8a8_grouped_matmul_workspace_size(M, N, K, E);
     if (workspace == nullptr || workspace_bytes < need) {
         return W8A8_ERR_WORKSPACE;
     }
@@ -813,6 +889,29 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
         return list_rc;
     }
     const bool b_mn = (w_layout == W8A8_W_KN);
+    if (f32) {
+        // split both operands into bf16 pieces laid out along K (6K in all), then run the bf16 path on them
+        if (SPLIT_TERMS * K >= (int64_t(1) << 31)) {
+            return W8A8_ERR_UNSUPPORTED;
+        }
+        uint8_t* base = static_cast<uint8_t*>(workspace) + g.total;
+        __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base);
+        __nv_bfloat16* wsplit =
+            reinterpret_cast<__nv_bfloat16*>(base + align_up_sz(static_cast<size_t>(M) * SPLIT_TERMS * K * 2, 256));
+        const unsigned grid = static_cast<unsigned>(sm_count()) * 8;
+        split_rows_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(x), xs, M, K, 0); w8a8::note_launch();
+        if (b_mn) {
+            split_weight_kn_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(w), wsplit, E, K, N); w8a8::note_launch();
+        } else {
+            split_rows_kernel<<<grid, 256, 0, st>>>(static_cast<const float*>(w), wsplit, E * N, K, 1); w8a8::note_launch();
+        }
+        if (cudaGetLastError() != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
+        x = xs;
+        w = wsplit;
+        K = SPLIT_TERMS * K;
+    }
     CUtensorMap ta, tb;
     if (!make_map_a(&ta, x, M, K, kind) || !make_map_b(&tb, w, E, N, K, kind, b_mn)) {
         return W8A8_ERR_CUDA;

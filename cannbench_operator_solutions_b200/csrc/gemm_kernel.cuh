@@ -297,7 +297,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
             }
         }
         constexpr int HALF_COLS = BLOCK_N / 2;
-        // byte address of this thread's output row (16-bit outputs)
+        // byte address of this thread's output row (16-bit outputs; fp32 outputs are addressed where they are stored)
         uint64_t row_ptr = reinterpret_cast<uint64_t>(p.out) + static_cast<uint64_t>(row) * p.N * 2;
         if constexpr (EPI == EPI_GMM) {
             if (p.out_row_ptrs != nullptr) {
@@ -387,6 +387,22 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
                         for (int j = 0; j < 32; ++j) {
                             v[j] = __fadd_rn(v[j], w[j]);
                         }
+                    }
+                }
+                if constexpr (EPI == EPI_GMM && KIND == KIND_BF16) {
+                    if (p.out_dtype == W8A8_DT_F32) {
+                        // fp32 output (the split-operand path): 32 values are one whole 128-byte line of the row
+                        if (row_ok) {
+                            float* dst = static_cast<float*>(p.out) + row * p.N + col0;
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                if (q * 4 < valid) {
+                                    *reinterpret_cast<float4*>(dst + q * 4) =
+                                        make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                                }
+                            }
+                        }
+                        continue;
                     }
                 }
                 // 32 outputs = 64 bytes of this thread's row.  They are not stored from here (every lane would

@@ -441,7 +441,8 @@ struct GroupedMatmul {
         call.require(!b.defined() || b.numel() == e * n, "grouped_matmul: bias must have shape [E, N]");
         const Tensor y = joined(rows, w, transpose_weight, x_scale);
         if (m > 0) {
-            const size_t bytes = w8a8_grouped_matmul_workspace_size(m, n, k, e);
+            const size_t bytes = (type_bit(rows) == F32) ? w8a8_grouped_matmul_f32_workspace_size(m, n, k, e)
+                                                         : w8a8_grouped_matmul_workspace_size(m, n, k, e);
             const Tensor ws_buf = call.scratch(bytes, rows);
             call.done(w8a8_grouped_matmul(rows.data_ptr(), w.data_ptr(), Call::ptr(b), y.data_ptr(),
                                           Call::as<const float>(xs), Call::as<const float>(ws), m, n, k, e,

@@ -267,7 +267,8 @@ class PeerBuffers:
 
 class MoeFfnChain:
     def __init__(self, num_experts: int, shard: ExpertShard, backend=None, group=None, transport: str = "nccl",
-                 capacity_rows: Optional[int] = None, device_tables: Optional[bool] = None):
+                 capacity_rows: Optional[int] = None, device_tables: Optional[bool] = None,
+                 native_step: Optional[bool] = None):
         self.group = group
         if transport not in ("nccl", "p2p"):
             raise ValueError("transport must be 'nccl' or 'p2p'")
@@ -279,10 +280,9 @@ class MoeFfnChain:
         self._dev_state = None
         self.peer: Optional[PeerBuffers] = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        # Default: device tables from 4 ranks up.  Measured per step: 8 GPUs 4.16 ms against 4.34 ms with the
-        # host readback; 2 GPUs 13.30 against 13.38 ms; one GPU, where the step is bound by the power cap and
-        # the readback's idle gap costs nothing, 4.90 against 4.70 ms.
-        self.device_tables = (self.world >= 4) if device_tables is None else bool(device_tables)
+        # Default: tables built on the device at every rank count, so that no step ever waits for the host (with
+        # the host readback the step was 4 % slower on 8 GPUs and equal within noise on 1 and 2).
+        self.device_tables = True if device_tables is None else bool(device_tables)
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if num_experts % self.world != 0:
             raise ValueError("the expert count must be divisible by the number of ranks")
@@ -292,6 +292,11 @@ class MoeFfnChain:
             raise ValueError("expert shard does not match E / world_size")
         self.shard = shard
         self.backend = backend if backend is not None else CudaBackend()
+        # p2p transport with device-built tables: the whole step is ONE call of the library's C++ step function
+        # (w8a8_moe_ffn_step, with its own NCCL communicator for the count all-gather and the barriers); the
+        # Python sequence of the same calls stays for injected backends (the CPU tests) and for comparison
+        self.native_step = (backend is None) if native_step is None else bool(native_step)
+        self._native = None
         self.last_counts: Optional[np.ndarray] = None
         # measurement hook: called with a phase name after each phase of a step has been enqueued (the benchmark
         # records a CUDA event there); None in normal use
@@ -406,6 +411,83 @@ class MoeFfnChain:
         self._mark("combine")
         return out, x_out
 
+    # -- the step as one C++ call ---------------------------------------------------------------------------
+    def _native_state(self, x, expert_idx):
+        """Peer buffers, the library's NCCL communicator, the step descriptor and its workspace (made once)."""
+        from . import _lib as L
+        import ctypes
+
+        t, topk = expert_idx.shape
+        hidden = x.shape[1]
+        dev = x.device
+        key = (t, topk, hidden, x.dtype)
+        if self._native is not None and self._native["key"] == key:
+            return self._native
+        lib = L.load()
+        if self.peer is None:
+            cap = self.capacity_rows
+            if cap is None:
+                cap = int(1.5 * t * topk) + 1024
+            self.peer = PeerBuffers(cap, hidden, t * topk, dev, self.world, self.group)
+        pb = self.peer
+        comm = ctypes.c_void_p(None)
+        if self.world > 1:
+            if self._native is not None:
+                comm = self._native["comm"]
+            else:
+                ident = torch.zeros((128,), dtype=torch.uint8, device=dev)
+                if self.rank == 0:
+                    raw = (ctypes.c_uint8 * 128)()
+                    rc = lib.w8a8_ep_unique_id(raw)
+                    if rc != 0:
+                        raise RuntimeError(f"ep_unique_id: {L.status_string(rc)}")
+                    ident.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+                src = dist.get_global_rank(self.group, 0) if self.group is not None else 0
+                dist.broadcast(ident, src=src, group=self.group)
+                raw = (ctypes.c_uint8 * 128)(*ident.cpu().tolist())
+                with torch.cuda.device(dev):
+                    rc = lib.w8a8_ep_comm_create(raw, self.world, self.rank, ctypes.byref(comm))
+                if rc != 0:
+                    raise RuntimeError(f"ep_comm_create: {L.status_string(rc)}")
+        peer_base = torch.tensor([int(p) for p in pb.ptrs], dtype=torch.int64, device=dev)
+        step = L.MoeFfnStep()
+        step.world, step.rank, step.num_experts, step.topk = self.world, self.rank, self.E, topk
+        step.dtype = L.DT_BF16 if x.dtype == torch.bfloat16 else L.DT_F16
+        step.tokens, step.hidden, step.inter = t, hidden, self.shard.w_down.shape[1]
+        step.cap_rows, step.home_rows = pb.cap_rows, pb.home_rows
+        step.peer_base, step.local_base = peer_base.data_ptr(), pb.buf.data_ptr()
+        step.off_x, step.off_s, step.off_back = pb.off_x, pb.off_s, pb.off_back
+        step.w_up, step.s_up = self.shard.w_up.data_ptr(), self.shard.s_up.data_ptr()
+        step.w_down, step.s_down = self.shard.w_down.data_ptr(), self.shard.s_down.data_ptr()
+        step.comm = comm
+        step.workspace, step.workspace_bytes = None, 0
+        need = lib.w8a8_moe_ffn_step_workspace_size(ctypes.byref(step))
+        if need == 0:
+            raise RuntimeError("moe_ffn_step: invalid step description")
+        ws = torch.zeros((need,), dtype=torch.uint8, device=dev)
+        step.workspace, step.workspace_bytes = ws.data_ptr(), need
+        self._native = {"key": key, "step": step, "workspace": ws, "peer_base": peer_base, "comm": comm, "lib": lib,
+                        "L": L}
+        return self._native
+
+    def _forward_native(self, x, residual, gamma, eps, expert_idx, probs):
+        import ctypes
+
+        st = self._native_state(x, expert_idx)
+        for tns in (x, residual, gamma, expert_idx, probs):
+            if not tns.is_contiguous():
+                raise ValueError("the step takes contiguous tensors")
+        out = torch.empty_like(x)
+        x_out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            rc = st["lib"].w8a8_moe_ffn_step(ctypes.byref(st["step"]), x.data_ptr(), residual.data_ptr(),
+                                             gamma.data_ptr(), float(eps), expert_idx.data_ptr(), probs.data_ptr(),
+                                             out.data_ptr(), x_out.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise RuntimeError(f"moe_ffn_step: {st['L'].status_string(rc)}")
+        return out, x_out
+
     def _forward_p2p_device_tables(self, x, residual, gamma, eps, expert_idx, probs):
         """The p2p step with no host readback: count all-gather -> ep_tables kernel -> dispatch -> grouped matmuls
         on the capacity with a device group list -> combine.  `check()` reads the overflow flag when asked."""
@@ -479,6 +561,16 @@ class MoeFfnChain:
         if self._dev_state is not None and int(self._dev_state["status"][0].item()) != 0:
             self._dev_state["status"].zero_()
             raise RuntimeError("expert-parallel receive buffer too small for this routing: raise capacity_rows")
+        if self._native is not None:
+            import ctypes
+
+            with torch.cuda.device(self._native["workspace"].device):
+                rc = self._native["lib"].w8a8_moe_ffn_step_status(ctypes.byref(self._native["step"]),
+                                                                  torch.cuda.current_stream().cuda_stream)
+            if rc == 1:
+                raise RuntimeError("expert-parallel receive buffer too small for this routing: raise capacity_rows")
+            if rc != 0:
+                raise RuntimeError(f"moe_ffn_step_status: {self._native['L'].status_string(rc)}")
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, gamma: torch.Tensor, eps: float,
                 expert_idx: torch.Tensor, probs: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -486,6 +578,8 @@ class MoeFfnChain:
         Returns (ffn_out [T_local, hidden], residual_out [T_local, hidden])."""
         if self.transport == "p2p":
             if self.device_tables:
+                if self.native_step and self.phase_hook is None:
+                    return self._forward_native(x, residual, gamma, eps, expert_idx, probs)
                 return self._forward_p2p_device_tables(x, residual, gamma, eps, expert_idx, probs)
             return self._forward_p2p(x, residual, gamma, eps, expert_idx, probs)
         b = self.backend

@@ -291,7 +291,8 @@ def grouped_matmul(x: torch.Tensor, weight: torch.Tensor, group_list: GroupList,
     y = torch.empty((m, n), dtype=out_dtype, device=xc.device)
     if m > 0:
         lib = L.load()
-        need = lib.w8a8_grouped_matmul_workspace_size(m, n, k, e)
+        need = (lib.w8a8_grouped_matmul_f32_workspace_size(m, n, k, e) if dt == L.DT_F32
+                else lib.w8a8_grouped_matmul_workspace_size(m, n, k, e))
         if workspace is None:
             workspace = torch.empty((max(need, 1),), dtype=torch.uint8, device=xc.device)
         _check(workspace.numel() * workspace.element_size() >= need, "grouped_matmul: workspace too small")

@@ -217,12 +217,18 @@ int w8a8_grouped_matmul_swiglu_quant_static(const int8_t* x, const int8_t* w, co
  * (operators/groupedmatmul/csrc/ops/grouped_matmul/op_kernel/grouped_matmul_launch.h:50-71).
  *   dtype F16 / BF16: the reference's float path, fp32 accumulate, output in
  *   dtype (x_scale, w_scale NULL).
+ *   dtype F32 (the reference's GMM_DT_FLOAT): both operands are split into
+ *   three bf16 pieces each and the six leading piece products are accumulated
+ *   in fp32 on the bf16 tensor path (what is dropped is below 2^-24 of
+ *   |x||w|); output and bias F32; needs the larger workspace of
+ *   w8a8_grouped_matmul_f32_workspace_size (room for the split operands).
  *   dtype I8: the quantised down projection the reference operator lacks:
  *   int32 accumulate, (float(acc) * w_scale[g, n]) * x_scale[m] (+ bias),
  *   rounded to out_dtype.
  * group_list as for grouped_matmul_swiglu_quant.
  */
 size_t w8a8_grouped_matmul_workspace_size(int64_t M, int64_t N, int64_t K, int64_t E);
+size_t w8a8_grouped_matmul_f32_workspace_size(int64_t M, int64_t N, int64_t K, int64_t E);
 int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y,
                         const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K,
                         int64_t E, const int64_t* group_list, int list_on_device, int dtype,
@@ -394,6 +400,61 @@ int w8a8_moe_gating_top_k_softmax(const void* x, const uint8_t* finished, void* 
 int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const float* activation_scale,
                               const float* quant_scale, int8_t* y, float* scale, int64_t M, int64_t H,
                               int x_dtype, int activate_left, int flags, void* stream);
+
+/*
+ * The whole expert-parallel MoE FFN step as one host call (no reference counterpart: the reference is
+ * single-device and has no step function; this is the C++ host side of benchmark configuration 5).  One call
+ * enqueues on `stream`, with no host readback: add_rms_norm_dynamic_quant -> w8a8_route_plan -> all-gather of the
+ * per-expert counts -> w8a8_ep_tables -> w8a8_dispatch_rows (rows stored straight into the owning rank's
+ * expert-major buffer) -> barrier -> grouped_matmul_swiglu_quant -> w8a8_grouped_matmul_to_rows (int8 down
+ * projection whose epilogue stores each row where its home rank's combine reads it) -> barrier -> w8a8_combine.
+ * Rank r owns tokens [r * tokens, (r + 1) * tokens) and experts [r * E / world, (r + 1) * E / world).
+ *
+ * Every rank owns one buffer laid out as int8 rows [cap_rows, hidden] at off_x, fp32 row scales [cap_rows] at off_s
+ * and 16-bit return rows [home_rows, hidden] at off_back; peer_base (a device array of `world` addresses) says where
+ * each rank's buffer is mapped in this rank's address space, local_base is this rank's own buffer.  Those mappings
+ * (CUDA IPC, virtual memory management, torch symmetric memory ...) are the caller's business; this library only
+ * stores through them.
+ *
+ * Collectives (the count all-gather and two one-word all-reduces used as stream-ordered barriers) run on an NCCL
+ * communicator made by w8a8_ep_comm_create: rank 0 calls w8a8_ep_unique_id, hands the 128 bytes to every rank by
+ * any means, every rank calls w8a8_ep_comm_create.  NCCL is looked up in the process at that moment (no link-time
+ * dependency): W8A8_ERR_UNSUPPORTED when it is not there.  world == 1 needs no communicator (comm NULL).
+ *
+ * A step that routes more than cap_rows rows to some rank stores nothing out of bounds: that step's tables are
+ * zeroed, its output is meaningless, and a sticky flag is raised that w8a8_moe_ffn_step_status reads and clears
+ * (returns 1; it synchronises the stream).  Every rank must make the same sequence of step calls.
+ */
+typedef struct W8A8MoeFfnStep {
+    int32_t world, rank;
+    int32_t num_experts; /* global; a multiple of world */
+    int32_t topk;
+    int32_t dtype;       /* W8A8_DT_F16 / W8A8_DT_BF16: x, residual, gamma, outputs */
+    int32_t reserved;
+    int64_t tokens;      /* rows of x on this rank */
+    int64_t hidden, inter;
+    int64_t cap_rows;    /* rows every rank's receive buffer holds */
+    int64_t home_rows;   /* rows every rank's return buffer holds (>= tokens * topk) */
+    const uint64_t* peer_base; /* device array [world] */
+    void* local_base;
+    uint64_t off_x, off_s, off_back;
+    const int8_t* w_up;   /* [E / world, hidden, 2 * inter] */
+    const float* s_up;    /* [E / world, 2 * inter] */
+    const int8_t* w_down; /* [E / world, inter, hidden] */
+    const float* s_down;  /* [E / world, hidden] */
+    void* comm;           /* from w8a8_ep_comm_create; NULL when world == 1 */
+    void* workspace;      /* device, w8a8_moe_ffn_step_workspace_size bytes, zeroed once before the first step */
+    size_t workspace_bytes;
+} W8A8MoeFfnStep;
+
+int w8a8_ep_unique_id(void* id128);
+int w8a8_ep_comm_create(const void* id128, int world, int rank, void** comm);
+int w8a8_ep_comm_destroy(void* comm);
+size_t w8a8_moe_ffn_step_workspace_size(const W8A8MoeFfnStep* step);
+int w8a8_moe_ffn_step(const W8A8MoeFfnStep* step, const void* x, const void* residual, const void* gamma,
+                      float epsilon, const int32_t* expert_idx, const float* probs, void* out, void* x_out,
+                      void* stream);
+int w8a8_moe_ffn_step_status(const W8A8MoeFfnStep* step, void* stream);
 
 /*
  * Measurement and self-test entry points of the tensor-core layer.  (No

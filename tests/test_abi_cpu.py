@@ -83,8 +83,13 @@ def test_argument_validation_needs_no_gpu(lib):
                                                 None) == L.OK
     assert lib.w8a8_grouped_matmul(p, p, None, p, None, None, 8, 64, 32, 2, gl_ok, 0, L.DT_I8, 0, L.DT_BF16, L.W_KN,
                                    p, 1 << 30, None) == L.ERR_INVALID  # int8 needs scales
+    # fp32 operands answer in fp32 only, and need the larger workspace that holds their bf16 pieces
+    assert lib.w8a8_grouped_matmul(p, p, None, p, None, None, 8, 64, 32, 2, gl_ok, 0, L.DT_F32, 0, L.DT_BF16, L.W_KN,
+                                   p, 1 << 30, None) == L.ERR_INVALID
+    small = lib.w8a8_grouped_matmul_workspace_size(8, 64, 32, 2)
+    assert lib.w8a8_grouped_matmul_f32_workspace_size(8, 64, 32, 2) > small
     assert lib.w8a8_grouped_matmul(p, p, None, p, None, None, 8, 64, 32, 2, gl_ok, 0, L.DT_F32, 0, L.DT_F32, L.W_KN,
-                                   p, 1 << 30, None) == L.ERR_UNSUPPORTED
+                                   p, small, None) == L.ERR_WORKSPACE
     assert lib.w8a8_grouped_matmul(p, p, None, p, p, p, 8, 64, 32, 2, gl_bad, 0, L.DT_I8, 0, L.DT_BF16, L.W_KN,
                                    p, 1 << 30, None) == L.ERR_GROUP_LIST
     assert lib.w8a8_route_plan(p, 4, 2, 8, p, p, p, p, 16, None) == L.ERR_WORKSPACE

@@ -104,10 +104,50 @@ def test_single_gpu_chain_peer_transport_equals_collective_transport(ops):
         b, bx = chain.forward(*args)
         assert torch.equal(a, b) and torch.equal(ax, bx)
     chain.check()
-    tight = MoeFfnChain(experts, shard, transport="p2p", device_tables=True, capacity_rows=256)   # 1200 rows routed
-    tight.forward(*args)
-    with pytest.raises(RuntimeError, match="too small"):
-        tight.check()
+    assert chain._native is not None  # that was the library's C++ step function (one call per step)
+    # ... and as the Python sequence of the same library calls
+    chain = MoeFfnChain(experts, shard, transport="p2p", device_tables=True, native_step=False)
+    for _ in range(2):
+        b, bx = chain.forward(*args)
+        assert torch.equal(a, b) and torch.equal(ax, bx)
+    chain.check()
+    assert chain._native is None
+    for native in (True, False):
+        tight = MoeFfnChain(experts, shard, transport="p2p", device_tables=True, capacity_rows=256,
+                            native_step=native)   # 1200 rows routed
+        tight.forward(*args)
+        with pytest.raises(RuntimeError, match="too small"):
+            tight.check()
+        tight.check()  # the flag was cleared by the read
+        # an overflow is not forgotten when a later step fits (the flag is sticky until it is read)
+        tight.forward(*args)
+        small = tuple(t[:40].contiguous() if i in (0, 1, 4, 5) else t for i, t in enumerate(args))
+        if not native:  # the C++ step is built for one token count; the Python sequence takes any
+            tight.forward(*small)
+        with pytest.raises(RuntimeError, match="too small"):
+            tight.check()
+
+
+def test_moe_ffn_step_argument_checks(ops):
+    """The C++ step function validates its description before it touches the GPU."""
+    import ctypes
+
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    step = L.MoeFfnStep()
+    assert lib.w8a8_moe_ffn_step_workspace_size(ctypes.byref(step)) == 0
+    step.world, step.rank, step.num_experts, step.topk, step.dtype = 1, 0, 8, 2, L.DT_BF16
+    step.tokens, step.hidden, step.inter, step.cap_rows, step.home_rows = 16, 64, 32, 64, 32
+    need = lib.w8a8_moe_ffn_step_workspace_size(ctypes.byref(step))
+    assert need > 16 * 64
+    p = 4096
+    assert lib.w8a8_moe_ffn_step(ctypes.byref(step), p, p, p, 1e-6, p, p, p, p, None) == L.ERR_INVALID  # no buffers
+    step.num_experts = 7
+    step.world = 2
+    assert lib.w8a8_moe_ffn_step_workspace_size(ctypes.byref(step)) == 0  # experts not divisible by ranks
+    assert lib.w8a8_ep_comm_create(None, 2, 0, None) == L.ERR_INVALID
+    assert lib.w8a8_ep_comm_destroy(None) == L.OK
 
 
 @pytest.mark.parametrize("tok_dtype", [torch.int8, torch.bfloat16, torch.float16])

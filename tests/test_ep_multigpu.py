@@ -16,6 +16,11 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
         sys.path.insert(0, p)
 
 
+# the NCCL all-to-all transport; peer stores with host-built tables; peer stores with device-built tables as one call
+# of the library's C++ step function (its own NCCL communicator), and as the Python sequence of the same calls
+TRANSPORTS = ("nccl", "p2p", "p2p-device-tables", "p2p-device-tables-python")
+
+
 def _worker(rank, world, port, experts, ret):
     import torch.distributed as dist
 
@@ -39,9 +44,10 @@ def _worker(rank, world, port, experts, ret):
         args = (x[st].contiguous().to(dev), res[st].contiguous().to(dev), gamma.to(dev), 1e-6,
                 idx[st].contiguous().to(dev), probs[st].contiguous().to(dev))
         out = {}
-        for transport in ("nccl", "p2p", "p2p-device-tables"):
+        for transport in TRANSPORTS:
             chain = MoeFfnChain(experts, shard, transport=transport.split("-")[0],
-                                device_tables=transport.endswith("device-tables"))
+                                device_tables="device-tables" in transport,
+                                native_step=not transport.endswith("python"))
             for _ in range(2):
                 o, xo = chain.forward(*args)
             torch.cuda.synchronize()
@@ -76,7 +82,7 @@ def test_two_gpu_chain_both_transports_equal_single_rank(ops):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, port, experts, ret), nprocs=2, join=True)
-    for transport in ("nccl", "p2p", "p2p-device-tables"):
+    for transport in TRANSPORTS:
         got = np.concatenate([ret[r][transport][0] for r in range(2)], 0)
         got_x = np.concatenate([ret[r][transport][1] for r in range(2)], 0)
         assert np.array_equal(got_x, want_x), transport

@@ -297,6 +297,44 @@ def test_grouped_matmul_float_path(ops, oracle, dtype, layout_nk):
     assert err <= ref.abs().max().item() * 2.0**-7, err
 
 
+@pytest.mark.parametrize("layout_nk", [False, True])
+def test_grouped_matmul_fp32_operands(ops, layout_nk):
+    """fp32 x and weight (the reference's GMM_DT_FLOAT dispatch): three-piece bf16 split of both operands on the
+    tensor cores, fp32 accumulation.  Against the fp64 product the error stays within 2^-20 of the largest output
+    (fp32 rounding of a 320-term sum; a plain bf16 or tf32 product would miss this bound by orders of magnitude)."""
+    rng = np.random.default_rng(17)
+    m, k, n, e = 300, 320, 272, 4
+    gl = [130, 130, 171, 300]
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(F)).cuda()
+    w = torch.from_numpy((rng.standard_normal((e, k, n)) * 0.1).astype(F)).cuda()
+    bias = torch.from_numpy(rng.standard_normal((e, n)).astype(F)).cuda()
+    wt = w.transpose(1, 2).contiguous() if layout_nk else w
+    out = ops.grouped_matmul(x, wt, gl, bias, 2, layout_nk)[0]
+    assert out.dtype == torch.float32 and out.shape == (m, n)
+    xf, wf, bf = x.double().cpu(), w.double().cpu(), bias.double().cpu()
+    ref = torch.empty((m, n), dtype=torch.float64)
+    start = 0
+    for g, end in enumerate(gl):
+        ref[start:end] = xf[start:end] @ wf[g] + bf[g]
+        start = end
+    err = (out.double().cpu() - ref).abs().max().item()
+    assert err <= ref.abs().max().item() * 2.0**-20, err
+    views = ops.grouped_matmul(x, wt, gl, None, 0, layout_nk)
+    assert [v.shape[0] for v in views] == [130, 0, 41, 129]
+
+
+def test_grouped_matmul_float_rejects_partial_column_chunks(ops):
+    """The epilogue moves per-channel operands and outputs in 16-column pieces: N must be a multiple of 16 for
+    every operand type (N = 24 used to slip through for 16-bit operands and lose the bias of its last columns)."""
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    x = torch.zeros((8, 32), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((1, 32, 24), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="not supported"):
+        ops.grouped_matmul(x, w, [8], None, 2, False)
+    assert L.ERR_UNSUPPORTED == -6
+
+
 def test_quant_matmul_full_size_sampled_rows(ops, oracle, cta_group):
     """Benchmark configuration 3 at full size (M=8192, K=7168, N=18432): rows sampled across all row tiles are
     compared bit for bit with the oracle, and the remaining rows through linearity in the per-token scale."""
