@@ -359,8 +359,6 @@ class GmsqWorkload(Workload):
         row-max epilogue)."""
         self._call(self.L.F_STAGE_MATMUL)
 
-    kernels_per_step = 5  # two tile-table planners, pair-tile matmul, single-tile matmul, requant (+ one memset)
-
     def ops_per_step(self):
         return 2.0 * self.m * self.K * self.N
 
@@ -400,7 +398,7 @@ class GmsqWorkload(Workload):
 
 class QmmWorkload(Workload):
     """Benchmark configuration 3 of 5, M = 8192: dense W8A8 matmul K=7168 N=18432, bf16 output."""
-    name, metric, unit, dtype, bound = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "int8", "tensor"
+    name, metric, unit, dtype = "quant_matmul", "quant_matmul_int8_tops", "TOPS", "int8"
     M, K, N = 8192, 7168, 18432
     kernels_per_step = 1
 
@@ -438,7 +436,15 @@ class QmmWorkload(Workload):
     def units_per_step(self):
         return 2.0 * self.M * self.K * self.n / 1e12
 
+    @property
+    def bound(self):
+        """With few rows the operator streams the weights once and little else: HBM-bound (245 operations per byte
+        at M = 128 against a machine balance of about 500)."""
+        return "hbm" if self.M <= 256 else "tensor"
+
     def roofline_units(self):
+        if self.bound == "hbm":  # algorithmic bytes: x, weights, scales, output
+            return (self.M * self.K + self.K * self.n + 4 * self.n + 4 * self.M + 2 * self.M * self.n) / 1e9
         return self.units_per_step()
 
     def host_inputs(self):
@@ -1107,6 +1113,9 @@ def main():
                          "keep experts whole")
     ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                     help="time the K steps as one CUDA-graph replay (auto: the bandwidth-bound workloads)")
+    ap.add_argument("--gmsq-requant", choices=["two-kernel", "fused"], default="two-kernel",
+                    help="grouped workload: requantise in a second kernel (the library's default) or inside the "
+                         "matmul kernels (w8a8_set_gmsq_fused_requant)")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of K steps each; the median is reported")
     ap.add_argument("--no-secondary", action="store_true",
                     help="default workload only: skip the other operators of the path and the chain")
@@ -1149,6 +1158,10 @@ def main():
         torch.cuda.synchronize()
 
     wl.gpu_setup(torch, rank, world)
+    if args.gmsq_requant == "fused":
+        from cannbench_operator_solutions_b200 import _lib as _L
+
+        _L.load().w8a8_set_gmsq_fused_requant(1)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

@@ -154,6 +154,7 @@ static cudaError_t dispatch_gemm(int cta_group, int block_n, bool b_mn, const CU
 // tests use it to run every case on every shape.
 constexpr int GEMM_SHAPE_HYBRID = 3;
 static std::atomic<int> g_shape_override{0};
+static std::atomic<int> g_fuse_requant{0};  // see w8a8_set_gmsq_fused_requant
 
 static int choose_cta_group(int64_t rows, bool grouped)
 {
@@ -429,6 +430,11 @@ struct GroupedWorkspace {
     GroupedHeader* tail_header;
     TileEntry* tail_tiles;
     int64_t tail_max_tiles;
+    // finished-column-tile counters of the fused requantisation, one per (row tile, CTA of the tile): for the first
+    // table, then for the tail table; they follow the row maxima so that one memset clears both
+    int32_t* tile_done;
+    int32_t* tail_tile_done;
+    size_t clear_bytes;  // from `amax`: row maxima + counters
     size_t total;
 };
 
@@ -443,7 +449,13 @@ static GroupedWorkspace carve_workspace(void* ws, int64_t M, int64_t E, int64_t 
     g.tiles = reinterpret_cast<TileEntry*>(p + off);
     off += align_up_sz(static_cast<size_t>(g.max_tiles) * sizeof(TileEntry), 256);
     g.amax = reinterpret_cast<uint32_t*>(p + off);
+    const size_t clear_from = off;
     off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * sizeof(uint32_t), 256) : 0;
+    g.tile_done = reinterpret_cast<int32_t*>(p + off);
+    off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(g.max_tiles) * 2 * sizeof(int32_t), 256) : 0;
+    g.tail_tile_done = reinterpret_cast<int32_t*>(p + off);
+    off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(E + 1) * 2 * sizeof(int32_t), 256) : 0;
+    g.clear_bytes = off - clear_from;
     g.act = reinterpret_cast<float*>(p + off);
     off += (act_cols > 0) ? align_up_sz(static_cast<size_t>(M) * act_cols * sizeof(float), 256) : 0;
     g.tail_header = reinterpret_cast<GroupedHeader*>(p + off);
@@ -541,6 +553,7 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
         }
         p.tiles = g.tiles;
         p.header = g.header;
+        p.tile_done = g.tile_done;
         const cudaError_t e = dispatch_gemm<KIND, EPI>(shape, 256, b_mn, ta, tb, p, g.max_tiles * p.n_tiles, st);
         return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
     }
@@ -554,12 +567,14 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
     }
     p.tiles = g.tiles;
     p.header = g.header;
+    p.tile_done = g.tile_done;
     cudaError_t e = dispatch_gemm<KIND, EPI>(2, 256, b_mn, ta, tb, p, (M / 256 + E + 1) * p.n_tiles, st);
     if (e != cudaSuccess) {
         return W8A8_ERR_CUDA;
     }
     p.tiles = g.tail_tiles;
     p.header = g.tail_header;
+    p.tile_done = g.tail_tile_done;
     e = dispatch_gemm<KIND, EPI>(1, 256, b_mn, ta, tb, p, g.tail_max_tiles * p.n_tiles, st);
     return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
@@ -748,12 +763,14 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const GroupedWorkspace g = carve_workspace(workspace, M, E, H);
+    bool fused = false;
     if (run_matmul) {
         const int list_rc = check_host_group_list(group_list, list_on_device, E, M);
         if (list_rc != W8A8_OK) {
             return list_rc;
         }
-        if (cudaMemsetAsync(g.amax, 0, static_cast<size_t>(M) * sizeof(uint32_t), st) != cudaSuccess) {
+        // row maxima and finished-tile counters start at zero
+        if (cudaMemsetAsync(g.amax, 0, g.clear_bytes, st) != cudaSuccess) {
             return W8A8_ERR_CUDA;
         }
         const bool b_mn = (w_layout == W8A8_W_KN);
@@ -772,12 +789,19 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.row_scale = x_scale;
         p.act = g.act;
         p.amax = g.amax;
+        // Optional (off by default, it measures slower): the matmul kernels quantise each row block themselves as
+        // soon as its last column tile is done, and no second kernel runs.
+        p.fuse_requant = (run_requant && g_fuse_requant.load(std::memory_order_relaxed)) ? 1 : 0;
+        p.y = y;
+        p.y_scale = y_scale;
+        p.round_direct = (flags & W8A8_F_ROUND_DIRECT) ? 1 : 0;
+        fused = p.fuse_requant != 0;
         const int rc = run_grouped<KIND_I8, EPI_GMSQ>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
         if (rc != W8A8_OK) {
             return rc;
         }
     }
-    if (!run_requant) {
+    if (!run_requant || fused) {
         return W8A8_OK;
     }
     const int64_t warps_needed = M;
@@ -976,6 +1000,11 @@ extern "C" int w8a8_pipeline_error(void* stream)
         return W8A8_ERR_CUDA;
     }
     return v;
+}
+
+extern "C" int w8a8_set_gmsq_fused_requant(int on)
+{
+    return g_fuse_requant.exchange(on ? 1 : 0, std::memory_order_relaxed);
 }
 
 extern "C" int w8a8_set_gemm_shape(int shape)

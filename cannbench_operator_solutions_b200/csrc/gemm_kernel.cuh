@@ -108,6 +108,12 @@ struct GemmParams {
     int32_t a_box_bytes;  // bytes one A load delivers: GEMM_A_BYTES, or less when the A map's box has fewer rows
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
+    // GMSQ with the requantisation fused in: the CTA that finishes the last column tile of its rows quantises them
+    int32_t* tile_done;   // per (row tile, CTA of the tile): column tiles finished so far (zeroed by the caller)
+    int8_t* y;            // [M, N/2]
+    float* y_scale;       // [M]
+    int32_t fuse_requant;
+    int32_t round_direct;
 };
 
 __device__ __forceinline__ float vec_elem_as_float(const void* p, int64_t i, int kind)
@@ -180,11 +186,69 @@ __device__ __forceinline__ void load_vec32(const void* base, int64_t idx0, int k
 }
 
 
+// Requantisation of `rows` finished rows of SwiGLU activations starting at `row0` by the eight epilogue warps of
+// one CTA (warp w takes rows w, w + 8, ...): amax clamp at FLT_MIN, y_scale = amax * (1/127), inv = 127 / amax,
+// clamp to [-128, 127], narrowing (gmsq_vec_kernel.cpp:233-257).  The activations and row maxima were written
+// by other SMs: they are read through L2 (ld.global.cg), never through this SM's L1.
+template <bool DIRECT>
+__device__ __forceinline__ void requant_rows(const float* act, const uint32_t* amax_bits, int8_t* y, float* y_scale,
+                                             int64_t row0, int rows, int64_t H, int warp_in_group, int lane)
+{
+    const int64_t n4 = H / 4;
+    for (int r = warp_in_group; r < rows; r += 8) {
+        const int64_t row = row0 + r;
+        float amax = __uint_as_float(__ldcg(amax_bits + row));
+        if (!(amax > 1.1754944e-38f)) {
+            amax = 1.1754944e-38f;
+        }
+        if (lane == 0) {
+            y_scale[row] = __fmul_rn(amax, INV127);
+        }
+        const float inv = __fdiv_rn(127.0f, amax);
+        const float4* src = reinterpret_cast<const float4*>(act + row * H);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(y + row * H);
+        // eight independent 16-byte loads in flight per lane: only eight warps work here, and a load at a time
+        // would leave them waiting on L2 latency
+        constexpr int DEPTH = 8;
+        for (int64_t c0 = 0; c0 < n4; c0 += 32 * DEPTH) {
+            float4 a[DEPTH];
+#pragma unroll
+            for (int j = 0; j < DEPTH; ++j) {
+                const int64_t c = c0 + lane + 32 * j;
+                a[j] = (c < n4) ? __ldcg(src + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int j = 0; j < DEPTH; ++j) {
+                const int64_t c = c0 + lane + 32 * j;
+                if (c >= n4) {
+                    continue;
+                }
+                const float w[4] = {__fmul_rn(a[j].x, inv), __fmul_rn(a[j].y, inv), __fmul_rn(a[j].z, inv),
+                                    __fmul_rn(a[j].w, inv)};
+                float v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    v[q] = fminf(fmaxf(w[q], -128.0f), 127.0f);
+                }
+                uint32_t packed = narrow4_fast<DIRECT>(v[0], v[1], v[2], v[3]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (w[q] != w[q]) {  // a NaN activation narrows to 0 (fmaxf / fminf turned it into a bound)
+                        packed &= ~(0xffu << (8 * q));
+                    }
+                }
+                __stcs(dst + c, packed);
+            }
+        }
+    }
+}
+
 struct TileInfo {
     int32_t a_row0;  // first row this CTA loads and owns (global row index)
     int32_t m_rows;  // valid rows among this CTA's 128
     int32_t group;   // expert / batch (B's outermost coordinate)
     int32_t nt;      // column tile
+    int32_t mt;      // row tile (grouped: index into the tile table)
 };
 
 // The work of one epilogue thread on one tile: row `row_in_tile` of this CTA's
@@ -483,9 +547,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // the same offset in both CTAs of a pair, so the layout below is identical in both.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4..2S+6) epilogue rendezvous
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* requant_flag = abort_flag + 1;  // GMSQ: this CTA finished the last column tile of its rows
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -497,6 +562,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
     auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+    auto epi_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 4 + s); };  // rendezvous of the epilogue warps
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -507,6 +573,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             tc::mbar_init(tfull_bar(s), 1);
             tc::mbar_init(tempty_bar(s), 8 * CG);  // one arrival per epilogue warp of every CTA on the tile
         }
+        tc::mbar_init(epi_bar(0), 8);  // one arrival per epilogue warp of this CTA
+        tc::mbar_init(epi_bar(1), 1);  // the thread that counts finished tiles
         *abort_flag = 0;
         tc::fence_mbar_init();
         tc::prefetch_tensormap(&tm_a);
@@ -549,6 +617,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (p.grouped) {
             const int32_t mt = static_cast<int32_t>(t / p.n_tiles);
             tl.nt = static_cast<int32_t>(t % p.n_tiles);
+            tl.mt = mt;
             const TileEntry e = p.tiles[mt];
             tile_row0 = e.m_start;
             tile_rows = e.m_rows;
@@ -556,6 +625,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         } else {
             const int32_t mg = static_cast<int32_t>(t % dense_m_tiles);
             tl.nt = static_cast<int32_t>(t / dense_m_tiles);
+            tl.mt = mg;
             const int32_t b = mg / p.m_tiles_per_batch;
             const int32_t mt = mg % p.m_tiles_per_batch;
             const int64_t m0 = static_cast<int64_t>(mt) * TILE_M;
@@ -766,6 +836,49 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     tc::mbar_arrive_cluster(tempty0 + 8u * acc);
                 } else {
                     tc::mbar_arrive(tempty0 + 8u * acc);
+                }
+            }
+            if constexpr (EPI == EPI_GMSQ) {
+                if (p.fuse_requant) {
+                    // This CTA's rows are complete once all their column tiles are: count finished tiles per
+                    // (row tile, CTA); whoever brings the count to n_tiles quantises the rows, while the MMA warp
+                    // is already on the next tiles (the accumulator was handed back above).  Every epilogue
+                    // thread publishes its stores, then one thread counts.
+                    // The two rendezvous of the eight warps are mbarriers, so that they are bounded waits like every
+                    // other wait of this kernel.
+                    __threadfence();
+                    __syncwarp();
+                    const uint32_t epi_phase = static_cast<uint32_t>(it & 1);
+                    if (lane == 0) {
+                        tc::mbar_arrive(epi_bar(0));
+                    }
+                    if (warp == 2) {
+                        // The counting thread's own warp must not enter the blocking wait below before it has
+                        // counted: a warp suspended in mbarrier.try_wait takes its diverged lane 0 with it until
+                        // the wait's time slice ends (measured: 0.1 ms per tile).
+                        if (lane == 0) {
+                            if (tc::mbar_wait(epi_bar(0), epi_phase, abort_flag)) {
+                                const int old = atomicAdd(p.tile_done + static_cast<int64_t>(tl.mt) * CG + cta_rank, 1);
+                                *requant_flag = (old == p.n_tiles - 1) ? 1 : 0;
+                            } else {
+                                *requant_flag = 0;
+                            }
+                            tc::mbar_arrive(epi_bar(1));
+                        }
+                        __syncwarp();
+                    }
+                    if (!tc::mbar_wait(epi_bar(1), epi_phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    if (*requant_flag != 0) {
+                        __threadfence();
+                        if (p.round_direct) {
+                            requant_rows<true>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, lane);
+                        } else {
+                            requant_rows<false>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, lane);
+                        }
+                    }
                 }
             }
         }

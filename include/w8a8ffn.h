@@ -244,6 +244,13 @@ int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y,
  */
 int w8a8_set_gemm_shape(int shape);
 
+/* Test and tuning hook (no reference counterpart): grouped_matmul_swiglu_quant requantises in a second kernel over
+ * the stored activations (on = 0, the default) or inside the matmul kernels, where the CTA that finishes the last
+ * column tile of a row block quantises it (on = 1).  Identical results; the fused form measures slower (the
+ * epilogue warps are already busy nine tenths of the time, and the extra work lands on the CTAs that are last
+ * anyway).  Returns the previous setting. */
+int w8a8_set_gmsq_fused_requant(int on);
+
 
 /* Reads (synchronously, on `stream`) the device-side error word a grouped
  * call left in its workspace: 0 = none, 1 = invalid device group list,

@@ -297,6 +297,47 @@ def test_grouped_matmul_float_path(ops, oracle, dtype, layout_nk):
     assert err <= ref.abs().max().item() * 2.0**-7, err
 
 
+def test_gmsq_fused_and_two_kernel_requantisation_agree(ops, oracle, cta_group):
+    """The requantisation runs as a second kernel over the stored activations by default, inside the matmul kernels
+    when switched on (the CTA that finishes the last column tile of a row block quantises it), and as a call of
+    its own when the caller runs the operator's two stages separately: all forms give the oracle's bits."""
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    rng = np.random.default_rng(31)
+    counts = [700, 0, 129, 5, 256, 300, 1, 127]
+    gl = np.cumsum(counts).tolist()
+    m, k, n, e = gl[-1], 256, 1280, len(counts)   # 5 column tiles per row block
+    x = _i8(rng, (m, k))
+    w = _i8(rng, (e, k, n))
+    ws = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n)).astype(F)).cuda()
+    xs = torch.from_numpy(rng.uniform(1e-3, 5e-2, m).astype(F)).cuda()
+    want_y, want_s = oracle.grouped_matmul_swiglu_quant(x.cpu().numpy(), w.cpu().numpy(), ws.cpu().numpy(),
+                                                        xs.cpu().numpy(), gl)
+    try:
+        for fused in (1, 0):
+            lib.w8a8_set_gmsq_fused_requant(fused)
+            for glarg in (gl, torch.tensor(gl, dtype=torch.int64, device="cuda")):
+                y, ysc = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, glarg)
+                assert np.array_equal(y.cpu().numpy(), want_y), fused
+                assert ysc.cpu().numpy().tobytes() == want_s.tobytes(), fused
+    finally:
+        lib.w8a8_set_gmsq_fused_requant(0)
+    # the two stages as two calls (the reference's two launchers)
+    need = lib.w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e)
+    wsb = torch.empty((need,), dtype=torch.uint8, device="cuda")
+    y = torch.zeros((m, n // 2), dtype=torch.int8, device="cuda")
+    ysc = torch.zeros((m,), dtype=torch.float32, device="cuda")
+    glt = torch.tensor(gl, dtype=torch.int64)
+    for stage in (L.F_STAGE_MATMUL, L.F_STAGE_REQUANT):
+        rc = lib.w8a8_grouped_matmul_swiglu_quant(x.data_ptr(), w.data_ptr(), ws.data_ptr(), xs.data_ptr(),
+                                                  y.data_ptr(), ysc.data_ptr(), m, k, n, e, glt.data_ptr(), 0, L.W_KN,
+                                                  stage, wsb.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, L.status_string(rc)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), want_y) and ysc.cpu().numpy().tobytes() == want_s.tobytes()
+
+
 @pytest.mark.parametrize("layout_nk", [False, True])
 def test_grouped_matmul_fp32_operands(ops, layout_nk):
     """fp32 x and weight (the reference's GMM_DT_FLOAT dispatch): three-piece bf16 split of both operands on the
