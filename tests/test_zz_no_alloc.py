@@ -80,3 +80,30 @@ def test_static_entry_point_rejects_problems_beyond_its_scratch(ops):
     assert "capacity" in L.status_string(rc)
     torch.cuda.synchronize()
     assert bool((y == 5).all())
+
+
+def test_static_entry_point_reports_a_bad_device_group_list(ops):
+    """A group list that lives on the device is validated there; with this entry point the verdict sits in the
+    built-in scratch the caller never sees, so it is read with w8a8_static_scratch_error."""
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    lib = L.load()
+    x, w, ws, xs, _ = _problem(404, 130, 256, 512, 3, [0, 129, 130])
+    st = torch.cuda.current_stream().cuda_stream
+    y = torch.full((130, 256), 9, dtype=torch.int8, device="cuda")
+    ysc = torch.zeros((130,), dtype=torch.float32, device="cuda")
+    bad = torch.tensor([50, 40, 130], dtype=torch.int64, device="cuda")   # decreasing: not a cumulative list
+    rc = lib.w8a8_grouped_matmul_swiglu_quant_static(x.data_ptr(), w.data_ptr(), ws.data_ptr(), xs.data_ptr(),
+                                                     y.data_ptr(), ysc.data_ptr(), 130, 256, 512, 3, bad.data_ptr(), 1,
+                                                     L.W_KN, 0, st)
+    assert rc == 0  # nothing is wrong that the host could see
+    assert lib.w8a8_static_scratch_error(st) == 1
+    assert bool((y == 9).all())  # y left untouched
+    good = torch.tensor([0, 129, 130], dtype=torch.int64, device="cuda")
+    rc = lib.w8a8_grouped_matmul_swiglu_quant_static(x.data_ptr(), w.data_ptr(), ws.data_ptr(), xs.data_ptr(),
+                                                     y.data_ptr(), ysc.data_ptr(), 130, 256, 512, 3, good.data_ptr(), 1,
+                                                     L.W_KN, 0, st)
+    assert rc == 0 and lib.w8a8_static_scratch_error(st) == 0
+    assert not bool((y == 9).all())
+    # the dense matmuls' error word (no wait ran out in this process)
+    assert lib.w8a8_pipeline_error(st) == 0
