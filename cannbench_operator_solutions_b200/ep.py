@@ -554,6 +554,15 @@ class MoeFfnChain:
         self._mark("combine")
         return out, x_out
 
+    def close(self) -> None:
+        """Releases the C++ step's NCCL communicator (every rank must call it, or none)."""
+        if self._native is not None and self._native["comm"].value:
+            rc = self._native["lib"].w8a8_ep_comm_destroy(self._native["comm"])
+            self._native = None
+            if rc != 0:
+                raise RuntimeError("ep_comm_destroy failed")
+        self._native = None
+
     def check(self) -> None:
         """Device-table mode: raises if any step since the last check routed more rows to a rank than its buffers
         hold (the flag is sticky on the device and cleared here; reading it synchronises, so call it when that is
