@@ -1033,7 +1033,8 @@ MMA_PEAK_SHAPES = [
     # the matmul kernels' shape: 4 K steps per shared-memory stage
     (2, 256, 256, 0, 1, 1, 1, 4, 4, 0), (2, 256, 256, 0, 1, 0, 1, 4, 4, 0), (2, 256, 256, 0, 1, 1, 1, 4, 4, 3),
     (2, 256, 256, 0, 1, 1, 1, 8, 4, 0), (2, 256, 256, 0, 1, 1, 1, 8, 4, 1), (2, 256, 256, 0, 1, 1, 1, 8, 4, 2),
-    (2, 256, 256, 0, 1, 1, 1, 8, 4, 3), (2, 256, 256, 0, 1, 1, 1, 8, 3, 0), (2, 256, 256, 0, 1, 1, 1, 12, 2, 0),
+    (2, 256, 256, 0, 1, 1, 1, 8, 4, 3), (2, 256, 256, 0, 1, 1, 1, 8, 4, 4), (2, 256, 256, 0, 1, 1, 1, 4, 4, 4),
+    (2, 256, 256, 0, 1, 1, 1, 4, 6, 4), (2, 256, 256, 0, 1, 1, 1, 8, 3, 0), (2, 256, 256, 0, 1, 1, 1, 12, 2, 0),
     (2, 256, 256, 0, 1, 1, 1, 16, 4, 0), (2, 256, 256, 0, 1, 1, 1, 64, 2, 0),
     (1, 128, 256, 0, 1, 1, 1, 4, 4, 0), (1, 128, 256, 0, 1, 1, 1, 8, 4, 0), (1, 128, 256, 0, 1, 1, 1, 8, 2, 0),
     (1, 128, 256, 0, 1, 1, 1, 16, 4, 0),

@@ -72,6 +72,10 @@ SIGNATURES = {
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "w8a8_dequant_swiglu_quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp]),
     "w8a8_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "w8a8_gmsq_host_pipe_device_bytes": (_sz, [_i64, _i64, _i64, _i64]),
+    "w8a8_gmsq_host_pipe_create": (_i32, [ctypes.POINTER(_vp), _vp, _vp, _i64, _i64, _i64, _i32, _i64, _vp, _sz]),
+    "w8a8_gmsq_host_pipe_run": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp]),
+    "w8a8_gmsq_host_pipe_destroy": (_i32, [_vp]),
     "w8a8_ep_unique_id": (_i32, [_vp]),
     "w8a8_ep_comm_create": (_i32, [_vp, _i32, _i32, ctypes.POINTER(_vp)]),
     "w8a8_ep_comm_destroy": (_i32, [_vp]),

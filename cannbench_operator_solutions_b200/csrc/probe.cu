@@ -105,8 +105,22 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1)
         for (long long b = 0; ok && b < batches; ++b) {
             if (round != 0) {
                 // pattern 3: the wait a matmul's issuing thread makes on a barrier other CTAs' copies complete
-                const bool got = (pattern == 3) ? tc::mbar_wait_cluster(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag)
-                                                : tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                bool got;
+                if (pattern == 3) {
+                    got = tc::mbar_wait_cluster(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                } else if (pattern == 4) {
+                    // a few non-blocking tests first, the blocking bounded wait only if the phase is really open
+                    got = false;
+#pragma unroll 1
+                    for (int spin = 0; spin < 16 && !got; ++spin) {
+                        got = tc::mbar_test_wait(bar0 + 8u * slot, (round - 1u) & 1u);
+                    }
+                    if (!got) {
+                        got = tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                    }
+                } else {
+                    got = tc::mbar_wait(bar0 + 8u * slot, (round - 1u) & 1u, abort_flag);
+                }
                 if (!got) {
                     ok = false;
                     break;
@@ -208,7 +222,7 @@ extern "C" int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a
                                     int accumulators, int per_commit, int depth, int pattern, int64_t batches,
                                     int32_t* error_word, void* stream)
 {
-    if (pattern < 0 || pattern > 3) {
+    if (pattern < 0 || pattern > 4) {
         return W8A8_ERR_INVALID;
     }
     if (per_commit < PROBE_KSTEPS || per_commit > 256 || (per_commit % PROBE_KSTEPS) != 0 || depth < 1 ||

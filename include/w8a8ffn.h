@@ -409,6 +409,26 @@ int w8a8_dequant_swiglu_quant(const void* x, const float* weight_scale, const fl
                               int x_dtype, int activate_left, int flags, void* stream);
 
 /*
+ * GroupedMatmulSwigluQuant for rows that start, and results that end, in pinned HOST memory (no reference
+ * counterpart: its plugin takes device tensors only).  Host C++ that cuts the rows into chunks of chunk_rows and keeps
+ * a copy-in stream, the caller's stream and a copy-out stream busy at once over double-buffered device staging, each
+ * chunk being one w8a8_grouped_matmul_swiglu_quant call with the chunk's own group list; the call then costs about
+ * as long as the slower copy direction instead of copy + compute + copy, and the results equal one call over all
+ * rows bit for bit.  Weights and their scales stay on the device.  device_mem: w8a8_gmsq_host_pipe_device_bytes()
+ * bytes of device memory the caller owns (staging + workspace).  create makes two streams and a few events;
+ * run enqueues everything and returns (the results are complete when `stream` has caught up); one run at a time per
+ * pipe.  flags: W8A8_F_ROUND_DIRECT.
+ */
+typedef struct W8A8HostPipe W8A8HostPipe;
+size_t w8a8_gmsq_host_pipe_device_bytes(int64_t K, int64_t N, int64_t E, int64_t chunk_rows);
+int w8a8_gmsq_host_pipe_create(W8A8HostPipe** pipe, const int8_t* w, const float* w_scale, int64_t K, int64_t N,
+                               int64_t E, int w_layout, int64_t chunk_rows, void* device_mem, size_t device_bytes);
+int w8a8_gmsq_host_pipe_run(W8A8HostPipe* pipe, const int8_t* x_host, const float* x_scale_host,
+                            const int64_t* group_list_host, int64_t M, int8_t* y_host, float* y_scale_host, int flags,
+                            void* stream);
+int w8a8_gmsq_host_pipe_destroy(W8A8HostPipe* pipe);
+
+/*
  * The whole expert-parallel MoE FFN step as one host call (no reference counterpart: the reference is
  * single-device and has no step function; this is the C++ host side of benchmark configuration 5).  One call
  * enqueues on `stream`, with no host readback: add_rms_norm_dynamic_quant -> w8a8_route_plan -> all-gather of the
@@ -482,8 +502,9 @@ int w8a8_moe_ffn_step_status(const W8A8MoeFfnStep* step, void* stream);
  * instructions add to different accumulators (umma_n x accumulators <= 512).
  * pattern varies what the issuing thread does around a batch, to price each
  * piece: 0 = wait, instructions, commit; 1 = a second (already satisfied) wait;
- * 2 = an extra commit after every four instructions; 3 = the cluster-scope
- * wait plus tcgen05.fence the matmul kernels use.  error_word (device, may be NULL) receives 2 if a wait
+ * 2 = an extra commit after every four instructions; 3 = a cluster-scope
+ * wait plus tcgen05.fence; 4 = non-blocking mbarrier.test_wait polls before
+ * the blocking wait.  error_word (device, may be NULL) receives 2 if a wait
  * ran out.  w8a8_mma_issue_probe_ops returns the integer operations one such
  * launch performs on the current device.
  *
