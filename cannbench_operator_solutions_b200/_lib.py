@@ -53,6 +53,7 @@ SIGNATURES = {
     "w8a8_workspace_error": (_i32, [_vp, _vp]),
     "w8a8_set_gemm_shape": (_i32, [_i32]),
     "w8a8_set_gmsq_fused_requant": (_i32, [_i32]),
+    "w8a8_set_gmsq_epilogue_warps": (_i32, [_i32]),
     "w8a8_pipeline_error": (_i32, [_vp]),
     "w8a8_static_scratch_error": (_i32, [_vp]),
     "w8a8_route_plan_workspace_size": (_sz, [_i64, _i64, _i64]),

@@ -87,7 +87,7 @@ template <int CG, int BLOCK_N>
 constexpr size_t gemm_smem_bytes()
 {
     return static_cast<size_t>(gemm_stages(CG, BLOCK_N)) * (GEMM_A_BYTES + (BLOCK_N / CG) * GEMM_KBYTES) +
-           1024 /*alignment slack*/ + 512 /*barriers, tmem slot, abort flag*/ + 8 * 4096 /*epilogue store patches*/;
+           1024 /*alignment slack*/ + 512 /*barriers, tmem slot, abort flag*/ + GEMM_EPI_PATCH_BYTES /*store patches*/;
 }
 
 // number of workers (CTAs, or CTA pairs) a persistent launch uses
@@ -101,11 +101,11 @@ static int64_t worker_count(int64_t max_tiles)
     return workers < 1 ? 1 : workers;
 }
 
-template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN>
+template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN, int EPI_WARPS = 8>
 static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int64_t max_tiles,
                                cudaStream_t st)
 {
-    auto kern = gemm_tc_kernel<CG, BLOCK_N, KIND, EPI, B_MN>;
+    auto kern = gemm_tc_kernel<CG, BLOCK_N, KIND, EPI, B_MN, EPI_WARPS>;
     constexpr size_t smem = gemm_smem_bytes<CG, BLOCK_N>();
     // the attribute is per device; setting it on every call is cheap and covers multi-GPU processes
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -115,7 +115,7 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
     const int64_t workers = worker_count<CG>(max_tiles);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * CG), 1, 1);
-    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.blockDim = dim3(gemm_threads(EPI_WARPS), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -131,10 +131,23 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
 }
 
+static std::atomic<int> g_gmsq_epilogue_warps{16};
+
 template <int KIND, int EPI>
 static cudaError_t dispatch_gemm(int cta_group, int block_n, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
                                  const GemmParams& p, int64_t max_tiles, cudaStream_t st)
 {
+    if constexpr (EPI == EPI_GMSQ) {
+        // the SwiGLU epilogue with sixteen epilogue warps (see w8a8_set_gmsq_epilogue_warps)
+        if (g_gmsq_epilogue_warps.load(std::memory_order_relaxed) == 16) {
+            if (cta_group == 2) {
+                return b_mn ? launch_gemm<2, 256, KIND, EPI, true, 16>(ta, tb, p, max_tiles, st)
+                            : launch_gemm<2, 256, KIND, EPI, false, 16>(ta, tb, p, max_tiles, st);
+            }
+            return b_mn ? launch_gemm<1, 256, KIND, EPI, true, 16>(ta, tb, p, max_tiles, st)
+                        : launch_gemm<1, 256, KIND, EPI, false, 16>(ta, tb, p, max_tiles, st);
+        }
+    }
     if (cta_group == 2) {
         return b_mn ? launch_gemm<2, 256, KIND, EPI, true>(ta, tb, p, max_tiles, st)
                     : launch_gemm<2, 256, KIND, EPI, false>(ta, tb, p, max_tiles, st);
@@ -1000,6 +1013,14 @@ extern "C" int w8a8_pipeline_error(void* stream)
         return W8A8_ERR_CUDA;
     }
     return v;
+}
+
+extern "C" int w8a8_set_gmsq_epilogue_warps(int warps)
+{
+    if (warps != 8 && warps != 16) {
+        return W8A8_ERR_INVALID;
+    }
+    return g_gmsq_epilogue_warps.exchange(warps, std::memory_order_relaxed);
 }
 
 extern "C" int w8a8_set_gmsq_fused_requant(int on)

@@ -1,6 +1,6 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a with fused epilogues.
 //
-// One CTA per SM, 320 threads:
+// One CTA per SM, 320 threads (576 with the SwiGLU epilogue's sixteen epilogue warps):
 //   warp 0      TMA producer: fills a ring of shared-memory stages (128-byte
 //               swizzle) with A and B tiles, one mbarrier per stage.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma into one of two TMEM
@@ -10,7 +10,10 @@
 //               lanes its index modulo 4 selects; two warps share each lane
 //               quarter and split the columns), apply the operator's dequant
 //               chain, store.  Double-buffered TMEM lets the epilogue of tile i
-//               overlap the main loop of tile i+1.
+//               overlap the main loop of tile i+1.  The SwiGLU epilogue (an
+//               exponential and an IEEE division per element) runs on warps
+//               2-17, four per lane quarter: with eight warps it took as long
+//               per tile as the main loop.
 //
 // Two shapes of the same kernel (template parameter CG):
 //   CG = 1  one CTA per tile of 128 rows x BLOCK_N columns, 4 stages of
@@ -42,7 +45,10 @@
 
 namespace w8a8 {
 
-constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, 8 epilogue warps
+// producer warp, MMA warp and the epilogue warps (8, or 16 for the SwiGLU epilogue, whose per-element arithmetic -
+// exp and an IEEE division - otherwise keeps eight warps busy for as long as the MMA warp needs for the tile)
+__host__ __device__ constexpr int gemm_threads(int epi_warps) { return 64 + 32 * epi_warps; }
+constexpr int GEMM_EPI_PATCH_BYTES = 8 * 4096;  // shared by the epilogue warps: 4 KB each for 8, 2 KB each for 16
 constexpr int GEMM_BLOCK_M = 128;
 constexpr int GEMM_KBYTES = 128;  // bytes of K per stage row (one swizzle atom)
 constexpr int GEMM_A_BYTES = GEMM_BLOCK_M * GEMM_KBYTES;
@@ -186,16 +192,16 @@ __device__ __forceinline__ void load_vec32(const void* base, int64_t idx0, int k
 }
 
 
-// Requantisation of `rows` finished rows of SwiGLU activations starting at `row0` by the eight epilogue warps of
-// one CTA (warp w takes rows w, w + 8, ...): amax clamp at FLT_MIN, y_scale = amax * (1/127), inv = 127 / amax,
+// Requantisation of `rows` finished rows of SwiGLU activations starting at `row0` by the epilogue warps of
+// one CTA (warp w of `warps` takes rows w, w + warps, ...): amax clamp at FLT_MIN, y_scale = amax * (1/127), inv = 127 / amax,
 // clamp to [-128, 127], narrowing (gmsq_vec_kernel.cpp:233-257).  The activations and row maxima were written
 // by other SMs: they are read through L2 (ld.global.cg), never through this SM's L1.
 template <bool DIRECT>
 __device__ __forceinline__ void requant_rows(const float* act, const uint32_t* amax_bits, int8_t* y, float* y_scale,
-                                             int64_t row0, int rows, int64_t H, int warp_in_group, int lane)
+                                             int64_t row0, int rows, int64_t H, int warp_in_group, int warps, int lane)
 {
     const int64_t n4 = H / 4;
-    for (int r = warp_in_group; r < rows; r += 8) {
+    for (int r = warp_in_group; r < rows; r += warps) {
         const int64_t row = row0 + r;
         float amax = __uint_as_float(__ldcg(amax_bits + row));
         if (!(amax > 1.1754944e-38f)) {
@@ -253,7 +259,7 @@ struct TileInfo {
 
 // The work of one epilogue thread on one tile: row `row_in_tile` of this CTA's
 // accumulator, columns [col_half * BLOCK_N/2, (col_half+1) * BLOCK_N/2).
-template <int BLOCK_N, int KIND, int EPI>
+template <int BLOCK_N, int KIND, int EPI, int EPI_WARPS>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInfo& tl, uint32_t t_addr,
                                               int row_in_tile, int col_half, int64_t H, bool no_epilogue,
                                               uint4* stage)
@@ -264,19 +270,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
         const float xs = row_ok ? p.row_scale[row] : 0.0f;
         const float* wsg = static_cast<const float*>(p.scale) + static_cast<int64_t>(tl.group) * p.N;
         float local_max = 0.0f;
-        constexpr int HALF_COLS = 64;  // act columns per epilogue warp
+        // `col_half` counts this warp among the EPI_WARPS / 4 warps that share a TMEM lane quarter: each takes
+        // 128 / (EPI_WARPS / 4) activation columns, 16 at a time
+        constexpr int WARP_COLS = 128 / (EPI_WARPS / 4);
 #pragma unroll 1
-        for (int cc = 0; cc < HALF_COLS; cc += 32) {
-            const int c = col_half * HALF_COLS + cc;
-            uint32_t g[32], u[32];
-            tc::tmem_ld_32x32(t_addr + c, g);
-            tc::tmem_ld_32x32(t_addr + 128 + c, u);
+        for (int cc = 0; cc < WARP_COLS; cc += 16) {
+            const int c = col_half * WARP_COLS + cc;
+            uint32_t g[16], u[16];
+            tc::tmem_ld_32x16(t_addr + c, g);
+            tc::tmem_ld_32x16(t_addr + 128 + c, u);
             tc::tmem_ld_wait();
             const int64_t col0 = static_cast<int64_t>(tl.nt) * 128 + c;  // column in [0, H)
             const int lane = row_in_tile & 31;
             if (row_ok) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
+                for (int q = 0; q < 4; ++q) {
                     const int64_t col = col0 + q * 4;
                     if (col < H) {
                         const float4 wg = __ldg(reinterpret_cast<const float4*>(wsg + col));
@@ -293,25 +301,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
                             a[j] = __fmul_rn(canonical_silu(l), r);
                             local_max = fmaxf(local_max, fabsf(a[j]));
                         }
-                        // parked in the warp's shared-memory patch (piece q of row `lane`, xor-swizzled)
-                        stage[lane * 8 + (q ^ (lane & 7))] =
+                        // parked in the warp's shared-memory patch: piece q of row `lane`, the pieces permuted by
+                        // the row so that the eight lanes of a store phase hit eight different bank groups
+                        stage[lane * 4 + (q ^ ((lane ^ (lane >> 2)) & 3))] =
                             make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]),
                                        __float_as_uint(a[3]));
                     }
                 }
             }
-            // the 32 activations of each row are one 128-byte line: written by 8 lanes per row, 4 rows per
+            // the 16 activations of each row are a 64-byte piece of a line: written by 4 lanes per row, 8 rows per
             // instruction, instead of 16-byte pieces of 32 different rows
             __syncwarp();
             {
-                const int piece = lane & 7;
+                const int piece = lane & 3;
                 const int64_t col = col0 + piece * 4;
                 const int first_row = row_in_tile & ~31;
 #pragma unroll
-                for (int it = 0; it < 8; ++it) {
-                    const int rr = it * 4 + (lane >> 3);
+                for (int it = 0; it < 4; ++it) {
+                    const int rr = it * 8 + (lane >> 2);
                     if (first_row + rr < tl.m_rows && !no_epilogue && col < H) {
-                        const uint4 val = stage[rr * 8 + (piece ^ (rr & 7))];
+                        const uint4 val = stage[rr * 4 + (piece ^ ((rr ^ (rr >> 2)) & 3))];
                         *reinterpret_cast<uint4*>(p.act + (static_cast<int64_t>(tl.a_row0) + first_row + rr) * H + col) =
                             val;
                     }
@@ -518,8 +527,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const TileInf
     }
 }
 
-template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <int CG, int BLOCK_N, int KIND, int EPI, bool B_MN, int EPI_WARPS>
+__global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const GemmParams p)
 {
@@ -541,6 +550,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "BLOCK_N");
     static_assert(CG == 1 || BLOCK_N == 256, "CTA pairs use 256-column tiles");
     static_assert(EPI != EPI_GMSQ || BLOCK_N == 256, "the SwiGLU epilogue pairs 128 gate with 128 up columns");
+    static_assert(EPI_WARPS == 8 || (EPI_WARPS == 16 && EPI == EPI_GMSQ), "16 epilogue warps: SwiGLU epilogue only");
 
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms.  The dynamic shared memory window starts at
@@ -571,9 +581,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         for (int s = 0; s < 2; ++s) {
             tc::mbar_init(tfull_bar(s), 1);
-            tc::mbar_init(tempty_bar(s), 8 * CG);  // one arrival per epilogue warp of every CTA on the tile
+            tc::mbar_init(tempty_bar(s), EPI_WARPS * CG);  // one arrival per epilogue warp of every CTA on the tile
         }
-        tc::mbar_init(epi_bar(0), 8);  // one arrival per epilogue warp of this CTA
+        tc::mbar_init(epi_bar(0), EPI_WARPS);  // one arrival per epilogue warp of this CTA
         tc::mbar_init(epi_bar(1), 1);  // the thread that counts finished tiles
         *abort_flag = 0;
         tc::fence_mbar_init();
@@ -805,14 +815,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         __syncwarp();
     } else {
-        // ===================== epilogue (warps 2..9) =====================
-        // Two warps per TMEM lane quarter; they split the tile's columns in halves.
+        // ===================== epilogue (warps 2 .. 2 + EPI_WARPS) =====================
+        // EPI_WARPS / 4 warps per TMEM lane quarter; they split the tile's columns evenly.
         const int quarter = warp & 3;          // TMEM lanes [32*quarter, 32*quarter+32)
-        const int col_half = (warp - 2) >> 2;  // 0 or 1
+        const int col_half = (warp - 2) >> 2;  // which share of the columns
         const int row_in_tile = quarter * 32 + lane;
         const bool no_epilogue = false;
-        // this warp's 4 KB patch for turning per-thread rows into full-line stores
-        uint4* stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 512) + (warp - 2) * 256;
+        // this warp's patch (4 KB, or 2 KB with 16 warps) for turning per-thread rows into whole-segment stores
+        uint4* stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 512) +
+                       (warp - 2) * (GEMM_EPI_PATCH_BYTES / 16 / EPI_WARPS);
         const uint32_t tempty0 = (CG == 2) ? tc::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         int64_t it = 0;
         bool ok = true;
@@ -827,7 +838,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             tc::tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                     static_cast<uint32_t>(acc * BLOCK_N);
-            epilogue_tile<BLOCK_N, KIND, EPI>(p, tl, t_addr, row_in_tile, col_half, H, no_epilogue, stage);
+            epilogue_tile<BLOCK_N, KIND, EPI, EPI_WARPS>(p, tl, t_addr, row_in_tile, col_half, H, no_epilogue, stage);
             // accumulator stage drained: hand it back to the MMA issuer (one arrival per warp)
             tc::tc_fence_before_sync();
             __syncwarp();
@@ -874,9 +885,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     if (*requant_flag != 0) {
                         __threadfence();
                         if (p.round_direct) {
-                            requant_rows<true>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, lane);
+                            requant_rows<true>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, EPI_WARPS, lane);
                         } else {
-                            requant_rows<false>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, lane);
+                            requant_rows<false>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, EPI_WARPS, lane);
                         }
                     }
                 }

@@ -251,6 +251,11 @@ int w8a8_set_gemm_shape(int shape);
  * anyway).  Returns the previous setting. */
 int w8a8_set_gmsq_fused_requant(int on);
 
+/* Test and tuning hook (no reference counterpart): how many warps of the grouped_matmul_swiglu_quant kernels run the
+ * dequant / SwiGLU / row-max epilogue, 8 or 16 (default 16).  Identical results.  Returns the previous setting, or
+ * W8A8_ERR_INVALID. */
+int w8a8_set_gmsq_epilogue_warps(int warps);
+
 
 /* Reads (synchronously, on `stream`) the device-side error word a grouped
  * call left in its workspace: 0 = none, 1 = invalid device group list,

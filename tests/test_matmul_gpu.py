@@ -315,14 +315,18 @@ def test_gmsq_fused_and_two_kernel_requantisation_agree(ops, oracle, cta_group):
     want_y, want_s = oracle.grouped_matmul_swiglu_quant(x.cpu().numpy(), w.cpu().numpy(), ws.cpu().numpy(),
                                                         xs.cpu().numpy(), gl)
     try:
-        for fused in (1, 0):
-            lib.w8a8_set_gmsq_fused_requant(fused)
-            for glarg in (gl, torch.tensor(gl, dtype=torch.int64, device="cuda")):
-                y, ysc = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, glarg)
-                assert np.array_equal(y.cpu().numpy(), want_y), fused
-                assert ysc.cpu().numpy().tobytes() == want_s.tobytes(), fused
+        for epilogue_warps in (8, 16):   # both widths of the SwiGLU epilogue
+            assert lib.w8a8_set_gmsq_epilogue_warps(epilogue_warps) in (8, 16)
+            for fused in (1, 0):
+                lib.w8a8_set_gmsq_fused_requant(fused)
+                for glarg in (gl, torch.tensor(gl, dtype=torch.int64, device="cuda")):
+                    y, ysc = ops.grouped_matmul_swiglu_quant(x, w, ws, xs, glarg)
+                    assert np.array_equal(y.cpu().numpy(), want_y), (epilogue_warps, fused)
+                    assert ysc.cpu().numpy().tobytes() == want_s.tobytes(), (epilogue_warps, fused)
+        assert lib.w8a8_set_gmsq_epilogue_warps(12) == L.ERR_INVALID
     finally:
         lib.w8a8_set_gmsq_fused_requant(0)
+        lib.w8a8_set_gmsq_epilogue_warps(16)
     # the two stages as two calls (the reference's two launchers)
     need = lib.w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e)
     wsb = torch.empty((need,), dtype=torch.uint8, device="cuda")
