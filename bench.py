@@ -1117,6 +1117,8 @@ def main():
     ap.add_argument("--gmsq-requant", choices=["two-kernel", "fused"], default="two-kernel",
                     help="grouped workload: requantise in a second kernel (the library's default) or inside the "
                          "matmul kernels (w8a8_set_gmsq_fused_requant)")
+    ap.add_argument("--gmsq-epilogue-warps", type=int, choices=[8, 16], default=16,
+                    help="grouped workload: warps that run the SwiGLU epilogue (w8a8_set_gmsq_epilogue_warps)")
     ap.add_argument("--gemm-shape", type=int, choices=[0, 1, 2, 3], default=0,
                     help="force the matmul kernel shape (w8a8_set_gemm_shape): 1 single CTAs, 2 CTA pairs, 3 pairs "
                          "plus singles for grouped problems; 0 = the library's choice")
@@ -1168,6 +1170,8 @@ def main():
         _L.load().w8a8_set_gmsq_fused_requant(1)
     if args.gemm_shape:
         _L.load().w8a8_set_gemm_shape(args.gemm_shape)
+    if args.gmsq_epilogue_warps != 16:
+        _L.load().w8a8_set_gmsq_epilogue_warps(args.gmsq_epilogue_warps)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

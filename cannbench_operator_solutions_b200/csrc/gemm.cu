@@ -804,7 +804,10 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.amax = g.amax;
         // Optional (off by default, it measures slower): the matmul kernels quantise each row block themselves as
         // soon as its last column tile is done, and no second kernel runs.
-        p.fuse_requant = (run_requant && g_fuse_requant.load(std::memory_order_relaxed)) ? 1 : 0;
+        // (a CTA waits for the other column tiles of its rows, which must then be running on other CTAs: only with
+        // at least as many workers as column tiles)
+        p.fuse_requant =
+            (run_requant && g_fuse_requant.load(std::memory_order_relaxed) && p.n_tiles <= sm_count() / 2) ? 1 : 0;
         p.y = y;
         p.y_scale = y_scale;
         p.round_direct = (flags & W8A8_F_ROUND_DIRECT) ? 1 : 0;

@@ -115,7 +115,7 @@ struct GemmParams {
     float* act;       // GMSQ: fp32 activations [M, N/2]
     uint32_t* amax;   // GMSQ: per-row max|act| bit patterns
     // GMSQ with the requantisation fused in: the CTA that finishes the last column tile of its rows quantises them
-    int32_t* tile_done;   // per (row tile, CTA of the tile): column tiles finished so far (zeroed by the caller)
+    int32_t* tile_done;   // per (row tile, CTA of the tile): epilogue warps done with a column tile (zeroed by the caller)
     int8_t* y;            // [M, N/2]
     float* y_scale;       // [M]
     int32_t fuse_requant;
@@ -192,59 +192,56 @@ __device__ __forceinline__ void load_vec32(const void* base, int64_t idx0, int k
 }
 
 
-// Requantisation of `rows` finished rows of SwiGLU activations starting at `row0` by the epilogue warps of
-// one CTA (warp w of `warps` takes rows w, w + warps, ...): amax clamp at FLT_MIN, y_scale = amax * (1/127), inv = 127 / amax,
-// clamp to [-128, 127], narrowing (gmsq_vec_kernel.cpp:233-257).  The activations and row maxima were written
-// by other SMs: they are read through L2 (ld.global.cg), never through this SM's L1.
+// Requantisation of one finished row of SwiGLU activations, 16-byte pieces [c_lo, c_hi) of it, by one warp:
+// amax clamp at FLT_MIN, y_scale = amax * (1/127), inv = 127 / amax, clamp to [-128, 127], narrowing
+// (gmsq_vec_kernel.cpp:233-257).  The activations and row maxima were written by other SMs: they are read through
+// L2 (ld.global.cg), never through this SM's L1.
 template <bool DIRECT>
-__device__ __forceinline__ void requant_rows(const float* act, const uint32_t* amax_bits, int8_t* y, float* y_scale,
-                                             int64_t row0, int rows, int64_t H, int warp_in_group, int warps, int lane)
+__device__ __forceinline__ void requant_row_part(const float* act, const uint32_t* amax_bits, int8_t* y, float* y_scale,
+                                                 int64_t row, int64_t H, int64_t c_lo, int64_t c_hi, bool write_scale,
+                                                 int lane)
 {
-    const int64_t n4 = H / 4;
-    for (int r = warp_in_group; r < rows; r += warps) {
-        const int64_t row = row0 + r;
-        float amax = __uint_as_float(__ldcg(amax_bits + row));
-        if (!(amax > 1.1754944e-38f)) {
-            amax = 1.1754944e-38f;
+    float amax = __uint_as_float(__ldcg(amax_bits + row));
+    if (!(amax > 1.1754944e-38f)) {
+        amax = 1.1754944e-38f;
+    }
+    if (write_scale && lane == 0) {
+        y_scale[row] = __fmul_rn(amax, INV127);
+    }
+    const float inv = __fdiv_rn(127.0f, amax);
+    const float4* src = reinterpret_cast<const float4*>(act + row * H);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(y + row * H);
+    // eight independent 16-byte loads in flight per lane: few warps work here, and a load at a time would leave
+    // them waiting on L2 latency
+    constexpr int DEPTH = 8;
+    for (int64_t c0 = c_lo; c0 < c_hi; c0 += 32 * DEPTH) {
+        float4 a[DEPTH];
+#pragma unroll
+        for (int j = 0; j < DEPTH; ++j) {
+            const int64_t c = c0 + lane + 32 * j;
+            a[j] = (c < c_hi) ? __ldcg(src + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
-        if (lane == 0) {
-            y_scale[row] = __fmul_rn(amax, INV127);
-        }
-        const float inv = __fdiv_rn(127.0f, amax);
-        const float4* src = reinterpret_cast<const float4*>(act + row * H);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(y + row * H);
-        // eight independent 16-byte loads in flight per lane: only eight warps work here, and a load at a time
-        // would leave them waiting on L2 latency
-        constexpr int DEPTH = 8;
-        for (int64_t c0 = 0; c0 < n4; c0 += 32 * DEPTH) {
-            float4 a[DEPTH];
 #pragma unroll
-            for (int j = 0; j < DEPTH; ++j) {
-                const int64_t c = c0 + lane + 32 * j;
-                a[j] = (c < n4) ? __ldcg(src + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int j = 0; j < DEPTH; ++j) {
+            const int64_t c = c0 + lane + 32 * j;
+            if (c >= c_hi) {
+                continue;
             }
+            const float w[4] = {__fmul_rn(a[j].x, inv), __fmul_rn(a[j].y, inv), __fmul_rn(a[j].z, inv),
+                                __fmul_rn(a[j].w, inv)};
+            float v[4];
 #pragma unroll
-            for (int j = 0; j < DEPTH; ++j) {
-                const int64_t c = c0 + lane + 32 * j;
-                if (c >= n4) {
-                    continue;
-                }
-                const float w[4] = {__fmul_rn(a[j].x, inv), __fmul_rn(a[j].y, inv), __fmul_rn(a[j].z, inv),
-                                    __fmul_rn(a[j].w, inv)};
-                float v[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    v[q] = fminf(fmaxf(w[q], -128.0f), 127.0f);
-                }
-                uint32_t packed = narrow4_fast<DIRECT>(v[0], v[1], v[2], v[3]);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    if (w[q] != w[q]) {  // a NaN activation narrows to 0 (fmaxf / fminf turned it into a bound)
-                        packed &= ~(0xffu << (8 * q));
-                    }
-                }
-                __stcs(dst + c, packed);
+            for (int q = 0; q < 4; ++q) {
+                v[q] = fminf(fmaxf(w[q], -128.0f), 127.0f);
             }
+            uint32_t packed = narrow4_fast<DIRECT>(v[0], v[1], v[2], v[3]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (w[q] != w[q]) {  // a NaN activation narrows to 0 (fmaxf / fminf turned it into a bound)
+                    packed &= ~(0xffu << (8 * q));
+                }
+            }
+            __stcs(dst + c, packed);
         }
     }
 }
@@ -557,10 +554,9 @@ __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
     // the same offset in both CTAs of a pair, so the layout below is identical in both.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4..2S+6) epilogue rendezvous
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* requant_flag = abort_flag + 1;  // GMSQ: this CTA finished the last column tile of its rows
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -572,7 +568,6 @@ __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
     auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
-    auto epi_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 4 + s); };  // rendezvous of the epilogue warps
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -583,8 +578,6 @@ __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
             tc::mbar_init(tfull_bar(s), 1);
             tc::mbar_init(tempty_bar(s), EPI_WARPS * CG);  // one arrival per epilogue warp of every CTA on the tile
         }
-        tc::mbar_init(epi_bar(0), EPI_WARPS);  // one arrival per epilogue warp of this CTA
-        tc::mbar_init(epi_bar(1), 1);  // the thread that counts finished tiles
         *abort_flag = 0;
         tc::fence_mbar_init();
         tc::prefetch_tensormap(&tm_a);
@@ -827,6 +820,52 @@ __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
         const uint32_t tempty0 = (CG == 2) ? tc::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
         int64_t it = 0;
         bool ok = true;
+        // Requantisation inside this kernel (SwiGLU epilogue, optional).  The rows of a row tile are shared out
+        // among the CTAs that compute its column tiles: the CTA of column tile nt quantises rows nt, nt + n_tiles,
+        // ... of its 128, one row per warp at a time, once every column tile of the rows has been counted in
+        // tile_done.  Column tiles of one row tile are consecutive tile numbers, so they run on different CTAs at
+        // the same time (the host switches this on only when there are at least n_tiles workers): a wait here
+        // only ever depends on tiles with smaller numbers than the waiter's current one, and it is bounded like
+        // every other wait of the kernel.
+        TileInfo late{};
+        bool have_late = false;
+        auto requant_share = [&](const TileInfo& d) -> bool {
+            // work units of this CTA for the tile: (row d.nt + n_tiles * k, half h of the row), unit = 2 k + h
+            const int units = 2 * ((d.m_rows - d.nt + p.n_tiles - 1) / p.n_tiles);
+            if (warp - 2 >= units) {
+                return true;
+            }
+            const int want = p.n_tiles * EPI_WARPS;
+            int seen = 0;
+            if (lane == 0) {
+                const int* counter = p.tile_done + static_cast<int64_t>(d.mt) * CG + cta_rank;
+                const long long t0 = clock64();
+                while ((seen = tc::ld_acquire_gpu(counter)) < want) {
+                    if (*abort_flag != 0 || clock64() - t0 > tc::WAIT_LIMIT_CYCLES) {
+                        *abort_flag = 1;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen < want) {
+                return false;
+            }
+            const int64_t n4 = H / 4, mid = n4 / 2;
+            for (int u = warp - 2; u < units; u += EPI_WARPS) {
+                const int64_t row = static_cast<int64_t>(d.a_row0) + d.nt + p.n_tiles * (u >> 1);
+                const bool second = (u & 1) != 0;
+                if (p.round_direct) {
+                    requant_row_part<true>(p.act, p.amax, p.y, p.y_scale, row, H, second ? mid : 0, second ? n4 : mid,
+                                           !second, lane);
+                } else {
+                    requant_row_part<false>(p.act, p.amax, p.y, p.y_scale, row, H, second ? mid : 0, second ? n4 : mid,
+                                            !second, lane);
+                }
+            }
+            return true;
+        };
         for (int64_t t = worker; ok && t < total_tiles; t += num_workers, ++it) {
             const TileInfo tl = decode(t);
             const int acc = static_cast<int>(it & 1);
@@ -851,46 +890,29 @@ __global__ void __launch_bounds__(gemm_threads(EPI_WARPS), 1)
             }
             if constexpr (EPI == EPI_GMSQ) {
                 if (p.fuse_requant) {
-                    // This CTA's rows are complete once all their column tiles are: count finished tiles per
-                    // (row tile, CTA); whoever brings the count to n_tiles quantises the rows, while the MMA warp
-                    // is already on the next tiles (the accumulator was handed back above).  Every epilogue
-                    // thread publishes its stores, then one thread counts.
-                    // The two rendezvous of the eight warps are mbarriers, so that they are bounded waits like every
-                    // other wait of this kernel.
+                    // Publish this warp's activation stores and row maxima, then count the warp on its row tile:
+                    // the rows are complete when n_tiles * EPI_WARPS warps have been counted.
                     __threadfence();
                     __syncwarp();
-                    const uint32_t epi_phase = static_cast<uint32_t>(it & 1);
                     if (lane == 0) {
-                        tc::mbar_arrive(epi_bar(0));
+                        atomicAdd(p.tile_done + static_cast<int64_t>(tl.mt) * CG + cta_rank, 1);
                     }
-                    if (warp == 2) {
-                        // The counting thread's own warp must not enter the blocking wait below before it has
-                        // counted: a warp suspended in mbarrier.try_wait takes its diverged lane 0 with it until
-                        // the wait's time slice ends (measured: 0.1 ms per tile).
-                        if (lane == 0) {
-                            if (tc::mbar_wait(epi_bar(0), epi_phase, abort_flag)) {
-                                const int old = atomicAdd(p.tile_done + static_cast<int64_t>(tl.mt) * CG + cta_rank, 1);
-                                *requant_flag = (old == p.n_tiles - 1) ? 1 : 0;
-                            } else {
-                                *requant_flag = 0;
-                            }
-                            tc::mbar_arrive(epi_bar(1));
-                        }
-                        __syncwarp();
-                    }
-                    if (!tc::mbar_wait(epi_bar(1), epi_phase, abort_flag)) {
+                    // This tile's share of the requantisation is taken one tile late: by then the other column
+                    // tiles of the same rows (on other CTAs, at about the same time) have been counted, so the wait
+                    // inside costs one load.  (Two tiles late measured slower: the second pending tile goes to
+                    // local memory.)
+                    if (have_late && !requant_share(late)) {
                         ok = false;
                         break;
                     }
-                    if (*requant_flag != 0) {
-                        __threadfence();
-                        if (p.round_direct) {
-                            requant_rows<true>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, EPI_WARPS, lane);
-                        } else {
-                            requant_rows<false>(p.act, p.amax, p.y, p.y_scale, tl.a_row0, tl.m_rows, H, warp - 2, EPI_WARPS, lane);
-                        }
-                    }
+                    late = tl;
+                    have_late = true;
                 }
+            }
+        }
+        if constexpr (EPI == EPI_GMSQ) {
+            if (p.fuse_requant && ok && have_late) {
+                requant_share(late);
             }
         }
     }
