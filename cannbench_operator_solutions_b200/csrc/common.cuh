@@ -69,7 +69,9 @@ __device__ __forceinline__ uint16_t float_to_bits16(float v)
 // pieces, degree-5 polynomial (the classic single-precision coefficients
 // published with the Cephes library), two-step power-of-two scaling.  Built
 // from IEEE mul / add / fma only, so host and device agree bit for bit.
-__device__ __forceinline__ float canonical_expf(float x)
+// This is the defining sequence; the kernels call canonical_expf below, which
+// returns the same bits with fewer instructions.
+__device__ __forceinline__ float canonical_expf_as_defined(float x)
 {
     if (x != x) {
         return x;
@@ -94,6 +96,39 @@ __device__ __forceinline__ float canonical_expf(float x)
     const float s1 = __int_as_float((n1 + 127) << 23);
     const float s2 = __int_as_float((n2 + 127) << 23);
     return __fmul_rn(__fmul_rn(e, s1), s2);
+}
+
+// The same function, bit for bit on every input (w8a8_selftest_exp sweeps all 2^32), arranged for the issue
+// slots it costs in the SwiGLU epilogues and the router softmax:
+//  - rint and the float -> int conversion (conversion-pipe instructions, a quarter of the fp32 rate) become an
+//    add and a subtract of 1.5 * 2^23, whose sum holds the integer in its low mantissa bits (|n| <= 151);
+//    a product that rounds to -0 gives n = +0 instead of -0, which the two fma that use n turn into the same r;
+//  - e lies in [0.70, 1.42] and n1 = n >> 1 in [-75, 64], so the first of the two multiplications by powers of
+//    two is exact and lands on a normal number: it becomes an integer add to e's exponent field.  The second
+//    multiplication stays, because it is the one that rounds (subnormal results) or overflows.
+__device__ __forceinline__ float canonical_expf(float x)
+{
+    const float xc = fminf(fmaxf(x, -104.0f), 89.0f);  // a NaN comes out as -104 here and is put back at the end
+    const float t = __fadd_rn(__fmul_rn(xc, 1.44269504088896341f), 12582912.0f);
+    const float n = __fsub_rn(t, 12582912.0f);
+    const int ni = __float_as_int(t) - 0x4B400000;
+    float r = fmaf(n, -0.693359375f, xc);
+    r = fmaf(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = fmaf(p, r, 1.3981999507e-3f);
+    p = fmaf(p, r, 8.3334519073e-3f);
+    p = fmaf(p, r, 4.1665795894e-2f);
+    p = fmaf(p, r, 1.6666665459e-1f);
+    p = fmaf(p, r, 5.0000001201e-1f);
+    const float r2 = __fmul_rn(r, r);
+    float e = fmaf(p, r2, r);
+    e = __fadd_rn(e, 1.0f);
+    const int n1 = ni >> 1;
+    const int n2 = ni - n1;
+    const float e1 = __int_as_float(__float_as_int(e) + (n1 << 23));
+    const float s2 = __int_as_float((n2 << 23) + 0x3f800000);
+    const float out = __fmul_rn(e1, s2);
+    return (x != x) ? x : out;
 }
 
 // silu(l) = l / (1 + exp(-l)), the operation sequence of the reference

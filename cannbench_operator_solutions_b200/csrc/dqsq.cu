@@ -91,6 +91,25 @@ __device__ __forceinline__ float dqsq_element(float a, float b, float wa, float 
     return __fdiv_rn(__fmul_rn(a, b), den);
 }
 
+// The same element with the two halves named by role (g: the half the gate is formed from, o: the other one) and the
+// smooth scale always applied (1 when the caller gave none; a multiplication by 1 is exact): a * b commutes, and
+// gate * -1 is a sign flip, so the bits are those of dqsq_element without its per-element case distinctions.
+template <int XT>
+__device__ __forceinline__ float dqsq_element_by_role(float g, float o, float wg, float wo, float qs, float as)
+{
+    if constexpr (XT == DQSQ_X_I32) {
+        g = __fmul_rn(g, wg);
+        o = __fmul_rn(o, wo);
+    }
+    o = __fmul_rn(o, qs);
+    if constexpr (XT == DQSQ_X_I32) {
+        g = __fmul_rn(g, as);
+        o = __fmul_rn(o, as);
+    }
+    const float den = __fadd_rn(canonical_expf(-g), 1.0f);
+    return __fdiv_rn(__fmul_rn(g, o), den);
+}
+
 __device__ __forceinline__ float dqsq_block_max(float m, float* s_red, int parity)
 {
 #pragma unroll
@@ -115,8 +134,10 @@ __device__ __forceinline__ float dqsq_scaled(float o, float s, bool divide)
     return divide ? __fdiv_rn(o, s) : __fmul_rn(o, s);
 }
 
-__device__ __forceinline__ uint32_t dqsq_quant4(const float* o, float s, bool divide, bool direct)
+template <bool DIVIDE>
+__device__ __forceinline__ uint32_t dqsq_quant4(const float* o, float s, bool direct)
 {
+    constexpr bool divide = DIVIDE;
     float v[4];
     bool any_nan = false;
 #pragma unroll
@@ -139,13 +160,13 @@ __device__ __forceinline__ uint32_t dqsq_quant4(const float* o, float s, bool di
 }
 
 // Register-resident rows: H a multiple of the chunk length, at most DQSQ_THREADS * EL * CPT long.
-template <int XT, int CPT>
+template <int XT, int CPT, bool DIVIDE>
 __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_kernel(const void* __restrict__ x,
                                                                  const float* __restrict__ weight_scale,
                                                                  const float* __restrict__ activation_scale,
                                                                  const float* __restrict__ quant_scale,
                                                                  int8_t* __restrict__ y, float* __restrict__ scale,
-                                                                 int64_t M, int64_t H, int left, int direct, int divide)
+                                                                 int64_t M, int64_t H, int left, int direct, int)
 {
     using C = DqsqChunk<XT>;
     constexpr int EL = C::EL;
@@ -154,6 +175,8 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
     const int nchunks = static_cast<int>(H / EL);
     const size_t elem = (XT == DQSQ_X_I32) ? 4 : 2;
     const bool has_q = (quant_scale != nullptr);
+    // where the gate half and the other half start, in the row and in weight_scale
+    const int64_t g_off = left ? 0 : H, o_off = left ? H : 0;
     int parity = 0;
     for (int64_t row = blockIdx.x; row < M; row += gridDim.x, parity ^= 1) {
         const uint8_t* xr = static_cast<const uint8_t*>(x) + static_cast<size_t>(row) * 2 * H * elem;
@@ -164,8 +187,8 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
         for (int i = 0; i < CPT; ++i) {
             const int c = tid + i * DQSQ_THREADS;
             if (c < nchunks) {
-                ca[i] = C::load_raw(xr, static_cast<int64_t>(c) * EL);
-                cb[i] = C::load_raw(xr, H + static_cast<int64_t>(c) * EL);
+                ca[i] = C::load_raw(xr, g_off + static_cast<int64_t>(c) * EL);
+                cb[i] = C::load_raw(xr, o_off + static_cast<int64_t>(c) * EL);
             }
         }
         float out[CPT][EL];
@@ -184,21 +207,20 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
                 for (int q = 0; q < EL / 4; ++q) {
                     float4 t = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
                     if constexpr (XT == DQSQ_X_I32) {
-                        t = __ldg(reinterpret_cast<const float4*>(weight_scale + j0) + q);
+                        t = __ldg(reinterpret_cast<const float4*>(weight_scale + g_off + j0) + q);
                     }
                     wa[4 * q] = t.x, wa[4 * q + 1] = t.y, wa[4 * q + 2] = t.z, wa[4 * q + 3] = t.w;
                     if constexpr (XT == DQSQ_X_I32) {
-                        t = __ldg(reinterpret_cast<const float4*>(weight_scale + H + j0) + q);
+                        t = __ldg(reinterpret_cast<const float4*>(weight_scale + o_off + j0) + q);
                     }
                     wb[4 * q] = t.x, wb[4 * q + 1] = t.y, wb[4 * q + 2] = t.z, wb[4 * q + 3] = t.w;
-                    if (has_q) {
-                        t = __ldg(reinterpret_cast<const float4*>(quant_scale + j0) + q);
-                    }
+                    t = has_q ? __ldg(reinterpret_cast<const float4*>(quant_scale + j0) + q)
+                              : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
                     qs[4 * q] = t.x, qs[4 * q + 1] = t.y, qs[4 * q + 2] = t.z, qs[4 * q + 3] = t.w;
                 }
 #pragma unroll
                 for (int j = 0; j < EL; ++j) {
-                    out[i][j] = dqsq_element<XT>(a[j], b[j], wa[j], wb[j], qs[j], as, has_q, left != 0);
+                    out[i][j] = dqsq_element_by_role<XT>(a[j], b[j], wa[j], wb[j], qs[j], as);
                     m = fmaxf(m, fabsf(out[i][j]));
                 }
             }
@@ -211,7 +233,7 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
         if (tid == 0) {
             scale[row] = s;
         }
-        const float qf = divide ? s : __fdiv_rn(1.0f, s);
+        const float qf = DIVIDE ? s : __fdiv_rn(1.0f, s);
         int8_t* yr = y + row * H;
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
@@ -219,10 +241,10 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
             if (c < nchunks) {
                 const int64_t j0 = static_cast<int64_t>(c) * EL;
                 if constexpr (EL == 4) {
-                    *reinterpret_cast<uint32_t*>(yr + j0) = dqsq_quant4(out[i], qf, divide != 0, direct != 0);
+                    *reinterpret_cast<uint32_t*>(yr + j0) = dqsq_quant4<DIVIDE>(out[i], qf, direct != 0);
                 } else {
-                    const uint2 o = make_uint2(dqsq_quant4(out[i], qf, divide != 0, direct != 0),
-                                               dqsq_quant4(out[i] + 4, qf, divide != 0, direct != 0));
+                    const uint2 o = make_uint2(dqsq_quant4<DIVIDE>(out[i], qf, direct != 0),
+                                               dqsq_quant4<DIVIDE>(out[i] + 4, qf, direct != 0));
                     *reinterpret_cast<uint2*>(yr + j0) = o;
                 }
             }
@@ -288,13 +310,13 @@ static cudaError_t dispatch_dqsq(const void* x, const float* ws, const float* as
                           int, int);
     Kern kern = dqsq_long_rows_kernel<XT>;
     if (vec && chunks <= DQSQ_THREADS) {
-        kern = dqsq_rows_kernel<XT, 1>;
+        kern = divide ? dqsq_rows_kernel<XT, 1, true> : dqsq_rows_kernel<XT, 1, false>;
     } else if (vec && chunks <= 2 * DQSQ_THREADS) {
-        kern = dqsq_rows_kernel<XT, 2>;
+        kern = divide ? dqsq_rows_kernel<XT, 2, true> : dqsq_rows_kernel<XT, 2, false>;
     } else if (vec && chunks <= 4 * DQSQ_THREADS) {
-        kern = dqsq_rows_kernel<XT, 4>;
+        kern = dqsq_rows_kernel<XT, 4, false>;  // rows this long always take the reciprocal form
     } else if (vec && chunks <= 8 * DQSQ_THREADS) {
-        kern = dqsq_rows_kernel<XT, 8>;
+        kern = dqsq_rows_kernel<XT, 8, false>;
     }
     // one wave: as many CTAs as are resident at once, each walking rows with a grid stride
     int per_sm = 1;

@@ -12,9 +12,12 @@
 // elements t, t+32, ... in ascending order, then a butterfly over lane distances 16, 8, 4, 2, 1).  Equal
 // exponentials are ordered by ascending expert index.
 //
-// Mapping: one warp per row, the row held in registers (lane t owns elements t + 32 v); the k selections are
-// k rounds of a warp arg-max (two `redux.sync` each).  The operator moves rows * inner input elements and
-// 10 k bytes of output per row; at router sizes (inner <= 1024) it is bound by the exp arithmetic, not by HBM.
+// Mapping: one warp per row, the row held in registers (lane t owns elements t + 32 v).  Each lane ranks its own
+// elements once (larger exponential first, equal ones by ascending index) and parks them in that order in shared
+// memory; the k selections are then k rounds of "largest head of the 32 lists" - two `redux.sync`, one 8-byte
+// shared-memory load and a counter per round - instead of a scan of the lane's elements per round.  The operator
+// moves rows * inner input elements and 10 k bytes of output per row; at router sizes (inner <= 1024) it is bound
+// by the exp arithmetic, not by HBM.
 #include "common.cuh"
 
 namespace w8a8 {
@@ -49,7 +52,9 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
                                                                    int32_t* __restrict__ row_idx, int64_t rows,
                                                                    int inner, int k)
 {
+    __shared__ uint2 lists[GATING_WARPS][(VPT + 1) * 32];
     const int lane = threadIdx.x & 31;
+    uint2* list = lists[threadIdx.x >> 5];
     const int64_t warps = static_cast<int64_t>(gridDim.x) * GATING_WARPS;
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * GATING_WARPS + (threadIdx.x >> 5); r < rows; r += warps) {
         float v[VPT];
@@ -80,37 +85,50 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
             s = __fadd_rn(s, __shfl_xor_sync(FULL_MASK, s, off));
         }
         const bool fin = (finished != nullptr) && (finished[r] != 0);
+        // Selection keys: exponentials are >= 0, so their bit patterns order like unsigned integers; 0 marks what
+        // can never be selected (a NaN, which compares as below everything, and the padding past `inner`).
+        uint32_t key[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            key[i] = (v[i] >= 0.0f) ? __float_as_uint(v[i]) + 1u : 0u;
+        }
+        // position of each element in the lane's own order: larger key first, equal keys by ascending i
+        int pos[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            pos[i] = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+            for (int j = i + 1; j < VPT; ++j) {
+                const bool first = key[i] >= key[j];  // i stays in front of j
+                pos[j] += first ? 1 : 0;
+                pos[i] += first ? 0 : 1;
+            }
+        }
+        // list[p * 32 + lane] = the lane's p-th element as (key, expert index); one more entry that ends the list
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            list[pos[i] * 32 + lane] = make_uint2(key[i], static_cast<uint32_t>(lane + 32 * i));
+        }
+        list[VPT * 32 + lane] = make_uint2(0u, 0u);
         // Lane j keeps the j-th selection and the lanes store together after every 32 rounds: one division and one
         // store instruction per 32 results instead of one per result.
         uint32_t keep_top = 0u;
-        uint32_t keep_win = 0xffffffffu;
+        uint32_t keep_win = 0u;
+        int taken = 0;  // how many of this lane's elements have been selected
         for (int j = 0; j < k; ++j) {
-            // this lane's best remaining element: largest value, then smallest index (ascending i is ascending index)
-            float best = -1.0f;
-            int best_i = 0;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                if (v[i] > best) {
-                    best = v[i];
-                    best_i = i;
-                }
-            }
-            // exponentials are >= 0 (or NaN, which compares as below): their bit patterns order like unsigned integers
-            const uint32_t key = (best >= 0.0f) ? __float_as_uint(best) + 1u : 0u;
-            const uint32_t top = __reduce_max_sync(FULL_MASK, key);
-            const uint32_t idx = (key == top) ? static_cast<uint32_t>(lane + 32 * best_i) : 0xffffffffu;
-            const uint32_t win = __reduce_min_sync(FULL_MASK, idx);
-            if (static_cast<uint32_t>(lane + 32 * best_i) == win && key == top) {
-#pragma unroll
-                for (int i = 0; i < VPT; ++i) {
-                    if (i == best_i) {
-                        v[i] = -1.0f;
-                    }
-                }
-            }
+            const uint2 head = list[taken * 32 + lane];
+            const uint32_t top = __reduce_max_sync(FULL_MASK, head.x);
+            // the largest exponential, and among equal ones the smallest expert index; with nothing selectable left
+            // (only after NaNs) the result is a NaN with index 0
+            const uint32_t cand = (head.x == top && top != 0u) ? head.y : 0xffffffffu;
+            const uint32_t win = __reduce_min_sync(FULL_MASK, cand);
+            taken += (cand == win && top != 0u) ? 1 : 0;
             if (lane == (j & 31)) {
                 keep_top = top;
-                keep_win = win;
+                keep_win = (top != 0u) ? win : 0u;
             }
             if ((j & 31) == 31 || j == k - 1) {
                 const int jj = (j & ~31) + lane;  // the round this lane holds

@@ -297,6 +297,44 @@ extern "C" int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_
     return groups * batches * per_commit * 2 * umma_m * umma_n * 32;
 }
 
+namespace w8a8 {
+
+// canonical_expf against its defining sequence on every fp32 bit pattern: counts the patterns whose results differ
+// in any bit and keeps the smallest of them.
+__global__ void __launch_bounds__(256) exp_selftest_kernel(unsigned long long* out)
+{
+    unsigned long long bad = 0, first = ~0ull;
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < (1ull << 32);
+         i += stride) {
+        const float x = __uint_as_float(static_cast<uint32_t>(i));
+        if (__float_as_uint(canonical_expf(x)) != __float_as_uint(canonical_expf_as_defined(x))) {
+            ++bad;
+            first = (i < first) ? i : first;
+        }
+    }
+    if (bad != 0) {
+        atomicAdd(out, bad);
+        atomicMin(out + 1, first);
+    }
+}
+
+}  // namespace w8a8
+
+extern "C" int w8a8_selftest_exp(uint64_t* result, void* stream)
+{
+    if (result == nullptr) {
+        return W8A8_ERR_INVALID;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(result, 0, 8, st) != cudaSuccess || cudaMemsetAsync(result + 1, 0xff, 8, st) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    w8a8::exp_selftest_kernel<<<w8a8::sm_count() * 8, 256, 0, st>>>(reinterpret_cast<unsigned long long*>(result));
+    w8a8::note_launch();
+    return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
+}
+
 extern "C" int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream)
 {
     if (limit_cycles <= 0 || limit_cycles > 4000000000ll || error_words == nullptr) {

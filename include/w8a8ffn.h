@@ -528,6 +528,12 @@ int w8a8_mma_issue_probe(int cta_group, int umma_m, int umma_n, int a_mn_major, 
 int64_t w8a8_mma_issue_probe_ops(int cta_group, int umma_m, int umma_n, int per_commit, int64_t batches);
 int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void* stream);
 
+/* Self-test (no reference counterpart): evaluates the library's fp32 exp (the one the SwiGLU epilogues and the
+ * router softmax use) and the operation sequence that defines it on all 2^32 fp32 bit patterns.  result: two
+ * uint64 in device memory; [0] = number of patterns whose results differ in any bit (0 expected), [1] = the smallest
+ * such pattern (all ones when there is none).  One launch of a few milliseconds. */
+int w8a8_selftest_exp(uint64_t* result, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

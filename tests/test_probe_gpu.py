@@ -58,3 +58,16 @@ def test_mma_issue_probe_rejects_bad_shapes():
         assert lib.w8a8_mma_issue_probe(cg, m, n, 0, 1, 0, 1, 4, 4, 0, 10, None, None) == L.ERR_INVALID
     assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 4, 4, 4, 0, 10, None, None) == L.ERR_INVALID
     assert lib.w8a8_mma_issue_probe(1, 128, 256, 0, 1, 0, 1, 4, 9, 0, 10, None, None) == L.ERR_INVALID
+
+
+def test_exp_equals_its_defining_sequence_on_every_input():
+    """The kernels' exp is an instruction-count-reduced arrangement of the sequence the CPU oracle states; the
+    library compares the two on all 2^32 fp32 bit patterns."""
+    L, lib = _lib()
+    res = torch.zeros(2, dtype=torch.int64, device="cuda")
+    rc = lib.w8a8_selftest_exp(res.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.status_string(rc)
+    torch.cuda.synchronize()
+    bad, first = res.tolist()
+    assert bad == 0, f"{bad} patterns differ, the smallest is {first & 0xffffffff:#010x}"
+    assert lib.w8a8_selftest_exp(None, None) == L.ERR_INVALID
