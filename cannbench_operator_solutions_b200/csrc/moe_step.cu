@@ -1,5 +1,6 @@
 // The expert-parallel MoE FFN step as host C++ over this library's own entry
-// points: one call enqueues, on one stream and with no host readback,
+// points: one call enqueues, on the caller's stream (and a second one for two
+// pieces that can run beside it) and with no host readback,
 //   add_rms_norm_dynamic_quant -> route plan -> count all-gather -> address
 //   tables -> dispatch (rows stored straight into the owning rank's
 //   expert-major buffer, peer memory when that rank is another GPU) ->
@@ -215,6 +216,43 @@ static int step_barrier(const W8A8MoeFfnStep* s, int32_t* token, cudaStream_t st
     return nccl().all_reduce(token, token, 1, NCCL_INT32, NCCL_SUM, s->comm, st) == 0 ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
+// A second stream per device for the two pieces of the step that depend on nothing the main stream is busy with
+// (the normalisation + quantisation of the tokens beside the routing tables, and the row-pointer expansion beside
+// the up projection), with the events that fork it from and join it to the caller's stream.  Made on first use,
+// kept for the life of the process.  Fork and join are event waits, so a stream capture of the step follows
+// both streams.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork[2] = {nullptr, nullptr};
+    cudaEvent_t join[2] = {nullptr, nullptr};
+    bool ok = false;
+};
+
+static SideStream* side_stream()
+{
+    constexpr int MAX_DEVICES = 64;
+    static SideStream streams[MAX_DEVICES];
+    static std::mutex lock;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> guard(lock);
+    SideStream& s = streams[dev];
+    if (!s.ok) {
+        bool good = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess;
+        for (int i = 0; i < 2 && good; ++i) {
+            good = cudaEventCreateWithFlags(&s.fork[i], cudaEventDisableTiming) == cudaSuccess &&
+                   cudaEventCreateWithFlags(&s.join[i], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!good) {
+            return nullptr;
+        }
+        s.ok = true;
+    }
+    return &s;
+}
+
 extern "C" int w8a8_moe_ffn_step(const W8A8MoeFfnStep* s, const void* x, const void* residual, const void* gamma,
                                  float epsilon, const int32_t* expert_idx, const float* probs, void* out, void* x_out,
                                  void* stream)
@@ -253,9 +291,23 @@ extern "C" int w8a8_moe_ffn_step(const W8A8MoeFfnStep* s, const void* x, const v
     float* xe_scale = reinterpret_cast<float*>(local + s->off_s);
     void* back = local + s->off_back;
 
-    int rc = w8a8_add_rms_norm_dynamic_quant(x, residual, gamma, b.xq, x_out, b.xs, T, hidden, epsilon, s->dtype, 0, st);
+    SideStream* side = side_stream();
+    if (side == nullptr) {
+        return W8A8_ERR_CUDA;
+    }
+    // the tokens are normalised and quantised on the second stream while this one plans the routes, exchanges the
+    // counts and builds the address tables (small kernels that wait on latency, not on bandwidth)
+    if (cudaEventRecord(side->fork[0], st) != cudaSuccess ||
+        cudaStreamWaitEvent(side->stream, side->fork[0], 0) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    int rc = w8a8_add_rms_norm_dynamic_quant(x, residual, gamma, b.xq, x_out, b.xs, T, hidden, epsilon, s->dtype, 0,
+                                             side->stream);
     if (rc != W8A8_OK) {
         return rc;
+    }
+    if (cudaEventRecord(side->join[0], side->stream) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
     }
     rc = w8a8_route_plan(expert_idx, T, topk, E, b.count, b.cumsum, b.pos, b.plan_ws, b.plan_ws_bytes, st);
     if (rc != W8A8_OK) {
@@ -275,6 +327,20 @@ extern "C" int w8a8_moe_ffn_step(const W8A8MoeFfnStep* s, const void* x, const v
     if (rc != W8A8_OK) {
         return rc;
     }
+    // the tables are complete: the second stream expands them into one output address per expanded row while this
+    // one dispatches and runs the up projection
+    if (cudaEventRecord(side->fork[1], st) != cudaSuccess ||
+        cudaStreamWaitEvent(side->stream, side->fork[1], 0) != cudaSuccess) {
+        return W8A8_ERR_CUDA;
+    }
+    rc = w8a8_expand_row_pointers(b.seg_first, b.seg_ptr, nseg, cap, hidden * elem, b.out_ptrs, side->stream);
+    if (rc != W8A8_OK) {
+        return rc;
+    }
+    if (cudaEventRecord(side->join[1], side->stream) != cudaSuccess ||
+        cudaStreamWaitEvent(st, side->join[0], 0) != cudaSuccess) {  // the quantised tokens are ready
+        return W8A8_ERR_CUDA;
+    }
     // No barrier before the stores: this rank's all-gather has completed, so every other rank's stream has reached
     // its own all-gather of this step, which it enqueued after everything that read its buffers in the step before.
     rc = w8a8_dispatch_rows(b.xq, b.xs, expert_idx, b.pos, b.row_dst, b.scale_dst, b.my_base, T, topk, hidden, st);
@@ -290,9 +356,8 @@ extern "C" int w8a8_moe_ffn_step(const W8A8MoeFfnStep* s, const void* x, const v
     if (rc != W8A8_OK) {
         return rc;
     }
-    rc = w8a8_expand_row_pointers(b.seg_first, b.seg_ptr, nseg, cap, hidden * elem, b.out_ptrs, st);
-    if (rc != W8A8_OK) {
-        return rc;
+    if (cudaStreamWaitEvent(st, side->join[1], 0) != cudaSuccess) {  // the output addresses are ready
+        return W8A8_ERR_CUDA;
     }
     rc = w8a8_grouped_matmul_to_rows(b.h, s->w_down, nullptr, b.out_ptrs, b.hs, s->s_down, cap, hidden, inter, e_local,
                                      b.group_list, 2, W8A8_DT_I8, W8A8_DT_F32, s->dtype, W8A8_W_KN, b.mm_ws,

@@ -458,6 +458,10 @@ int w8a8_gmsq_host_pipe_destroy(W8A8HostPipe* pipe);
  * A step that routes more than cap_rows rows to some rank stores nothing out of bounds: that step's tables are
  * zeroed, its output is meaningless, and a sticky flag is raised that w8a8_moe_ffn_step_status reads and clears
  * (returns 1; it synchronises the stream).  Every rank must make the same sequence of step calls.
+ * The step runs two of its pieces (the normalisation + quantisation of the tokens, the row-pointer expansion) on a
+ * second stream that the library keeps per device, forked from and joined to `stream` by events: for the caller
+ * the step is ordered on `stream` like any other call, a stream capture follows both streams, and one step at a
+ * time may be in the making per device (two host threads must not call it for the same device at once).
  */
 typedef struct W8A8MoeFfnStep {
     int32_t world, rank;
