@@ -174,6 +174,30 @@ std::vector<int64_t> group_ends(const c10::List<int64_t>& list, int64_t experts,
     return ends;
 }
 
+// The tensor-core kernels take K in multiples of 16 bytes (8 elements for 16- and 32-bit operands) and N in multiples
+// of 16; the schemas accept any K and N.  Shapes in between are run on zero-padded copies and the result is cut
+// back: a zero K column adds nothing to any accumulator, and padded N columns are never returned, so the
+// returned elements are those of the unpadded problem bit for bit.
+int64_t round_up(int64_t v, int64_t to) { return (v + to - 1) / to * to; }
+
+// `t` with its last dimension zero-padded from its present size to `size` (the tensor itself when nothing is to add)
+Tensor widen_last(const Tensor& t, int64_t size)
+{
+    if (!t.defined() || t.size(-1) == size) {
+        return t;
+    }
+    return torch::constant_pad_nd(t, {0, size - t.size(-1)}, 0).contiguous();
+}
+
+// the last two dimensions zero-padded to [rows, cols]
+Tensor widen_last2(const Tensor& t, int64_t rows, int64_t cols)
+{
+    if (t.size(-2) == rows && t.size(-1) == cols) {
+        return t;
+    }
+    return torch::constant_pad_nd(t, {0, cols - t.size(-1), 0, rows - t.size(-2)}, 0).contiguous();
+}
+
 // ================================================================ dynamic_quant
 struct DynamicQuant {
     using Out = std::tuple<Tensor, Tensor>;
@@ -323,11 +347,28 @@ struct QuantMatmul {
                 }
             }
         }
-        call.done(w8a8_quant_matmul(Call::as<const int8_t>(a), Call::as<const int8_t>(b), sc.data_ptr(),
-                                    Call::as<const float>(off), Call::as<const float>(pt), Call::ptr(bs),
-                                    out.data_ptr(), batch, rows, cols, depth, flags,
+        // K and N as the kernels take them; per-channel operands grow with N (a scalar stays a scalar)
+        const int64_t depth_p = round_up(depth, 16), cols_p = round_up(cols, 16);
+        const bool padded = depth_p != depth || cols_p != cols;
+        const auto per_channel = [&](const Tensor& t) {
+            return (t.defined() && t.numel() > 1) ? widen_last(t.reshape({-1, cols}), cols_p) : t;
+        };
+        const Tensor a_p = widen_last(a, depth_p), b_p = widen_last2(b, depth_p, cols_p);
+        const Tensor sc_p = per_channel(sc), off_p = per_channel(off), bs_p = per_channel(bs);
+        Tensor out_p = out;
+        if (padded) {
+            std::vector<int64_t> dims = all_but_last(out);
+            dims.push_back(cols_p);
+            out_p = torch::empty(dims, out.options());
+        }
+        call.done(w8a8_quant_matmul(Call::as<const int8_t>(a_p), Call::as<const int8_t>(b_p), sc_p.data_ptr(),
+                                    Call::as<const float>(off_p), Call::as<const float>(pt), Call::ptr(bs_p),
+                                    out_p.data_ptr(), batch, rows, cols_p, depth_p, flags,
                                     out.scalar_type() == torch::kBFloat16 ? W8A8_DT_BF16 : W8A8_DT_F16, W8A8_W_KN,
-                                    bias_per_batch ? cols : 0, call.stream()));
+                                    bias_per_batch ? cols_p : 0, call.stream()));
+        if (padded) {
+            out.copy_(out_p.narrow(-1, 0, cols));
+        }
         return out;
     }
 };
@@ -368,13 +409,31 @@ struct GroupedMatmulSwigluQuant {
         call.require(ws.dim() == 2 && ws.size(0) == e && ws.size(1) == n,
                      "grouped_matmul_swiglu_quant: weight_scale must be [E, N]");
         const std::vector<int64_t> ends = group_ends(group_list, e, m, "grouped_matmul_swiglu_quant");
-        const size_t bytes = w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e);
+        // The gate columns are the first half of N and the up columns the second: each half is padded on its own.
+        // A padded column has weight 0, so its activation is silu(0) * 0 = 0: it neither moves the row maximum
+        // nor is it returned.
+        const int64_t half = n / 2, half_p = round_up(half, 16), k_p = round_up(k, 16);
+        const bool padded = half_p != half || k_p != k;
+        Tensor rows_p = rows, w_p = w, ws_p = ws, y_p = std::get<0>(out);
+        if (padded) {
+            rows_p = widen_last(rows, k_p);
+            w_p = torch::cat({widen_last2(w.narrow(2, 0, half), k_p, half_p), widen_last2(w.narrow(2, half, half), k_p, half_p)},
+                             2)
+                      .contiguous();
+            ws_p = torch::cat({widen_last(ws.narrow(1, 0, half), half_p), widen_last(ws.narrow(1, half, half), half_p)}, 1)
+                       .contiguous();
+            y_p = torch::empty({m, half_p}, y_p.options());
+        }
+        const size_t bytes = w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k_p, 2 * half_p, e);
         const Tensor ws_buf = call.scratch(bytes, rows);
-        call.done(w8a8_grouped_matmul_swiglu_quant(Call::as<const int8_t>(rows), Call::as<const int8_t>(w),
-                                                   Call::as<const float>(ws), Call::as<const float>(xs),
-                                                   Call::as<int8_t>(std::get<0>(out)),
-                                                   Call::as<float>(std::get<1>(out)), m, k, n, e, ends.data(), 0,
-                                                   W8A8_W_KN, 0, ws_buf.data_ptr(), bytes, call.stream()));
+        call.done(w8a8_grouped_matmul_swiglu_quant(Call::as<const int8_t>(rows_p), Call::as<const int8_t>(w_p),
+                                                   Call::as<const float>(ws_p), Call::as<const float>(xs),
+                                                   Call::as<int8_t>(y_p), Call::as<float>(std::get<1>(out)), m, k_p,
+                                                   2 * half_p, e, ends.data(), 0, W8A8_W_KN, 0, ws_buf.data_ptr(),
+                                                   bytes, call.stream()));
+        if (padded) {
+            std::get<0>(out).copy_(y_p.narrow(1, 0, half));
+        }
         return out;
     }
 };
@@ -441,14 +500,27 @@ struct GroupedMatmul {
         call.require(!b.defined() || b.numel() == e * n, "grouped_matmul: bias must have shape [E, N]");
         const Tensor y = joined(rows, w, transpose_weight, x_scale);
         if (m > 0) {
-            const size_t bytes = (type_bit(rows) == F32) ? w8a8_grouped_matmul_f32_workspace_size(m, n, k, e)
-                                                         : w8a8_grouped_matmul_workspace_size(m, n, k, e);
+            const int64_t k_p = round_up(k, quantised ? 16 : 8), n_p = round_up(n, 16);
+            const bool padded = k_p != k || n_p != n;
+            Tensor rows_p = rows, w_p = w, b_p = b, ws_p = ws, y_p = y;
+            if (padded) {
+                rows_p = widen_last(rows, k_p);
+                w_p = transpose_weight ? widen_last2(w, n_p, k_p) : widen_last2(w, k_p, n_p);
+                b_p = b.defined() ? widen_last(b.reshape({e, n}), n_p) : b;
+                ws_p = ws.defined() ? widen_last(ws.reshape({e, n}), n_p) : ws;
+                y_p = torch::empty({m, n_p}, y.options());
+            }
+            const size_t bytes = (type_bit(rows) == F32) ? w8a8_grouped_matmul_f32_workspace_size(m, n_p, k_p, e)
+                                                         : w8a8_grouped_matmul_workspace_size(m, n_p, k_p, e);
             const Tensor ws_buf = call.scratch(bytes, rows);
-            call.done(w8a8_grouped_matmul(rows.data_ptr(), w.data_ptr(), Call::ptr(b), y.data_ptr(),
-                                          Call::as<const float>(xs), Call::as<const float>(ws), m, n, k, e,
+            call.done(w8a8_grouped_matmul(rows_p.data_ptr(), w_p.data_ptr(), Call::ptr(b_p), y_p.data_ptr(),
+                                          Call::as<const float>(xs), Call::as<const float>(ws_p), m, n_p, k_p, e,
                                           ends.data(), 0, abi_type(rows), b.defined() ? abi_type(b) : abi_type(rows),
                                           abi_type(y), transpose_weight ? W8A8_W_NK : W8A8_W_KN, ws_buf.data_ptr(),
                                           bytes, call.stream()));
+            if (padded) {
+                y.copy_(y_p.narrow(1, 0, n));
+            }
         }
         return views(y, ends, split_item);
     }

@@ -124,3 +124,88 @@ def test_plugin_dequant_swiglu_quant_matches_ctypes_operator(cb, ops):
         cb.dequant_swiglu_quant(x)
     with pytest.raises(RuntimeError, match="must be None for float16"):
         cb.dequant_swiglu_quant(xb, ws[:128])
+
+
+def _bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _i8(rng, shape):
+    return torch.from_numpy(rng.integers(-127, 128, shape).astype(np.int8)).cuda()
+
+
+@pytest.mark.parametrize("m,k,n", [(37, 40, 24), (130, 100, 250), (5, 17, 1)])
+def test_plugin_quant_matmul_any_k_and_n(cb, oracle, m, k, n):
+    """The schema takes any K and N; the kernels take multiples of 16.  The plugin runs shapes in between on
+    zero-padded copies and cuts the result back: the returned elements are the oracle's on the unpadded problem."""
+    O = oracle
+    rng = np.random.default_rng(100 + k)
+    x1, x2 = _i8(rng, (m, k)), _i8(rng, (k, n))
+    scale = torch.from_numpy(rng.uniform(1e-3, 1e-2, n).astype(np.float32)).cuda()
+    offset = torch.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)).cuda()
+    pt = torch.from_numpy(rng.uniform(1e-3, 5e-2, m).astype(np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).cuda()
+    per = O.QM_SCALE_PERCHAN | O.QM_OFFSET_PERCHAN | O.QM_BIAS_PERCHAN if n > 1 else 0
+    got = cb.quant_matmul(x1, x2, scale, offset=offset, pertoken_scale=pt, bias=bias, output_dtype="bfloat16")
+    assert got.shape == (m, n)
+    ref = O.quant_matmul(x1.cpu().numpy(), x2.cpu().numpy(), scale.cpu().numpy(), offset=offset.cpu().numpy(),
+                         pertoken=pt.cpu().numpy(), bias=bias.cpu().numpy(),
+                         flags=per | O.QM_HAS_OFFSET | O.QM_HAS_PT | (O.QM_BIAS_F32 << O.QM_BIAS_SHIFT),
+                         out_dtype=O.DT_BF16)
+    assert np.array_equal(_bits(got), ref)
+    # batched, one bias row per batch entry
+    xb, wb = _i8(rng, (2, m, k)), _i8(rng, (2, k, n))
+    bb = torch.from_numpy(rng.standard_normal((2, 1, n)).astype(np.float32)).cuda()
+    got = cb.quant_matmul(xb, wb, scale, bias=bb)
+    assert got.shape == (2, m, n)
+    for i in range(2):
+        ref = O.quant_matmul(xb[i].cpu().numpy(), wb[i].cpu().numpy(), scale.cpu().numpy(),
+                             bias=bb[i, 0].cpu().numpy(),
+                             flags=(O.QM_SCALE_PERCHAN | O.QM_BIAS_PERCHAN if n > 1 else 0)
+                             | (O.QM_BIAS_F32 << O.QM_BIAS_SHIFT), out_dtype=O.DT_F16)
+        assert np.array_equal(_bits(got[i]), ref)
+
+
+@pytest.mark.parametrize("k,half", [(72, 40), (100, 129), (256, 8)])
+def test_plugin_gmsq_any_k_and_n(cb, oracle, k, half):
+    rng = np.random.default_rng(200 + half)
+    counts = [33, 0, 140, 7]
+    gl = np.cumsum(counts).tolist()
+    m, e, n = gl[-1], len(counts), 2 * half
+    x, w = _i8(rng, (m, k)), _i8(rng, (e, k, n))
+    ws = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n)).astype(np.float32)).cuda()
+    xs = torch.from_numpy(rng.uniform(1e-3, 5e-2, m).astype(np.float32)).cuda()
+    y, ys = cb.grouped_matmul_swiglu_quant(x, w, ws, xs, gl)
+    want_y, want_s = oracle.grouped_matmul_swiglu_quant(x.cpu().numpy(), w.cpu().numpy(), ws.cpu().numpy(),
+                                                        xs.cpu().numpy(), gl)
+    assert y.shape == (m, half)
+    assert np.array_equal(y.cpu().numpy(), want_y)
+    assert ys.cpu().numpy().tobytes() == want_s.tobytes()
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_plugin_grouped_matmul_any_k_and_n(cb, oracle, transpose):
+    O = oracle
+    rng = np.random.default_rng(300)
+    gl = [50, 50, 131]
+    m, k, n, e = 131, 100, 40, 3
+    x, w = _i8(rng, (m, k)), _i8(rng, (e, k, n))
+    ws = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n)).astype(np.float32)).cuda()
+    xs = torch.from_numpy(rng.uniform(1e-3, 5e-2, m).astype(np.float32)).cuda()
+    bias = torch.from_numpy(rng.standard_normal((e, n)).astype(np.float32)).cuda()
+    wt = w.transpose(1, 2).contiguous() if transpose else w
+    got = cb.grouped_matmul(x, wt, gl, bias, 2, transpose, xs, ws)[0]
+    ref = O.grouped_matmul(x.cpu().numpy(), w.cpu().numpy(), gl, dtype=O.DT_I8, x_scale=xs.cpu().numpy(),
+                           w_scale=ws.cpu().numpy(), bias=bias.cpu().numpy(), bias_dtype=O.DT_F32)
+    assert got.shape == (m, n) and np.array_equal(_bits(got), ref)
+    # the float form: K = 100 is not a multiple of 8 for fp32 either; fp64 product as the yardstick
+    xf = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda()
+    wf = torch.from_numpy((rng.standard_normal((e, k, n)) * 0.1).astype(np.float32)).cuda()
+    for dtype, tol in ((torch.float32, 2.0**-18), (torch.bfloat16, 2.0**-7)):
+        xd, wd = xf.to(dtype), wf.to(dtype)
+        wdt = wd.transpose(1, 2).contiguous() if transpose else wd
+        outs = cb.grouped_matmul(xd, wdt, gl, None, 0, transpose)
+        assert [o.shape for o in outs] == [(50, n), (0, n), (81, n)]
+        ref = torch.cat([xd[:50].double() @ wd[0].double(), xd[50:].double() @ wd[2].double()]).cpu()
+        err = (torch.cat(list(outs)).double().cpu() - ref).abs().max().item()
+        assert err <= ref.abs().max().item() * tol, (dtype, err)
