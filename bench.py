@@ -433,6 +433,12 @@ class QmmWorkload(Workload):
     def kernel_step(self):
         return self.gpu_step()
 
+    def plain_read_step(self):
+        """The weight matrix read once by a kernel that does nothing else."""
+        rc = self.L.load().w8a8_stream_read_probe(self.w.data_ptr(), self.w.numel(), None,
+                                                  self.torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, self.L.status_string(rc)
+
     def units_per_step(self):
         return 2.0 * self.M * self.K * self.n / 1e12
 
@@ -1223,6 +1229,21 @@ def main():
     k1.record()
     torch.cuda.synchronize()
     ms_kernel = k0.elapsed_time(k1) / args.steps
+    # yardstick of the weight-streaming matmul shapes: the same bytes read once by a kernel that does nothing else,
+    # timed the same way (K launches, as a graph replay when the step is timed as one)
+    ms_plain_read = None
+    if hasattr(wl, "plain_read_step") and wl.bound == "hbm":
+        wl.plain_read_step()
+        torch.cuda.synchronize()
+        g2 = None
+        if graph is not None:
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2):
+                for _ in range(args.steps):
+                    wl.plain_read_step()
+            g2.replay()
+            torch.cuda.synchronize()
+        ms_plain_read = float(np.median(timed_regions(torch, barrier, wl.plain_read_step, args.steps, args.repeats, g2)))
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end with host buffers ----
@@ -1295,6 +1316,11 @@ def main():
                          "traffic_source": primary["traffic_source"], "kernel_ms": ms_kernel,
                          "peak_source": peak_note},
         }
+        if ms_plain_read is not None:
+            line["roofline"]["plain_read_of_the_weights_ms"] = ms_plain_read
+            line["roofline"]["frac_of_plain_read"] = ms_plain_read / ms_per_step  # both medians of the same regions
+            line["roofline"]["plain_read_note"] = ("one launch of w8a8_stream_read_probe over the weight matrix (the "
+                                                   "bytes this shape has to move), timed like the step")
         if secondary is not None:
             line["secondary"] = secondary
         if e2e_ms is not None:

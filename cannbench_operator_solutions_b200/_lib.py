@@ -87,6 +87,7 @@ SIGNATURES = {
     "w8a8_mma_issue_probe_ops": (_i64, [_i32, _i32, _i32, _i32, _i64]),
     "w8a8_selftest_bounded_wait": (_i32, [_i64, _vp, _vp]),
     "w8a8_selftest_exp": (_i32, [_vp, _vp]),
+    "w8a8_stream_read_probe": (_i32, [_vp, _i64, _vp, _vp]),
 }
 
 class MoeFfnStep(ctypes.Structure):

@@ -538,6 +538,12 @@ int w8a8_selftest_bounded_wait(int64_t limit_cycles, int32_t* error_words, void*
  * such pattern (all ones when there is none).  One launch of a few milliseconds. */
 int w8a8_selftest_exp(uint64_t* result, void* stream);
 
+/* Measurement aid (no reference counterpart): one launch that reads `bytes` (a multiple of 16, 16-byte aligned) of
+ * device memory once with streaming loads and does nothing else - what pulling that many bytes out of HBM costs in
+ * a single launch, the yardstick bench.py prints beside the weight-streaming quant_matmul shapes.  sink: 4 bytes of
+ * device memory that are practically never written, or NULL. */
+int w8a8_stream_read_probe(const void* src, int64_t bytes, void* sink, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
