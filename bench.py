@@ -1053,6 +1053,33 @@ MMA_PEAK_SHAPES = [
 ]
 
 
+def issue_probe_figures(torch, lib):
+    """The tensor pipe's own rate on the matmul kernels' instruction shape (CTA pair, 256 x 256 x 32, int8, random
+    operands resident in shared memory): back to back, and with one barrier wait per eight instructions as in the
+    kernels' main loop.  Two launches of a few milliseconds."""
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+    for key, per, depth in (("back_to_back_tops", 64, 2), ("one_wait_per_8_instructions_tops", 8, 4)):
+        batches = 40000 // per
+        times = []
+        for _ in range(3):  # the first launch is the warm-up
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = lib.w8a8_mma_issue_probe(2, 256, 256, 0, 1, 1, 1, per, depth, 0, batches, err.data_ptr(), st)
+            e1.record()
+            if rc != 0:
+                return None
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        out[key] = round(lib.w8a8_mma_issue_probe_ops(2, 256, 256, per, batches) / (min(times[1:]) * 1e-3) / 1e12, 1)
+    if int(err[0]) != 0:
+        return None
+    out["note"] = ("w8a8_mma_issue_probe, no loads and no epilogue, measured in this run after the timed regions "
+                   "(python bench.py --workload mma_peak lists every shape)")
+    return out
+
+
 def run_mma_peak(args):
     """Issue-bound rate of tcgen05.mma kind::i8 per instruction shape (w8a8_mma_issue_probe), CUDA events around one
     launch of about 20 ms each, SM clock sampled meanwhile.  Prints one JSON line."""
@@ -1245,6 +1272,9 @@ def main():
             torch.cuda.synchronize()
         ms_plain_read = float(np.median(timed_regions(torch, barrier, wl.plain_read_step, args.steps, args.repeats, g2)))
     clocks = sampler.stop() if rank == 0 else None
+    probe = None
+    if rank == 0 and wl.bound == "tensor":
+        probe = issue_probe_figures(torch, _L.load())
 
     # ---- end to end with host buffers ----
     e2e_ms, h2d, d2h = None, 0, 0
@@ -1316,6 +1346,8 @@ def main():
                          "traffic_source": primary["traffic_source"], "kernel_ms": ms_kernel,
                          "peak_source": peak_note},
         }
+        if probe is not None:
+            line["roofline"]["int8_issue_probe"] = probe
         if ms_plain_read is not None:
             line["roofline"]["plain_read_of_the_weights_ms"] = ms_plain_read
             line["roofline"]["frac_of_plain_read"] = ms_plain_read / ms_per_step  # both medians of the same regions
