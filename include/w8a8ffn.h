@@ -247,8 +247,8 @@ int w8a8_set_gemm_shape(int shape);
 /* Test and tuning hook (no reference counterpart): grouped_matmul_swiglu_quant requantises in a second kernel over
  * the stored activations (on = 0, the default) or inside the matmul kernels (on = 1): the CTAs that compute the
  * column tiles of a row block each quantise a share of its rows one tile later, once all column tiles have been
- * counted.  Identical results and, measured, the same time to within 2 %; the fused form reads the activations back
- * from L2 and has one launch less, but its CTAs wait for one another (bounded; error word 2), which assumes that
+ * counted.  Identical results and, measured, the same time to within 2 % and the same DRAM traffic; the fused form
+ * has one launch less, but its CTAs wait for one another (bounded; error word 2), which assumes that
  * the CTAs of the launch are resident together.  Used only when N / 2 spans at most half as many 128-column tiles
  * as the GPU has SMs; otherwise the call runs the second kernel.  Returns the previous setting. */
 int w8a8_set_gmsq_fused_requant(int on);
