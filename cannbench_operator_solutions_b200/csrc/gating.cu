@@ -44,7 +44,8 @@ __device__ __forceinline__ void gating_store(void* y, int64_t i, float v)
 
 constexpr int GATING_WARPS = 4;
 
-template <int DT, int VPT>
+// FULL: inner == 32 * VPT, so no element needs a bounds check.
+template <int DT, int VPT, bool FULL>
 __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* __restrict__ x,
                                                                    const uint8_t* __restrict__ finished,
                                                                    void* __restrict__ y,
@@ -52,9 +53,9 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
                                                                    int32_t* __restrict__ row_idx, int64_t rows,
                                                                    int inner, int k)
 {
-    __shared__ uint2 lists[GATING_WARPS][(VPT + 1) * 32];
+    __shared__ int2 lists[GATING_WARPS][(VPT + 1) * 32];
     const int lane = threadIdx.x & 31;
-    uint2* list = lists[threadIdx.x >> 5];
+    int2* list = lists[threadIdx.x >> 5];
     const int64_t warps = static_cast<int64_t>(gridDim.x) * GATING_WARPS;
     for (int64_t r = static_cast<int64_t>(blockIdx.x) * GATING_WARPS + (threadIdx.x >> 5); r < rows; r += warps) {
         float v[VPT];
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int c = lane + 32 * i;
-            v[i] = (c < inner) ? gating_load<DT>(x, r * inner + c) : -INFINITY;
+            v[i] = (FULL || c < inner) ? gating_load<DT>(x, r * inner + c) : -INFINITY;
             m = fmaxf(m, v[i]);
         }
 #pragma unroll
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int c = lane + 32 * i;
-            if (c < inner) {
+            if (FULL || c < inner) {
                 v[i] = canonical_expf(__fsub_rn(v[i], m));
                 s = __fadd_rn(s, v[i]);
             } else {
@@ -85,12 +86,12 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
             s = __fadd_rn(s, __shfl_xor_sync(FULL_MASK, s, off));
         }
         const bool fin = (finished != nullptr) && (finished[r] != 0);
-        // Selection keys: exponentials are >= 0, so their bit patterns order like unsigned integers; 0 marks what
-        // can never be selected (a NaN, which compares as below everything, and the padding past `inner`).
-        uint32_t key[VPT];
+        // Selection keys: exponentials are >= 0, so their bit patterns order like integers; what can never be
+        // selected (a NaN, which fmaxf drops, and the padding past `inner`) gets the bits of -1, a negative integer.
+        int key[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            key[i] = (v[i] >= 0.0f) ? __float_as_uint(v[i]) + 1u : 0u;
+            key[i] = __float_as_int(fmaxf(v[i], -1.0f));
         }
         // position of each element in the lane's own order: larger key first, equal keys by ascending i
         int pos[VPT];
@@ -110,33 +111,33 @@ __global__ void __launch_bounds__(GATING_WARPS * 32) gating_kernel(const void* _
         // list[p * 32 + lane] = the lane's p-th element as (key, expert index); one more entry that ends the list
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            list[pos[i] * 32 + lane] = make_uint2(key[i], static_cast<uint32_t>(lane + 32 * i));
+            list[pos[i] * 32 + lane] = make_int2(key[i], lane + 32 * i);
         }
-        list[VPT * 32 + lane] = make_uint2(0u, 0u);
+        list[VPT * 32 + lane] = make_int2(-1, 0);
         // Lane j keeps the j-th selection and the lanes store together after every 32 rounds: one division and one
         // store instruction per 32 results instead of one per result.
-        uint32_t keep_top = 0u;
-        uint32_t keep_win = 0u;
+        int keep_top = -1;
+        int keep_win = 0;
         int taken = 0;  // how many of this lane's elements have been selected
         for (int j = 0; j < k; ++j) {
-            const uint2 head = list[taken * 32 + lane];
-            const uint32_t top = __reduce_max_sync(FULL_MASK, head.x);
+            const int2 head = list[taken * 32 + lane];
+            const int top = __reduce_max_sync(FULL_MASK, head.x);
             // the largest exponential, and among equal ones the smallest expert index; with nothing selectable left
             // (only after NaNs) the result is a NaN with index 0
-            const uint32_t cand = (head.x == top && top != 0u) ? head.y : 0xffffffffu;
-            const uint32_t win = __reduce_min_sync(FULL_MASK, cand);
-            taken += (cand == win && top != 0u) ? 1 : 0;
+            const unsigned cand = (head.x == top && top >= 0) ? static_cast<unsigned>(head.y) : 0xffffffffu;
+            const unsigned win = __reduce_min_sync(FULL_MASK, cand);
+            taken += (cand == win && top >= 0) ? 1 : 0;
             if (lane == (j & 31)) {
                 keep_top = top;
-                keep_win = (top != 0u) ? win : 0u;
+                keep_win = (top >= 0) ? static_cast<int>(win) : 0;
             }
             if ((j & 31) == 31 || j == k - 1) {
                 const int jj = (j & ~31) + lane;  // the round this lane holds
                 if (jj <= j) {
-                    const float e = (keep_top != 0u) ? __uint_as_float(keep_top - 1u) : NAN;
+                    const float e = (keep_top >= 0) ? __int_as_float(keep_top) : NAN;
                     const int64_t o = r * k + jj;
                     gating_store<DT>(y, o, __fdiv_rn(e, s));
-                    expert_idx[o] = fin ? inner : static_cast<int32_t>(keep_win);
+                    expert_idx[o] = fin ? inner : keep_win;
                     row_idx[o] = static_cast<int32_t>(static_cast<int64_t>(jj) * rows + r);
                 }
             }
@@ -151,7 +152,12 @@ static cudaError_t launch_gating(const void* x, const uint8_t* finished, void* y
     const int64_t want = (rows + GATING_WARPS - 1) / GATING_WARPS;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-    gating_kernel<DT, VPT><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k); w8a8::note_launch();
+    if (inner == 32 * VPT) {
+        gating_kernel<DT, VPT, true><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k);
+    } else {
+        gating_kernel<DT, VPT, false><<<grid, GATING_WARPS * 32, 0, st>>>(x, finished, y, expert_idx, row_idx, rows, inner, k);
+    }
+    w8a8::note_launch();
     return cudaGetLastError();
 }
 
