@@ -71,3 +71,19 @@ def test_exp_equals_its_defining_sequence_on_every_input():
     bad, first = res.tolist()
     assert bad == 0, f"{bad} patterns differ, the smallest is {first & 0xffffffff:#010x}"
     assert lib.w8a8_selftest_exp(None, None) == L.ERR_INVALID
+
+
+def test_stream_read_probe_runs_and_checks_its_arguments():
+    """The plain-read yardstick: reads a buffer once, writes nothing, rejects sizes and addresses that are not
+    multiples of 16."""
+    L, lib = _lib()
+    buf = torch.randint(0, 255, (1 << 20,), dtype=torch.uint8, device="cuda")
+    before = buf.clone()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.w8a8_stream_read_probe(buf.data_ptr(), buf.numel(), None, st) == 0
+    assert lib.w8a8_stream_read_probe(buf.data_ptr(), 0, None, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(buf, before)
+    assert lib.w8a8_stream_read_probe(buf.data_ptr(), 24, None, st) == L.ERR_INVALID
+    assert lib.w8a8_stream_read_probe(buf.data_ptr() + 8, 32, None, st) == L.ERR_INVALID
+    assert lib.w8a8_stream_read_probe(None, 32, None, st) == L.ERR_INVALID
