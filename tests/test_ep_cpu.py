@@ -182,3 +182,54 @@ def test_expert_placement_covers_every_row_once_and_balances_tiles():
     _, loads_rep, replicas = bench.place_experts(counts, 8, "replicate")
     assert max(loads_lpt) / (sum(loads_lpt) / 8) > 1.5
     assert max(loads_rep) / (sum(loads_rep) / 8) < 1.2 and replicas >= 1
+
+
+@pytest.mark.timeout(300)
+def test_four_rank_chain_equals_single_rank():
+    """The same check with four ranks (two experts and twelve tokens each)."""
+    single_out, single_xout, _ = _run_chain(0, 1)
+    world = 4
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    out = np.concatenate([ret[r][0] for r in range(world)], 0)
+    x_out = np.concatenate([ret[r][1] for r in range(world)], 0)
+    assert np.array_equal(out, _bits(single_out))
+    assert np.array_equal(x_out, _bits(single_xout))
+    assert sum(int(ret[r][2].sum()) for r in range(world)) == 48 * 2
+
+
+def _worker_with_absent_peer(rank, world, port, ret):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        if rank == 1:
+            ret[rank] = "left before the step"  # never posts its counts
+            return
+        try:
+            _run_chain(rank, world)
+            ret[rank] = "completed"
+        except Exception as e:  # noqa: BLE001 - whatever the backend raises, it must be raised, not waited out
+            ret[rank] = "error: " + type(e).__name__
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+@pytest.mark.timeout(240)
+def test_a_rank_that_never_joins_the_step_is_an_error_not_a_hang():
+    """Failure detection on the host: one rank leaves between steps; the other rank's count exchange ends with an
+    exception inside the process group's timeout instead of waiting for ever."""
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker_with_absent_peer, args=(world, port, ret), nprocs=world, join=True)
+    assert ret[1] == "left before the step"
+    assert str(ret[0]).startswith("error: "), ret[0]
