@@ -460,3 +460,69 @@ def test_host_front_end_equals_the_whole_tensor_operator(ops, chunk, cta_group):
     assert torch.equal(got_y2, want_y.cpu()) and torch.equal(got_s2, want_s.cpu())
     with pytest.raises(RuntimeError, match="cumsum"):
         front(x.cpu(), xs.cpu(), [5, 3] + gl[2:])
+
+
+def test_grouped_operators_capture_into_a_cuda_graph(oracle):
+    """With the group list in device memory the grouped operators read nothing back and allocate nothing, so the up
+    projection and the down projection can be captured into one CUDA graph; a replay after the inputs AND the group
+    list have been overwritten in place gives the oracle's bits for the new problem (the tile tables are rebuilt on
+    the device inside the graph)."""
+    from cannbench_operator_solutions_b200 import _lib as L
+
+    O = oracle
+    lib = L.load()
+    rng = np.random.default_rng(77)
+    m, k, n, e, n2 = 900, 256, 512, 5, 384
+    x = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    xs = torch.empty((m,), dtype=torch.float32, device="cuda")
+    gl = torch.empty((e,), dtype=torch.int64, device="cuda")
+    w = _i8(rng, (e, k, n))
+    ws = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n)).astype(F)).cuda()
+    w2 = _i8(rng, (e, n // 2, n2))
+    ws2 = torch.from_numpy(rng.uniform(1e-3, 1e-2, (e, n2)).astype(F)).cuda()
+    y = torch.zeros((m, n // 2), dtype=torch.int8, device="cuda")
+    ys = torch.zeros((m,), dtype=torch.float32, device="cuda")
+    out = torch.zeros((m, n2), dtype=torch.bfloat16, device="cuda")
+    need1 = lib.w8a8_grouped_matmul_swiglu_quant_workspace_size(m, k, n, e)
+    need2 = lib.w8a8_grouped_matmul_workspace_size(m, n2, n // 2, e)
+    wsb1 = torch.empty((need1,), dtype=torch.uint8, device="cuda")
+    wsb2 = torch.empty((need2,), dtype=torch.uint8, device="cuda")
+
+    def fill(counts, seed):
+        r = np.random.default_rng(seed)
+        x.copy_(torch.from_numpy(r.integers(-127, 128, (m, k)).astype(np.int8)))
+        xs.copy_(torch.from_numpy(r.uniform(1e-3, 5e-2, m).astype(F)))
+        gl.copy_(torch.from_numpy(np.cumsum(counts).astype(np.int64)))
+
+    def enqueue():
+        st = torch.cuda.current_stream().cuda_stream
+        rc = lib.w8a8_grouped_matmul_swiglu_quant(x.data_ptr(), w.data_ptr(), ws.data_ptr(), xs.data_ptr(),
+                                                  y.data_ptr(), ys.data_ptr(), m, k, n, e, gl.data_ptr(), 1, L.W_KN, 0,
+                                                  wsb1.data_ptr(), need1, st)
+        assert rc == 0, L.status_string(rc)
+        rc = lib.w8a8_grouped_matmul(y.data_ptr(), w2.data_ptr(), None, out.data_ptr(), ys.data_ptr(), ws2.data_ptr(),
+                                     m, n2, n // 2, e, gl.data_ptr(), 1, L.DT_I8, L.DT_F32, L.DT_BF16, L.W_KN,
+                                     wsb2.data_ptr(), need2, st)
+        assert rc == 0, L.status_string(rc)
+
+    first, second = [300, 0, 257, 43, 300], [1, 640, 0, 130, 129]
+    fill(first, 1)
+    enqueue()  # warm-up outside the capture (function attributes, first-use initialisation)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        enqueue()
+    for counts, seed in ((first, 1), (second, 2), (first, 3)):
+        fill(counts, seed)
+        y.zero_(), ys.zero_(), out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        gl_host = np.cumsum(counts).tolist()
+        want_y, want_s = O.grouped_matmul_swiglu_quant(x.cpu().numpy(), w.cpu().numpy(), ws.cpu().numpy(),
+                                                       xs.cpu().numpy(), gl_host)
+        assert np.array_equal(y.cpu().numpy(), want_y), counts
+        assert ys.cpu().numpy().tobytes() == want_s.tobytes(), counts
+        want_out = O.grouped_matmul(want_y, w2.cpu().numpy(), gl_host, dtype=O.DT_I8, x_scale=want_s,
+                                    w_scale=ws2.cpu().numpy())
+        assert np.array_equal(bits(out), want_out), counts
+        assert lib.w8a8_workspace_error(wsb1.data_ptr(), None) == 0
