@@ -205,12 +205,13 @@ struct GroupEndsByValue {
 constexpr int PLAN_ALL = 0;
 constexpr int PLAN_WHOLE = 1;
 constexpr int PLAN_LEFTOVER = 2;
+constexpr int PLAN_BOTH = 3;  // host side only: PLAN_WHOLE at 256 rows and PLAN_LEFTOVER at 128 rows in one launch
 
-__global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restrict__ dev_list,
-                                                          const GroupEndsByValue by_value, int use_by_value,
-                                                          int64_t E, int64_t M, GroupedHeader* header,
-                                                          TileEntry* tiles, int64_t max_tiles, int tile_m, int mode,
-                                                          int32_t* shared_error, int allow_prefix)
+__device__ __forceinline__ void plan_groups_body(const int64_t* __restrict__ dev_list,
+                                                 const GroupEndsByValue& by_value, int use_by_value, int64_t E,
+                                                 int64_t M, GroupedHeader* header, TileEntry* tiles,
+                                                 int64_t max_tiles, int tile_m, int mode, int32_t* shared_error,
+                                                 int allow_prefix)
 {
     extern __shared__ int32_t s_first[];  // first tile index of each group, E + 1 entries
     __shared__ int32_t s_warp_sum[8];
@@ -309,6 +310,44 @@ __global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restr
             te.m_rows = static_cast<int32_t>(left < tile_m ? left : tile_m);
             te.pad = 0;
             tiles[first + t] = te;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) plan_groups_kernel(const int64_t* __restrict__ dev_list,
+                                                          const GroupEndsByValue by_value, int use_by_value,
+                                                          int64_t E, int64_t M, GroupedHeader* header,
+                                                          TileEntry* tiles, int64_t max_tiles, int tile_m, int mode,
+                                                          int32_t* shared_error, int allow_prefix)
+{
+    plan_groups_body(dev_list, by_value, use_by_value, E, M, header, tiles, max_tiles, tile_m, mode, shared_error,
+                     allow_prefix);
+}
+
+// Both tile tables of the two-launch form in one launch: CTA 0 plans the 256-row blocks, CTA 1 the leftovers of at
+// most 128 rows (each validates the list itself; the leftover table cannot overflow, every group adds at most one
+// tile to it), and the remaining CTAs zero `clear16` 16-byte words at `clear` (row maxima and tile counters of the
+// SwiGLU form), which saves a second planner launch and a memset per call.
+constexpr int PLAN_CLEAR_CTAS = 30;
+
+__global__ void __launch_bounds__(256) plan_groups_both_kernel(const int64_t* __restrict__ dev_list,
+                                                               const GroupEndsByValue by_value, int use_by_value,
+                                                               int64_t E, int64_t M, GroupedHeader* header,
+                                                               TileEntry* tiles, int64_t max_tiles,
+                                                               GroupedHeader* tail_header, TileEntry* tail_tiles,
+                                                               int64_t tail_max_tiles, int allow_prefix,
+                                                               uint4* __restrict__ clear, int64_t clear16)
+{
+    if (blockIdx.x == 0) {
+        plan_groups_body(dev_list, by_value, use_by_value, E, M, header, tiles, max_tiles, 256, PLAN_WHOLE, nullptr,
+                         allow_prefix);
+    } else if (blockIdx.x == 1) {
+        plan_groups_body(dev_list, by_value, use_by_value, E, M, tail_header, tail_tiles, tail_max_tiles, 128,
+                         PLAN_LEFTOVER, nullptr, allow_prefix);
+    } else {
+        const int64_t stride = static_cast<int64_t>(gridDim.x - 2) * blockDim.x;
+        for (int64_t i = static_cast<int64_t>(blockIdx.x - 2) * blockDim.x + threadIdx.x; i < clear16; i += stride) {
+            clear[i] = make_uint4(0u, 0u, 0u, 0u);
         }
     }
 }
@@ -505,7 +544,8 @@ static int check_host_group_list(const int64_t* group_list, int list_on_device, 
 
 // returns W8A8_OK or an error; launches the planner on `st`
 static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E, int64_t M,
-                       const GroupedWorkspace& g, int tile_m, cudaStream_t st, int mode = PLAN_ALL)
+                       const GroupedWorkspace& g, int tile_m, cudaStream_t st, int mode = PLAN_ALL,
+                       void* clear = nullptr, size_t clear_bytes = 0)
 {
     GroupedHeader* header = (mode == PLAN_LEFTOVER) ? g.tail_header : g.header;
     TileEntry* tiles = (mode == PLAN_LEFTOVER) ? g.tail_tiles : g.tiles;
@@ -540,8 +580,18 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
     if (smem > 48 * 1024) {
         return W8A8_ERR_UNSUPPORTED;
     }
-    plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, header, tiles, max_tiles, tile_m, mode,
-                                             shared_error, list_on_device == 2 ? 1 : 0); w8a8::note_launch();
+    if (mode == PLAN_BOTH) {
+        const int64_t clear16 = static_cast<int64_t>(clear_bytes / 16);
+        const unsigned grid = 2 + (clear16 > 0 ? PLAN_CLEAR_CTAS : 0);
+        plan_groups_both_kernel<<<grid, 256, smem, st>>>(dev_list, bv, use_bv, E, M, g.header, g.tiles, g.max_tiles,
+                                                         g.tail_header, g.tail_tiles, g.tail_max_tiles,
+                                                         list_on_device == 2 ? 1 : 0, static_cast<uint4*>(clear),
+                                                         clear16);
+    } else {
+        plan_groups_kernel<<<1, 256, smem, st>>>(dev_list, bv, use_bv, E, M, header, tiles, max_tiles, tile_m, mode,
+                                                 shared_error, list_on_device == 2 ? 1 : 0);
+    }
+    w8a8::note_launch();
     return (cudaGetLastError() == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
 }
 
@@ -549,7 +599,8 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
 // the kernel shape(s) choose_cta_group picked.
 template <int KIND, int EPI>
 static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E, int64_t M, const GroupedWorkspace& g,
-                       bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st)
+                       bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st,
+                       void* clear = nullptr, size_t clear_bytes = 0)
 {
     int shape = choose_cta_group(M, true);
     // Rows stored one by one at caller-given addresses (peer memory) are bound by the link, not by the tensor
@@ -559,7 +610,12 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
     }
     p.grouped = 1;
     p.error = &g.header->error;
+    // `clear` (the SwiGLU form's row maxima and tile counters) must be zero before the first matmul launch: the
+    // two-table planner does it in its own launch, the other shapes with a memset
     if (shape != GEMM_SHAPE_HYBRID) {
+        if (clear_bytes != 0 && cudaMemsetAsync(clear, 0, clear_bytes, st) != cudaSuccess) {
+            return W8A8_ERR_CUDA;
+        }
         const int rc = plan_groups(group_list, list_on_device, E, M, g, 128 * shape, st);
         if (rc != W8A8_OK) {
             return rc;
@@ -570,11 +626,7 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
         const cudaError_t e = dispatch_gemm<KIND, EPI>(shape, 256, b_mn, ta, tb, p, g.max_tiles * p.n_tiles, st);
         return (e == cudaSuccess) ? W8A8_OK : W8A8_ERR_CUDA;
     }
-    int rc = plan_groups(group_list, list_on_device, E, M, g, 256, st, PLAN_WHOLE);
-    if (rc != W8A8_OK) {
-        return rc;
-    }
-    rc = plan_groups(group_list, list_on_device, E, M, g, 128, st, PLAN_LEFTOVER);
+    const int rc = plan_groups(group_list, list_on_device, E, M, g, 256, st, PLAN_BOTH, clear, clear_bytes);
     if (rc != W8A8_OK) {
         return rc;
     }
@@ -782,10 +834,6 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         if (list_rc != W8A8_OK) {
             return list_rc;
         }
-        // row maxima and finished-tile counters start at zero
-        if (cudaMemsetAsync(g.amax, 0, g.clear_bytes, st) != cudaSuccess) {
-            return W8A8_ERR_CUDA;
-        }
         const bool b_mn = (w_layout == W8A8_W_KN);
         CUtensorMap ta, tb;
         if (!make_map_a(&ta, x, M, K, KIND_I8) || !make_map_b(&tb, w, E, N, K, KIND_I8, b_mn)) {
@@ -812,7 +860,9 @@ extern "C" int w8a8_grouped_matmul_swiglu_quant(const int8_t* x, const int8_t* w
         p.y_scale = y_scale;
         p.round_direct = (flags & W8A8_F_ROUND_DIRECT) ? 1 : 0;
         fused = p.fuse_requant != 0;
-        const int rc = run_grouped<KIND_I8, EPI_GMSQ>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
+        // row maxima and finished-tile counters start at zero
+        const int rc = run_grouped<KIND_I8, EPI_GMSQ>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st, g.amax,
+                                                      g.clear_bytes);
         if (rc != W8A8_OK) {
             return rc;
         }
