@@ -68,8 +68,6 @@ SIGNATURES = {
     "w8a8_expand_row_pointers": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "w8a8_grouped_matmul_to_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32,
                                            _i32, _i32, _vp, _sz, _vp]),
-    "w8a8_grouped_matmul_to_local_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _i32, _i32, _i32,
-                                           _i32, _i32, _vp, _sz, _vp]),
     "w8a8_moe_finalize_routing": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32,
                                          _i32, _i32, _vp]),
     "w8a8_moe_gating_top_k_softmax": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),

@@ -600,15 +600,12 @@ static int plan_groups(const int64_t* group_list, int list_on_device, int64_t E,
 template <int KIND, int EPI>
 static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E, int64_t M, const GroupedWorkspace& g,
                        bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st,
-                       void* clear = nullptr, size_t clear_bytes = 0, bool rows_may_be_remote = true)
+                       void* clear = nullptr, size_t clear_bytes = 0)
 {
     int shape = choose_cta_group(M, true);
     // Rows stored one by one at caller-given addresses (peer memory) are bound by the link, not by the tensor
     // pipe; single tiles spread those stores more evenly in time (3.34 ms against 3.83 ms on two GPUs).
-    // When the caller says that every destination is local the rule does not apply (one GPU: 26.4 - 27.0 ms per
-    // chain step with pairs against 28.0 - 28.3 ms with single tiles).
-    if (p.out_row_ptrs != nullptr && rows_may_be_remote && shape == GEMM_SHAPE_HYBRID &&
-        g_shape_override.load(std::memory_order_relaxed) == 0) {
+    if (p.out_row_ptrs != nullptr && shape == GEMM_SHAPE_HYBRID && g_shape_override.load(std::memory_order_relaxed) == 0) {
         shape = 1;
     }
     p.grouped = 1;
@@ -916,8 +913,7 @@ extern "C" size_t w8a8_grouped_matmul_f32_workspace_size(int64_t M, int64_t N, i
 static int grouped_matmul_impl(const void* x, const void* w, const void* bias, void* y, const uint64_t* out_row_ptrs,
                                const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
                                const int64_t* group_list, int list_on_device, int dtype, int bias_dtype,
-                               int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream,
-                               bool rows_may_be_remote = true)
+                               int out_dtype, int w_layout, void* workspace, size_t workspace_bytes, void* stream)
 {
     if (M < 0 || K <= 0 || N <= 0 || E <= 0) {
         return W8A8_ERR_INVALID;
@@ -1026,15 +1022,12 @@ static int grouped_matmul_impl(const void* x, const void* w, const void* bias, v
     p.out_dtype = out_dtype;
     p.n_tiles = static_cast<int32_t>((N + 255) / 256);
     if (kind == KIND_I8) {
-        return run_grouped<KIND_I8, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st, nullptr, 0,
-                                              rows_may_be_remote);
+        return run_grouped<KIND_I8, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
     }
     if (kind == KIND_F16) {
-        return run_grouped<KIND_F16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st, nullptr, 0,
-                                              rows_may_be_remote);
+        return run_grouped<KIND_F16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
     }
-    return run_grouped<KIND_BF16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st, nullptr, 0,
-                                              rows_may_be_remote);
+    return run_grouped<KIND_BF16, EPI_GMM>(group_list, list_on_device, E, M, g, b_mn, ta, tb, p, st);
 }
 
 extern "C" int w8a8_grouped_matmul(const void* x, const void* w, const void* bias, void* y, const float* x_scale,
@@ -1058,21 +1051,6 @@ extern "C" int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const v
     return grouped_matmul_impl(x, w, bias, nullptr, out_row_ptrs, x_scale, w_scale, M, N, K, E, group_list,
                                list_on_device, dtype, bias_dtype, out_dtype, w_layout, workspace, workspace_bytes,
                                stream);
-}
-
-extern "C" int w8a8_grouped_matmul_to_local_rows(const void* x, const void* w, const void* bias,
-                                                 const uint64_t* out_row_ptrs, const float* x_scale,
-                                                 const float* w_scale, int64_t M, int64_t N, int64_t K, int64_t E,
-                                                 const int64_t* group_list, int list_on_device, int dtype,
-                                                 int bias_dtype, int out_dtype, int w_layout, void* workspace,
-                                                 size_t workspace_bytes, void* stream)
-{
-    if (out_row_ptrs == nullptr) {
-        return W8A8_ERR_INVALID;
-    }
-    return grouped_matmul_impl(x, w, bias, nullptr, out_row_ptrs, x_scale, w_scale, M, N, K, E, group_list,
-                               list_on_device, dtype, bias_dtype, out_dtype, w_layout, workspace, workspace_bytes,
-                               stream, /*rows_may_be_remote=*/false);
 }
 
 extern "C" int w8a8_pipeline_error(void* stream)

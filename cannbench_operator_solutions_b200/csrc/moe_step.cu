@@ -359,10 +359,9 @@ extern "C" int w8a8_moe_ffn_step(const W8A8MoeFfnStep* s, const void* x, const v
     if (cudaStreamWaitEvent(st, side->join[1], 0) != cudaSuccess) {  // the output addresses are ready
         return W8A8_ERR_CUDA;
     }
-    // with one rank every row's home is this GPU: the matmul may use the kernel shape of an ordinary grouped matmul
-    const auto down_projection = (P == 1) ? w8a8_grouped_matmul_to_local_rows : w8a8_grouped_matmul_to_rows;
-    rc = down_projection(b.h, s->w_down, nullptr, b.out_ptrs, b.hs, s->s_down, cap, hidden, inter, e_local,
-                         b.group_list, 2, W8A8_DT_I8, W8A8_DT_F32, s->dtype, W8A8_W_KN, b.mm_ws, b.mm_ws_bytes, st);
+    rc = w8a8_grouped_matmul_to_rows(b.h, s->w_down, nullptr, b.out_ptrs, b.hs, s->s_down, cap, hidden, inter, e_local,
+                                     b.group_list, 2, W8A8_DT_I8, W8A8_DT_F32, s->dtype, W8A8_W_KN, b.mm_ws,
+                                     b.mm_ws_bytes, st);
     if (rc != W8A8_OK) {
         return rc;
     }

@@ -189,15 +189,15 @@ class CudaBackend:
             raise RuntimeError(f"grouped_matmul_swiglu_quant: {L.status_string(rc)}")
 
     def grouped_matmul_int8_to_rows_capacity(self, x, w, group_list_dev, x_scale, w_scale, out_row_ptrs, out_dtype,
-                                             workspace, all_local=False):
+                                             workspace):
         cap, k = x.shape
         e, _, n = w.shape
         L = self.L
         code = L.DT_BF16 if out_dtype == torch.bfloat16 else L.DT_F16
-        fn = self.lib.w8a8_grouped_matmul_to_local_rows if all_local else self.lib.w8a8_grouped_matmul_to_rows
-        rc = fn(x.data_ptr(), w.data_ptr(), None, out_row_ptrs.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(), cap,
-                n, k, e, group_list_dev.data_ptr(), 2, L.DT_I8, L.DT_F32, code, L.W_KN, workspace.data_ptr(),
-                workspace.numel(), self._st())
+        rc = self.lib.w8a8_grouped_matmul_to_rows(x.data_ptr(), w.data_ptr(), None, out_row_ptrs.data_ptr(),
+                                                  x_scale.data_ptr(), w_scale.data_ptr(), cap, n, k, e,
+                                                  group_list_dev.data_ptr(), 2, L.DT_I8, L.DT_F32, code, L.W_KN,
+                                                  workspace.data_ptr(), workspace.numel(), self._st())
         if rc != 0:
             raise RuntimeError(f"grouped_matmul_to_rows: {L.status_string(rc)}")
 
@@ -545,8 +545,7 @@ class MoeFfnChain:
         self._mark("grouped_matmul_swiglu_quant")
         b.expand_row_pointers_into(st["seg_first"], st["seg_ptr"], nseg, cap, hidden * elem, st["out_ptrs"])
         b.grouped_matmul_int8_to_rows_capacity(st["h"], self.shard.w_down, st["group_list"], st["hs"],
-                                               self.shard.s_down, st["out_ptrs"], x.dtype, st["workspace"],
-                                               all_local=(self.world == 1))
+                                               self.shard.s_down, st["out_ptrs"], x.dtype, st["workspace"])
         self._mark("down_projection_with_peer_stores")
         self._barrier(dev)   # every rank's output rows have landed at home
         self._mark("barrier_after_down_projection")

@@ -362,15 +362,6 @@ int w8a8_grouped_matmul_to_rows(const void* x, const void* w, const void* bias, 
                                 int bias_dtype, int out_dtype, int w_layout, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
-/* The same with the caller's word that every out_row_ptrs[r] lies in this GPU's own memory: the kernel shape is
- * then chosen as for w8a8_grouped_matmul (CTA pairs on 256-row blocks) instead of the single tiles that spread
- * stores to peers more evenly.  Identical results. */
-int w8a8_grouped_matmul_to_local_rows(const void* x, const void* w, const void* bias, const uint64_t* out_row_ptrs,
-                                      const float* x_scale, const float* w_scale, int64_t M, int64_t N, int64_t K,
-                                      int64_t E, const int64_t* group_list, int list_on_device, int dtype,
-                                      int bias_dtype, int out_dtype, int w_layout, void* workspace,
-                                      size_t workspace_bytes, void* stream);
-
 /* out[i, :] = sum_k probs[i, k] * rows[pos[i*topk+k], :], fp32, ascending k,
  * rounded to dtype (F16 / BF16).  A negative position contributes nothing. */
 int w8a8_combine(const void* rows, const float* probs, const int64_t* expanded_pos, void* out,
