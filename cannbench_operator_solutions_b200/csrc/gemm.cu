@@ -602,12 +602,10 @@ static int run_grouped(const int64_t* group_list, int list_on_device, int64_t E,
                        bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st,
                        void* clear = nullptr, size_t clear_bytes = 0)
 {
-    int shape = choose_cta_group(M, true);
-    // Rows stored one by one at caller-given addresses (peer memory) are bound by the link, not by the tensor
-    // pipe; single tiles spread those stores more evenly in time (3.34 ms against 3.83 ms on two GPUs).
-    if (p.out_row_ptrs != nullptr && shape == GEMM_SHAPE_HYBRID && g_shape_override.load(std::memory_order_relaxed) == 0) {
-        shape = 1;
-    }
+    const int shape = choose_cta_group(M, true);
+    // (Rows stored one by one at caller-given addresses, possibly in peer memory, use the same shapes.  Single
+    // tiles for them once measured faster on two GPUs; with the present kernels the chain steps are 13.26 against
+    // 13.25 - 13.5 ms on two GPUs, 7.62 against 7.73 - 7.83 ms on four and 26.4 against 28.0 ms on one.)
     p.grouped = 1;
     p.error = &g.header->error;
     // `clear` (the SwiGLU form's row maxima and tile counters) must be zero before the first matmul launch: the
