@@ -23,7 +23,7 @@ class GroupedSwigluQuantFromHost:
     device, ``chunk_rows`` rows travel and compute at a time over a copy-in stream, the current stream and a
     copy-out stream; a chunk may start and end inside an expert's rows."""
 
-    def __init__(self, weight: torch.Tensor, weight_scale: torch.Tensor, chunk_rows: int = 16384,
+    def __init__(self, weight: torch.Tensor, weight_scale: torch.Tensor, chunk_rows: int = 4096,
                  transpose_weight: bool = False):
         import ctypes
 
