@@ -29,22 +29,6 @@ constexpr int DQSQ_X_F16 = 1;
 constexpr int DQSQ_X_BF16 = 2;
 constexpr int DQSQ_THREADS = 256;
 
-// 16 bytes from global to shared memory without passing through registers (L1 bypassed), in groups that complete
-// in order.
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
-{
-    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit()
-{
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all_but_newest()
-{
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
-}
-
 template <int XT>
 struct DqsqChunk {
     static constexpr int EL = (XT == DQSQ_X_I32) ? 4 : 8;
@@ -194,54 +178,17 @@ __global__ void __launch_bounds__(DQSQ_THREADS, (CPT <= 2) ? 4 : 1) dqsq_rows_ke
     // where the gate half and the other half start, in the row and in weight_scale
     const int64_t g_off = left ? 0 : H, o_off = left ? H : 0;
     int parity = 0;
-    // Short rows (CPT <= 2) are fetched one row ahead: while the CTA works on a row, each thread's 16-byte pieces of
-    // the CTA's next row travel into shared memory with cp.async, so the arithmetic never starts with a wait on HBM.
-    // A thread only ever reads the pieces it copied itself, so no barrier guards the buffer.
-    constexpr bool AHEAD = (CPT <= 2);
-    __shared__ uint4 s_ahead[AHEAD ? 2 * 2 * CPT * DQSQ_THREADS : 1];
-    auto fetch_ahead = [&](int64_t r, int buf) {
-        if (r < M) {
-            const uint8_t* xn = static_cast<const uint8_t*>(x) + static_cast<size_t>(r) * 2 * H * elem;
-#pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const int c = tid + i * DQSQ_THREADS;
-                if (c < nchunks) {
-                    uint4* slot = s_ahead + (buf * 2 * CPT + 2 * i) * DQSQ_THREADS + tid;
-                    cp_async_16(slot, xn + (g_off + static_cast<int64_t>(c) * EL) * elem);
-                    cp_async_16(slot + DQSQ_THREADS, xn + (o_off + static_cast<int64_t>(c) * EL) * elem);
-                }
-            }
-        }
-        cp_async_commit();  // one group per row, empty past the last row
-    };
-    if constexpr (AHEAD) {
-        fetch_ahead(blockIdx.x, 0);
-    }
     for (int64_t row = blockIdx.x; row < M; row += gridDim.x, parity ^= 1) {
         const uint8_t* xr = static_cast<const uint8_t*>(x) + static_cast<size_t>(row) * 2 * H * elem;
         const float as = (XT == DQSQ_X_I32) ? activation_scale[row] : 1.0f;
+        // every load of the row is issued before the first is used
         uint4 ca[CPT], cb[CPT];
-        if constexpr (AHEAD) {
-            fetch_ahead(row + gridDim.x, parity ^ 1);
-            cp_async_wait_all_but_newest();  // this row's group has landed; the next row's may still be in flight
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const int c = tid + i * DQSQ_THREADS;
-                if (c < nchunks) {
-                    const uint4* slot = s_ahead + (parity * 2 * CPT + 2 * i) * DQSQ_THREADS + tid;
-                    ca[i] = slot[0];
-                    cb[i] = slot[DQSQ_THREADS];
-                }
-            }
-        } else {
-            // every load of the row is issued before the first is used
-#pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const int c = tid + i * DQSQ_THREADS;
-                if (c < nchunks) {
-                    ca[i] = C::load_raw(xr, g_off + static_cast<int64_t>(c) * EL);
-                    cb[i] = C::load_raw(xr, o_off + static_cast<int64_t>(c) * EL);
-                }
+        for (int i = 0; i < CPT; ++i) {
+            const int c = tid + i * DQSQ_THREADS;
+            if (c < nchunks) {
+                ca[i] = C::load_raw(xr, g_off + static_cast<int64_t>(c) * EL);
+                cb[i] = C::load_raw(xr, o_off + static_cast<int64_t>(c) * EL);
             }
         }
         float out[CPT][EL];
