@@ -128,6 +128,48 @@ def test_single_gpu_chain_peer_transport_equals_collective_transport(ops):
             tight.check()
 
 
+def test_native_step_captures_into_a_cuda_graph(ops):
+    """The C++ step enqueues everything on the caller's stream and on a second stream forked from and joined to it by
+    events, reads nothing back and allocates nothing: a stream capture follows both streams, and replaying the graph
+    after the inputs have been overwritten in place gives the result of an eager step on the new inputs."""
+    from test_ep_cpu import _problem
+
+    from cannbench_operator_solutions_b200.ep import ExpertShard, MoeFfnChain
+
+    experts, dev = 16, "cuda"
+    first = _problem(seed=7, tokens=256, hidden=512, inter=256, experts=experts, topk=4)
+    second = _problem(seed=8, tokens=256, hidden=512, inter=256, experts=experts, topk=4)
+    shard = ExpertShard(*(t.to(dev) for t in first[5:]))
+
+    def step_args(problem):
+        x, res, gamma, idx, probs = problem[:5]
+        return [x.to(dev), res.to(dev), gamma.to(dev), idx.to(dev), probs.to(dev)]
+
+    eager = MoeFfnChain(experts, shard, transport="p2p", device_tables=True)
+    want = []
+    for problem in (first, second):
+        x, res, gamma, idx, probs = step_args(problem)
+        out, x_out = eager.forward(x, res, gamma, 1e-6, idx, probs)
+        want.append((out.clone(), x_out.clone()))
+    eager.check()
+
+    chain = MoeFfnChain(experts, shard, transport="p2p", device_tables=True)
+    static = step_args(first)
+    chain.forward(static[0], static[1], static[2], 1e-6, static[3], static[4])  # first-use set-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out, x_out = chain.forward(static[0], static[1], static[2], 1e-6, static[3], static[4])
+    assert chain._native is not None
+    for problem, (want_out, want_x) in ((first, want[0]), (second, want[1]), (first, want[0])):
+        for dst, src in zip(static, step_args(problem)):
+            dst.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want_out) and torch.equal(x_out, want_x)
+    chain.check()
+
+
 def test_moe_ffn_step_argument_checks(ops):
     """The C++ step function validates its description before it touches the GPU."""
     import ctypes
