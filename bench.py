@@ -1346,6 +1346,12 @@ def main():
                          "traffic_source": primary["traffic_source"], "kernel_ms": ms_kernel,
                          "peak_source": peak_note},
         }
+        if wl.bound == "tensor":
+            # the timed region sits inside a sustained-load window under the power cap: the sustained cuBLAS figure
+            # beside the burst one that `peak` and `frac` use
+            sustained = peaks["bf16_tflops_sustained"] * INT8_PER_BF16
+            line["roofline"]["peak_sustained"] = sustained
+            line["roofline"]["frac_of_sustained"] = achieved / sustained
         if probe is not None:
             line["roofline"]["int8_issue_probe"] = probe
         if ms_plain_read is not None:
