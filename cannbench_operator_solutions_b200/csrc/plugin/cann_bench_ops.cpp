@@ -87,6 +87,17 @@ std::vector<int64_t> all_but_last(const Tensor& t)
     return std::vector<int64_t>(t.sizes().begin(), t.sizes().end() - 1);
 }
 
+// The shape functions (the Meta implementations) state their rules with the same vocabulary as Call::in: a rank
+// range (hi < 0: no upper bound) and a set of element types per argument.
+void rank_between(const Tensor& t, int lo, int hi, const char* message)
+{
+    TORCH_CHECK(t.dim() >= lo && (hi < 0 || t.dim() <= hi), message);
+}
+void type_among(const Tensor& t, unsigned types, const char* message)
+{
+    TORCH_CHECK((type_bit(t) & types) != 0u, message);
+}
+
 // One operator invocation: device guard, stream, argument intake, status translation.
 class Call {
 public:
@@ -204,8 +215,8 @@ struct DynamicQuant {
 
     static Out shape(const Tensor& x)
     {
-        TORCH_CHECK(x.dim() >= 2, "dynamic_quant requires a tensor with rank >= 2.");
-        TORCH_CHECK((type_bit(x) & HALVES) != 0u, "dynamic_quant only supports float16 / bfloat16 inputs.");
+        rank_between(x, 2, -1, "dynamic_quant requires a tensor with rank >= 2.");
+        type_among(x, HALVES, "dynamic_quant only supports float16 / bfloat16 inputs.");
         return {torch::empty_like(x, x.options().dtype(torch::kChar)),
                 torch::empty(all_but_last(x), x.options().dtype(torch::kFloat))};
     }
@@ -233,12 +244,12 @@ struct AddRmsNormDynamicQuant {
 
     static Out shape(const Tensor& x1, const Tensor& x2, const Tensor& gamma, double /*epsilon*/)
     {
-        TORCH_CHECK(x1.dim() >= 1, "add_rms_norm_dynamic_quant: x1 must have at least one dimension.");
-        TORCH_CHECK(x1.sizes() == x2.sizes(), "add_rms_norm_dynamic_quant: x1 and x2 must share a shape.");
-        TORCH_CHECK(gamma.dim() == 1 && gamma.size(0) == x1.size(-1),
-                    "add_rms_norm_dynamic_quant: gamma must be 1-D with size == x1.size(-1).");
-        TORCH_CHECK(gamma.scalar_type() == x1.scalar_type(),
-                    "add_rms_norm_dynamic_quant: gamma dtype must match x1 dtype.");
+        rank_between(x1, 1, -1, "add_rms_norm_dynamic_quant: x1 must have at least one dimension.");
+        TORCH_CHECK(x2.sizes().equals(x1.sizes()), "add_rms_norm_dynamic_quant: x1 and x2 must share a shape.");
+        const char* gamma_shape = "add_rms_norm_dynamic_quant: gamma must be 1-D with size == x1.size(-1).";
+        rank_between(gamma, 1, 1, gamma_shape);
+        TORCH_CHECK(gamma.size(0) == x1.size(-1), gamma_shape);
+        type_among(gamma, type_bit(x1), "add_rms_norm_dynamic_quant: gamma dtype must match x1 dtype.");
         return {torch::empty_like(x1, x1.options().dtype(torch::kChar)), torch::empty_like(x1),
                 torch::empty(all_but_last(x1), x1.options().dtype(torch::kFloat))};
     }
@@ -274,8 +285,9 @@ struct QuantMatmul {
                         const OptTensor& /*pertoken_scale*/, const OptTensor& /*bias*/,
                         const c10::optional<std::string>& output_dtype)
     {
-        TORCH_CHECK(x1.dim() >= 2 && x2.dim() >= 2, "quant_matmul requires inputs of rank >= 2.");
-        TORCH_CHECK(x1.size(-1) == x2.size(-2), "quant_matmul requires x1.size(-1) == x2.size(-2).");
+        rank_between(x1, 2, -1, "quant_matmul requires inputs of rank >= 2.");
+        rank_between(x2, 2, -1, "quant_matmul requires inputs of rank >= 2.");
+        TORCH_CHECK(x2.size(-2) == x1.size(-1), "quant_matmul requires x1.size(-1) == x2.size(-2).");
         std::vector<int64_t> dims = all_but_last(x1);
         dims.push_back(x2.size(-1));
         const bool bf16 = output_dtype.has_value() && *output_dtype == "bfloat16";
@@ -380,8 +392,8 @@ struct GroupedMatmulSwigluQuant {
     static Out shape(const Tensor& x, const Tensor& weight, const Tensor& /*weight_scale*/, const Tensor& /*x_scale*/,
                      c10::List<int64_t> /*group_list*/)
     {
-        TORCH_CHECK(x.dim() == 2, "grouped_matmul_swiglu_quant: x must be 2D [M, K]");
-        TORCH_CHECK(weight.dim() == 3, "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]");
+        rank_between(x, 2, 2, "grouped_matmul_swiglu_quant: x must be 2D [M, K]");
+        rank_between(weight, 3, 3, "grouped_matmul_swiglu_quant: weight must be 3D [E, K, N]");
         TORCH_CHECK(weight.size(2) % 2 == 0, "grouped_matmul_swiglu_quant: N must be even");
         return {torch::empty({x.size(0), weight.size(2) / 2}, x.options().dtype(torch::kChar)),
                 torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32))};
@@ -460,8 +472,8 @@ struct GroupedMatmul {
 
     static Tensor joined(const Tensor& x, const Tensor& weight, bool transpose_weight, const OptTensor& x_scale)
     {
-        TORCH_CHECK(x.dim() == 2, "grouped_matmul: x must be 2D [M, K]");
-        TORCH_CHECK(weight.dim() == 3, "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]");
+        rank_between(x, 2, 2, "grouped_matmul: x must be 2D [M, K]");
+        rank_between(weight, 3, 3, "grouped_matmul: weight must be 3D [E, K, N] or [E, N, K]");
         const int64_t n = weight.size(transpose_weight ? 1 : 2);
         // the quantised form (this build's extension) always answers in bfloat16
         return torch::empty({x.size(0), n}, given(x_scale) ? x.options().dtype(torch::kBFloat16) : x.options());
@@ -533,8 +545,8 @@ struct MoeReRouting {
     static Out shape(const Tensor& tokens, const Tensor& counts, const OptTensor& /*scales*/,
                      int64_t /*expert_token_num_type*/, int64_t /*idx_type*/)
     {
-        TORCH_CHECK(tokens.dim() == 2, "moe_re_routing: tokens must be 2D (A, H).");
-        TORCH_CHECK(counts.dim() == 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
+        rank_between(tokens, 2, 2, "moe_re_routing: tokens must be 2D (A, H).");
+        rank_between(counts, 2, 2, "moe_re_routing: expert_token_num_per_rank must be 2D (N, E).");
         const int64_t a = tokens.size(0);
         const auto like = tokens.options();
         return {torch::empty({a, tokens.size(1)}, like), torch::empty({a}, like.dtype(torch::kFloat)),
@@ -577,7 +589,7 @@ struct MoeFinalizeRouting {
 
     static Dims dims(const Tensor& rows, const Tensor& src_to_dst, const OptTensor& scales)
     {
-        TORCH_CHECK(rows.dim() >= 2, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
+        rank_between(rows, 2, -1, "moe_finalize_routing: expanded_permuted_rows must have rank >= 2.");
         TORCH_CHECK(src_to_dst.scalar_type() == torch::kInt,
                     "moe_finalize_routing: expanded_src_to_dst_row must be int32.");
         TORCH_CHECK(!given(scales) || scales->dim() == 2, "moe_finalize_routing: scales must be 2-D (NUM_ROWS, K).");
@@ -598,8 +610,7 @@ struct MoeFinalizeRouting {
     static Tensor run(const Tensor& rows, const Tensor& src_to_dst, OptTensor skip1, OptTensor skip2, OptTensor bias,
                       OptTensor scales, OptTensor expert, int64_t drop_pad_mode)
     {
-        TORCH_CHECK((type_bit(rows) & FLOATS) != 0u,
-                    "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.");
+        type_among(rows, FLOATS, "moe_finalize_routing: expanded_permuted_rows must be float16 / float32 / bfloat16.");
         Call call("moe_finalize_routing", rows);
         const Dims d = dims(rows, src_to_dst, scales);
         Tensor out = torch::empty({d.tokens, d.hidden}, rows.options());
@@ -638,9 +649,8 @@ struct MoeGatingTopKSoftmax {
 
     static Out shape(const Tensor& x, const OptTensor& finished, int64_t k)
     {
-        TORCH_CHECK((type_bit(x) & FLOATS) != 0u,
-                    "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.");
-        TORCH_CHECK(x.dim() >= 2, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.");
+        type_among(x, FLOATS, "cann_bench.moe_gating_top_k_softmax only supports float32, float16 and bfloat16 inputs.");
+        rank_between(x, 2, -1, "cann_bench.moe_gating_top_k_softmax requires a tensor with rank >= 2.");
         TORCH_CHECK(x.size(-1) > 0, "cann_bench.moe_gating_top_k_softmax requires a non-empty last dimension.");
         TORCH_CHECK(k > 0 && k <= x.size(-1), "cann_bench.moe_gating_top_k_softmax requires 0 < k <= x.size(-1).");
         TORCH_CHECK(!given(finished) || finished->scalar_type() == torch::kBool,
@@ -676,7 +686,7 @@ struct DequantSwigluQuant {
     static Out shape(const Tensor& x, const OptTensor& /*weight_scale*/, const OptTensor& /*activation_scale*/,
                      const OptTensor& /*quant_scale*/, bool /*activate_left*/)
     {
-        TORCH_CHECK(x.dim() == 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
+        rank_between(x, 2, 2, "dequant_swiglu_quant requires a 2D input [TokensNum, 2H].");
         TORCH_CHECK(x.size(1) % 2 == 0, "dequant_swiglu_quant requires an even last dimension.");
         return {torch::empty({x.size(0), x.size(1) / 2}, x.options().dtype(torch::kChar)),
                 torch::empty({x.size(0)}, x.options().dtype(torch::kFloat))};
