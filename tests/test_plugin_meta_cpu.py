@@ -7,7 +7,10 @@ import torch
 @pytest.fixture(scope="module")
 def cb():
     import cannbench_operator_solutions_b200 as pkg
+    from cannbench_operator_solutions_b200 import build
 
+    build.build_library()  # no-ops when the in-tree libraries are up to date
+    build.build_plugin()
     pkg.load_torch_plugin()
     return torch.ops.cann_bench
 
