@@ -170,6 +170,33 @@ def test_native_step_captures_into_a_cuda_graph(ops):
     chain.check()
 
 
+def test_chain_with_requantisation_inside_the_matmul_kernels(ops):
+    """The optional in-kernel requantisation of grouped_matmul_swiglu_quant on the chain's capacity-sized buffers (a
+    device group list that ends below the row capacity): same bits as the default two-kernel form."""
+    from test_ep_cpu import _problem
+
+    from cannbench_operator_solutions_b200 import _lib as L
+    from cannbench_operator_solutions_b200.ep import ExpertShard, MoeFfnChain
+
+    experts, dev = 8, "cuda"
+    problem = _problem(seed=11, tokens=700, hidden=512, inter=384, experts=experts, topk=4)   # 2800 routed rows
+    shard = ExpertShard(*(t.to(dev) for t in problem[5:]))
+    x, res, gamma, idx, probs = (t.to(dev) for t in problem[:5])
+    lib = L.load()
+    results = []
+    try:
+        for fused in (0, 1):
+            lib.w8a8_set_gmsq_fused_requant(fused)
+            chain = MoeFfnChain(experts, shard, transport="p2p", device_tables=True)
+            out, x_out = chain.forward(x, res, gamma, 1e-6, idx, probs)
+            chain.check()
+            results.append((out.clone(), x_out.clone()))
+    finally:
+        lib.w8a8_set_gmsq_fused_requant(0)
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    assert lib.w8a8_pipeline_error(None) == 0
+
+
 def test_moe_ffn_step_argument_checks(ops):
     """The C++ step function validates its description before it touches the GPU."""
     import ctypes
