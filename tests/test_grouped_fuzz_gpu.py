@@ -16,11 +16,15 @@ def force_shape():
 
     lib = L.load()
 
-    def _set(shape):
+    def _set(shape, epilogue_warps=16, fused_requant=0):
         assert lib.w8a8_set_gemm_shape(0 if shape == "auto" else int(shape)) >= 0
+        assert lib.w8a8_set_gmsq_epilogue_warps(epilogue_warps) in (8, 16)
+        lib.w8a8_set_gmsq_fused_requant(fused_requant)
 
     yield _set
     lib.w8a8_set_gemm_shape(0)
+    lib.w8a8_set_gmsq_epilogue_warps(16)
+    lib.w8a8_set_gmsq_fused_requant(0)
 
 
 SPECIAL = [0, 0, 1, 2, 7, 63, 64, 65, 127, 128, 129, 130, 200, 255, 256, 257, 300, 383, 384, 385, 511, 512, 513, 700]
@@ -29,7 +33,8 @@ SPECIAL = [0, 0, 1, 2, 7, 63, 64, 65, 127, 128, 129, 130, 200, 255, 256, 257, 30
 @pytest.mark.parametrize("shape", ["auto", "1", "2", "3"])
 @pytest.mark.parametrize("seed", [11, 12])
 def test_random_grouped_problems_match_the_oracle(ops, oracle, force_shape, shape, seed):
-    force_shape(shape)
+    # the second seed also runs the SwiGLU kernels' other forms: eight epilogue warps, requantisation in the kernel
+    force_shape(shape, epilogue_warps=16 if seed == 11 else 8, fused_requant=0 if seed == 11 else 1)
     rng = np.random.default_rng(seed)
     for case in range(12):
         e = int(rng.integers(1, 24))
